@@ -1,0 +1,218 @@
+/*
+ * moe_b200_sampler.h — C ABI of the B200 (sm_100a) generation sampler and MoE
+ * router Top-K.  Plain C, opaque handle, integer status per call and per row,
+ * caller-owned buffers, no exceptions.  Every entry point below names the
+ * reference interface it stands in for (paths are relative to the
+ * ncnn-MoE-Runtime source tree).
+ *
+ * Threading: a handle serialises nothing.  Use one handle per host thread /
+ * CUDA stream; calls on one handle must be issued in stream order on a single
+ * stream because they share the handle's device workspace.
+ *
+ * There is no CPU fallback: every function that computes requires a CUDA
+ * device of compute capability 10.x and fails with MOE_STATUS_CUDA_ERROR
+ * otherwise.
+ */
+#ifndef MOE_B200_SAMPLER_H
+#define MOE_B200_SAMPLER_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Call status.  Values 1..5 are ErrorCode + 1 of include/ncnn/moe/result.h:12-19. */
+enum moe_status
+{
+    MOE_STATUS_OK = 0,
+    MOE_STATUS_INVALID_ARGUMENT = 1,
+    MOE_STATUS_IO_ERROR = 2,
+    MOE_STATUS_INVALID_MODEL = 3,
+    MOE_STATUS_UNSUPPORTED_MODEL = 4,
+    MOE_STATUS_INTERNAL_ERROR = 5,
+    MOE_STATUS_CUDA_ERROR = 6
+};
+
+/* Per-row result code written to `row_status`.  1..6 carry the fixed messages
+ * of src/engine/session.cpp:67-72,85,103,399,421; moe_row_status_message()
+ * returns the text and moe_row_status_error_code() the ErrorCode + 1. */
+enum moe_row_status
+{
+    MOE_ROW_OK = 0,
+    MOE_ROW_EMPTY_LOGITS = 1,        /* "cannot sample empty logits" */
+    MOE_ROW_BAD_TEMPERATURE = 2,     /* "temperature must be finite and non-negative" */
+    MOE_ROW_BAD_TOP_P = 3,           /* "top_p must be in the range (0, 1]" */
+    MOE_ROW_BAD_MIN_P = 4,           /* "min_p must be in the range [0, 1]" */
+    MOE_ROW_NO_FINITE_LOGIT = 5,     /* "sampling requires at least one finite logit" */
+    MOE_ROW_INVALID_DISTRIBUTION = 6,/* "sampling distribution is invalid" */
+    MOE_ROW_WORKSPACE_EXHAUSTED = 7  /* library limit, no reference counterpart */
+};
+
+enum moe_dtype
+{
+    MOE_DTYPE_F32 = 0,
+    MOE_DTYPE_BF16 = 1 /* widened exactly (bits << 16), src/kernels/cpu_bfloat16.cpp:26-28 */
+};
+
+/* Bits of the per-row `row_flags` output. */
+#define MOE_ROW_FLAG_STOP_TOKEN 1u   /* StreamToken::is_stop_token, include/ncnn/moe/session.h:63-72 */
+#define MOE_ROW_FLAG_USED_UNIFORM 2u /* the reference would have advanced its RNG (session.cpp:429-433) */
+
+/* Largest top_k served by the shared-memory radix select; larger values (and
+ * top_k = 0) take the exact full-vocabulary path. */
+#define MOE_SAMPLER_TOPK_FAST_MAX 1024u
+
+/* One row = one Session's SamplingOptions (include/ncnn/moe/session.h:49-55)
+ * plus the counter-based RNG coordinates that replace the Session's private
+ * std::mt19937_64 (session.h:303; session.cpp:291,432-433).  The uniform of a
+ * row is Philox4x32-10 with key = seed, counter = (row_id, step + step_offset):
+ * u = (word0 >> 8) * 2^-24. */
+typedef struct moe_row_params
+{
+    float temperature; /* 0 = greedy */
+    uint32_t top_k;    /* 0 = off */
+    float top_p;       /* (0, 1] */
+    float min_p;       /* [0, 1] */
+    uint64_t seed;
+    uint64_t row_id;
+    uint64_t step;
+} moe_row_params;
+
+typedef struct moe_sampler moe_sampler;
+
+/* ---- lifetime ----------------------------------------------------------- */
+
+/* Allocates the device workspace for batches of up to max_rows rows of up to
+ * max_vocab logits on CUDA device `device`.  No reference counterpart (the
+ * reference sampler is stateless apart from Session::random_generator_). */
+int moe_sampler_create(int device, uint32_t max_rows, uint32_t max_vocab, moe_sampler** out);
+void moe_sampler_destroy(moe_sampler* sampler);
+/* Text of the last failing call on this handle (never NULL). */
+const char* moe_sampler_last_error(const moe_sampler* sampler);
+
+const char* moe_row_status_message(int row_status);
+int moe_row_status_error_code(int row_status);
+
+/* The uniform a row would consume, computed on the host (same Philox as the
+ * kernels).  Replaces drawing from Session::random_generator_
+ * (src/engine/session.cpp:432-433). */
+float moe_philox_uniform(uint64_t seed, uint64_t row_id, uint64_t step);
+
+/* Page-locked host memory for callers that stage logits themselves. */
+int moe_host_alloc(size_t bytes, void** out);
+void moe_host_free(void* pointer);
+
+/* ---- batched sampling --------------------------------------------------- */
+
+/* Replaces, for `rows` Sessions at once, the caller-side loop of
+ * examples/internal/run_model.cpp:776-809: one Session::sample
+ * (include/ncnn/moe/session.h:326; src/engine/session.cpp:393-443) per row
+ * with that row's options, then the stop-token test of run_model.cpp:790.
+ *
+ * logits            device, [rows x row_stride] elements of `dtype`, vocab <= row_stride
+ * params            HOST array of `rows` entries, or NULL to reuse the parameters
+ *                   uploaded by the previous call on this handle (same row count)
+ * step_offset       added to every row's `step` (lets resident parameters serve
+ *                   consecutive decode steps)
+ * stop_offsets      HOST, rows + 1 entries (CSR) or NULL; stop_tokens HOST or NULL
+ *                   (GenerationOptions::stop_tokens, session.h:78); reused with params
+ * token_id, probability  device, rows entries (SampledToken, session.h:57-61)
+ * row_flags, row_status  device, rows entries (may be NULL)
+ * topk_index        device, [rows x topk_stride] or NULL: for rows with
+ *                   0 < top_k <= MOE_SAMPLER_TOPK_FAST_MAX the first min(top_k, topk_stride)
+ *                   token ids of the reference rank order (session.cpp:80-87), -1 padded
+ * Asynchronous on `stream` (a cudaStream_t). */
+int moe_sample_batch(moe_sampler* sampler, void* stream, const void* logits, int dtype, uint32_t rows, uint32_t vocab,
+                     size_t row_stride, const moe_row_params* params, uint64_t step_offset, const int32_t* stop_offsets,
+                     const int32_t* stop_tokens, int32_t* token_id, float* probability, uint32_t* row_flags,
+                     int32_t* row_status, int32_t* topk_index, uint32_t topk_stride);
+
+/* Same operation with every buffer in HOST memory (what a Session-shaped
+ * caller holds: LogitsOutput::values is a std::vector<float>, session.h:30-33).
+ * Copies in, samples, copies out and synchronises before returning. */
+int moe_sample_batch_host(moe_sampler* sampler, const void* logits, int dtype, uint32_t rows, uint32_t vocab, size_t row_stride,
+                          const moe_row_params* params, const int32_t* stop_offsets, const int32_t* stop_tokens,
+                          int32_t* token_id, float* probability, uint32_t* row_flags, int32_t* row_status,
+                          int32_t* topk_index, uint32_t topk_stride);
+
+/* ---- vocabulary-sharded sampling ---------------------------------------- */
+
+/* Step 1 on every GPU: the stable Top-K of this GPU's vocabulary slice
+ * (src/engine/session.cpp:80-87 restricted to [vocab_begin, vocab_begin + vocab)).
+ * candidates: device, [rows x top_k] 64-bit records, best first:
+ *   (ordered_logit_bits << 32) | (0xFFFFFFFF - global_token_id); 0 = empty slot. */
+int moe_sample_local_candidates(moe_sampler* sampler, void* stream, const void* logits, int dtype, uint32_t rows, uint32_t vocab,
+                                size_t row_stride, uint32_t vocab_begin, uint32_t top_k, uint64_t* candidates);
+
+/* Step 2 after the caller's all-gather: `gathered` is device,
+ * [shards x rows x top_k] records; merges them to the global stable Top-K and
+ * finishes session.cpp:89-136,429-442 on it.  Requires 0 < top_k <=
+ * MOE_SAMPLER_TOPK_FAST_MAX for every row and temperature > 0. */
+int moe_sample_merge_candidates(moe_sampler* sampler, void* stream, const uint64_t* gathered, uint32_t shards, uint32_t rows,
+                                uint32_t top_k, const moe_row_params* params, uint64_t step_offset, int32_t* token_id,
+                                float* probability, uint32_t* row_flags, int32_t* row_status, int32_t* topk_index,
+                                uint32_t topk_stride);
+
+/* ---- MoE router ---------------------------------------------------------- */
+
+enum moe_router_score
+{
+    MOE_ROUTER_SOFTMAX = 0,
+    MOE_ROUTER_SIGMOID = 1,
+    MOE_ROUTER_SQRT_SOFTPLUS = 2 /* RouterScoreFunction, include/ncnn/moe/types.h:216-221 */
+};
+
+#define MOE_ROUTER_FLAG_NORMALIZE_TOPK 1u /* ExpertDispatchNormalizeTopKWeights, expert_dispatcher.h:27-32 */
+
+/* ExpertDispatchOptions (include/ncnn/moe/expert_dispatcher.h:34-44). */
+typedef struct moe_router_options
+{
+    uint32_t expert_count;
+    uint32_t top_k;
+    int32_t score_function;      /* moe_router_score */
+    int32_t normalization;       /* 0 None, 1 SelectedExperts (types.h:223-227) */
+    float routed_scaling_factor;
+    uint32_t flags;
+    const float* selection_bias;       /* device, expert_count entries, or NULL */
+    const uint32_t* explicit_expert_ids; /* device, token_count * top_k entries, or NULL */
+} moe_router_options;
+
+/* Replaces ExpertDispatcher::dispatch / dispatch_into
+ * (include/ncnn/moe/expert_dispatcher.h:57-60; src/graph/expert_dispatcher.cpp:79-301).
+ * The ExpertDispatchPlan comes back as CSR arrays (all device):
+ *   expert_offsets[expert_count + 1]  routes of expert e are [offsets[e], offsets[e+1])
+ *   route_token / route_rank / route_weight [token_count * top_k]  ExpertRoute fields,
+ *     experts ascending, inside an expert token ascending then rank ascending
+ *   plan_status[1]  0, or a router status value (see moe_router_status_message)
+ * Asynchronous on `stream`; the shape checks that need no data are done on the
+ * host and returned directly. */
+int moe_router_dispatch(moe_sampler* sampler, void* stream, const float* router_logits, uint32_t token_count,
+                        const moe_router_options* options, uint32_t* expert_offsets, uint32_t* route_token,
+                        uint32_t* route_rank, float* route_weight, int32_t* plan_status);
+/* plan_status values: 0, or 101.. with the reference's fixed messages
+ * (expert_dispatcher.cpp:81-101,128,136-137); moe_router_status_error_code()
+ * maps them to ErrorCode + 1.  moe_router_check_options() runs the checks that
+ * need no data (token count, top_k range, scaling factor) and returns such a
+ * value. */
+const char* moe_router_status_message(int plan_status);
+int moe_router_status_error_code(int plan_status);
+int moe_router_check_options(uint32_t token_count, const moe_router_options* options);
+
+/* Host-buffer form of the same call (router logits are a host span in the
+ * reference).  Synchronous. */
+int moe_router_dispatch_host(moe_sampler* sampler, const float* router_logits, uint32_t token_count,
+                             const moe_router_options* options_with_host_pointers, uint32_t* expert_offsets,
+                             uint32_t* route_token, uint32_t* route_rank, float* route_weight, int32_t* plan_status);
+
+/* Replaces gather_tokens (src/engine/cpu_executor.cpp:635-642): copies
+ * hidden[route_token[i], :] to gathered[i, :] for every route.  All device. */
+int moe_regroup_gather(moe_sampler* sampler, void* stream, const float* hidden, uint32_t token_count, uint32_t columns,
+                       const uint32_t* route_token, uint32_t route_count, float* gathered);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MOE_B200_SAMPLER_H */

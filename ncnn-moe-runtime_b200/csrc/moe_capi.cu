@@ -1,0 +1,624 @@
+// C ABI of the library (include/moe_b200_sampler.h): handle management,
+// argument checks, parameter upload, kernel launches, host-buffer variants.
+
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "moe_common.cuh"
+#include "moe_internal.h"
+
+using namespace moe;
+
+struct moe_sampler
+{
+    int device = 0;
+    int sm_count = 0;
+    uint32_t max_rows = 0;
+    uint32_t max_vocab = 0;
+    Workspace ws;
+    cudaStream_t stream = nullptr; // used by the host-buffer entry points
+
+    // resident per-row parameters and stop lists
+    moe_row_params* params_dev = nullptr;
+    int32_t* stop_offsets_dev = nullptr;
+    int32_t* stop_tokens_dev = nullptr;
+    size_t stop_tokens_capacity = 0;
+    uint32_t resident_rows = 0;
+    bool resident_needs_exact = false;
+    bool resident_has_stops = false;
+
+    // staging for the host-buffer entry points
+    void* logits_dev = nullptr;
+    size_t logits_dev_bytes = 0;
+    int32_t* token_dev = nullptr;
+    float* probability_dev = nullptr;
+    uint32_t* flags_dev = nullptr;
+    int32_t* status_dev = nullptr;
+    int32_t* topk_dev = nullptr;
+    size_t topk_dev_entries = 0;
+
+    // router scratch
+    uint32_t* selected_expert = nullptr;
+    float* selected_weight = nullptr;
+    size_t selected_capacity = 0;
+    uint32_t* expert_counts = nullptr;
+    size_t expert_counts_capacity = 0;
+    unsigned long long* router_error = nullptr;
+    // router host staging
+    float* router_logits_dev = nullptr;
+    size_t router_logits_capacity = 0;
+    float* router_bias_dev = nullptr;
+    uint32_t* router_explicit_dev = nullptr;
+    size_t router_bias_capacity = 0;
+    size_t router_explicit_capacity = 0;
+    uint32_t* router_offsets_dev = nullptr;
+    size_t router_offsets_capacity = 0;
+    uint32_t* router_token_dev = nullptr;
+    uint32_t* router_rank_dev = nullptr;
+    float* router_weight_dev = nullptr;
+    size_t router_route_capacity = 0;
+    int32_t* router_status_dev = nullptr;
+
+    std::string last_error;
+};
+
+namespace {
+
+int fail(moe_sampler* sampler, int status, const std::string& text)
+{
+    if (sampler != nullptr)
+        sampler->last_error = text;
+    return status;
+}
+
+int fail_cuda(moe_sampler* sampler, cudaError_t error, const char* where)
+{
+    return fail(sampler, MOE_STATUS_CUDA_ERROR, std::string(where) + ": " + cudaGetErrorString(error));
+}
+
+#define MOE_CUDA_CHECK(sampler, call)                          \
+    do                                                         \
+    {                                                          \
+        const cudaError_t moe_cuda_status = (call);            \
+        if (moe_cuda_status != cudaSuccess)                    \
+            return fail_cuda((sampler), moe_cuda_status, #call); \
+    } while (0)
+
+template<typename T>
+cudaError_t grow(T*& pointer, size_t& capacity, size_t wanted)
+{
+    if (wanted <= capacity && pointer != nullptr)
+        return cudaSuccess;
+    if (pointer != nullptr)
+    {
+        cudaError_t status = cudaFree(pointer);
+        if (status != cudaSuccess)
+            return status;
+        pointer = nullptr;
+        capacity = 0;
+    }
+    const size_t entries = wanted > 0 ? wanted : 1;
+    cudaError_t status = cudaMalloc(reinterpret_cast<void**>(&pointer), entries * sizeof(T));
+    if (status == cudaSuccess)
+        capacity = entries;
+    return status;
+}
+
+struct DeviceGuard
+{
+    int previous = -1;
+    explicit DeviceGuard(int device)
+    {
+        cudaGetDevice(&previous);
+        if (previous != device)
+            cudaSetDevice(device);
+        else
+            previous = -1;
+    }
+    ~DeviceGuard()
+    {
+        if (previous >= 0)
+            cudaSetDevice(previous);
+    }
+};
+
+// Uploads per-row parameters (and stop lists) and records what the rows may need.
+int upload_rows(moe_sampler* sampler, cudaStream_t stream, uint32_t rows, const moe_row_params* params, const int32_t* stop_offsets,
+                const int32_t* stop_tokens)
+{
+    bool needs_exact = false;
+    for (uint32_t row = 0; row < rows; ++row)
+    {
+        const moe_row_params& p = params[row];
+        if (validate_row(p) != MOE_ROW_OK || p.temperature == 0.0f)
+            continue;
+        if (p.top_k == 0 || p.top_k > MOE_SAMPLER_TOPK_FAST_MAX)
+            needs_exact = true;
+    }
+    // pageable source: the runtime stages the bytes before returning, so the
+    // caller's array may be reused at once
+    MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(sampler->params_dev, params, sizeof(moe_row_params) * rows, cudaMemcpyHostToDevice, stream));
+    sampler->resident_has_stops = false;
+    if (stop_offsets != nullptr && stop_tokens != nullptr)
+    {
+        const size_t total = static_cast<size_t>(stop_offsets[rows]);
+        if (total > 0)
+        {
+            if (total > sampler->stop_tokens_capacity)
+            {
+                MOE_CUDA_CHECK(sampler, cudaStreamSynchronize(stream));
+                MOE_CUDA_CHECK(sampler, grow(sampler->stop_tokens_dev, sampler->stop_tokens_capacity, total));
+            }
+            MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(sampler->stop_offsets_dev, stop_offsets, sizeof(int32_t) * (rows + 1), cudaMemcpyHostToDevice, stream));
+            MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(sampler->stop_tokens_dev, stop_tokens, sizeof(int32_t) * total, cudaMemcpyHostToDevice, stream));
+            sampler->resident_has_stops = true;
+        }
+    }
+    sampler->resident_rows = rows;
+    sampler->resident_needs_exact = needs_exact;
+    return MOE_STATUS_OK;
+}
+
+int check_shape(moe_sampler* sampler, int dtype, uint32_t rows, uint32_t vocab, size_t row_stride)
+{
+    if (sampler == nullptr)
+        return MOE_STATUS_INVALID_ARGUMENT;
+    if (dtype != MOE_DTYPE_F32 && dtype != MOE_DTYPE_BF16)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "dtype must be MOE_DTYPE_F32 or MOE_DTYPE_BF16");
+    if (vocab == 0)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "cannot sample empty logits");
+    if (rows > sampler->max_rows)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "rows exceed the max_rows the sampler was created with");
+    if (vocab > sampler->max_vocab)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "vocab exceeds the max_vocab the sampler was created with");
+    if (row_stride < vocab)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "row_stride is smaller than vocab");
+    if (vocab > 0x7FFFFFFFu)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "vocab does not fit a 32-bit token id");
+    return MOE_STATUS_OK;
+}
+
+} // namespace
+
+extern "C" {
+
+int moe_sampler_create(int device, uint32_t max_rows, uint32_t max_vocab, moe_sampler** out)
+{
+    if (out == nullptr || max_rows == 0 || max_vocab == 0)
+        return MOE_STATUS_INVALID_ARGUMENT;
+    *out = nullptr;
+    int device_count = 0;
+    if (cudaGetDeviceCount(&device_count) != cudaSuccess || device < 0 || device >= device_count)
+        return MOE_STATUS_CUDA_ERROR;
+    cudaDeviceProp properties;
+    if (cudaGetDeviceProperties(&properties, device) != cudaSuccess)
+        return MOE_STATUS_CUDA_ERROR;
+    if (properties.major != 10)
+        return MOE_STATUS_CUDA_ERROR; // the kernels are built for sm_100a only
+    moe_sampler* sampler = new (std::nothrow) moe_sampler();
+    if (sampler == nullptr)
+        return MOE_STATUS_INTERNAL_ERROR;
+    sampler->device = device;
+    sampler->sm_count = properties.multiProcessorCount;
+    sampler->max_rows = max_rows;
+    sampler->max_vocab = max_vocab;
+    DeviceGuard guard(device);
+    Workspace& ws = sampler->ws;
+    ws.max_rows = max_rows;
+    ws.max_vocab = max_vocab;
+    ws.slots = max_rows < static_cast<uint32_t>(sampler->sm_count) ? max_rows : static_cast<uint32_t>(sampler->sm_count);
+    const size_t stride = (static_cast<size_t>(max_vocab) + 3u) & ~static_cast<size_t>(3u);
+    cudaError_t status = cudaSuccess;
+    auto allocate = [&](void** pointer, size_t bytes) {
+        if (status == cudaSuccess)
+            status = cudaMalloc(pointer, bytes);
+    };
+    uint32_t* counters = nullptr;
+    allocate(reinterpret_cast<void**>(&counters), 2 * sizeof(uint32_t));
+    allocate(reinterpret_cast<void**>(&ws.exact_rows), sizeof(uint32_t) * max_rows);
+    allocate(reinterpret_cast<void**>(&ws.sort_keys), sizeof(uint32_t) * 4u * stride * ws.slots);
+    allocate(reinterpret_cast<void**>(&sampler->params_dev), sizeof(moe_row_params) * max_rows);
+    allocate(reinterpret_cast<void**>(&sampler->stop_offsets_dev), sizeof(int32_t) * (static_cast<size_t>(max_rows) + 1));
+    allocate(reinterpret_cast<void**>(&sampler->token_dev), sizeof(int32_t) * max_rows);
+    allocate(reinterpret_cast<void**>(&sampler->probability_dev), sizeof(float) * max_rows);
+    allocate(reinterpret_cast<void**>(&sampler->flags_dev), sizeof(uint32_t) * max_rows);
+    allocate(reinterpret_cast<void**>(&sampler->status_dev), sizeof(int32_t) * max_rows);
+    allocate(reinterpret_cast<void**>(&sampler->router_error), sizeof(unsigned long long));
+    allocate(reinterpret_cast<void**>(&sampler->router_status_dev), sizeof(int32_t));
+    if (status == cudaSuccess)
+        status = cudaMemset(counters, 0, 2 * sizeof(uint32_t));
+    if (status == cudaSuccess)
+        status = cudaMemset(sampler->router_error, 0xFF, sizeof(unsigned long long));
+    if (status == cudaSuccess)
+        status = cudaStreamCreateWithFlags(&sampler->stream, cudaStreamNonBlocking);
+    if (status == cudaSuccess)
+        status = cudaDeviceSynchronize();
+    ws.exact_count = counters;
+    ws.exact_done = counters != nullptr ? counters + 1 : nullptr;
+    if (status != cudaSuccess)
+    {
+        moe_sampler_destroy(sampler);
+        return MOE_STATUS_CUDA_ERROR;
+    }
+    *out = sampler;
+    return MOE_STATUS_OK;
+}
+
+void moe_sampler_destroy(moe_sampler* sampler)
+{
+    if (sampler == nullptr)
+        return;
+    DeviceGuard guard(sampler->device);
+    cudaDeviceSynchronize();
+    void* pointers[] = {sampler->ws.exact_count, sampler->ws.exact_rows, sampler->ws.sort_keys, sampler->params_dev, sampler->stop_offsets_dev,
+                        sampler->stop_tokens_dev, sampler->logits_dev, sampler->token_dev, sampler->probability_dev, sampler->flags_dev,
+                        sampler->status_dev, sampler->topk_dev, sampler->selected_expert, sampler->selected_weight, sampler->expert_counts,
+                        sampler->router_error, sampler->router_logits_dev, sampler->router_bias_dev, sampler->router_explicit_dev,
+                        sampler->router_offsets_dev, sampler->router_token_dev, sampler->router_rank_dev, sampler->router_weight_dev,
+                        sampler->router_status_dev};
+    for (void* pointer : pointers)
+        if (pointer != nullptr)
+            cudaFree(pointer);
+    if (sampler->stream != nullptr)
+        cudaStreamDestroy(sampler->stream);
+    delete sampler;
+}
+
+const char* moe_sampler_last_error(const moe_sampler* sampler)
+{
+    return sampler != nullptr ? sampler->last_error.c_str() : "null sampler handle";
+}
+
+const char* moe_row_status_message(int row_status)
+{
+    switch (row_status)
+    {
+    case MOE_ROW_OK: return "";
+    case MOE_ROW_EMPTY_LOGITS: return "cannot sample empty logits";
+    case MOE_ROW_BAD_TEMPERATURE: return "temperature must be finite and non-negative";
+    case MOE_ROW_BAD_TOP_P: return "top_p must be in the range (0, 1]";
+    case MOE_ROW_BAD_MIN_P: return "min_p must be in the range [0, 1]";
+    case MOE_ROW_NO_FINITE_LOGIT: return "sampling requires at least one finite logit";
+    case MOE_ROW_INVALID_DISTRIBUTION: return "sampling distribution is invalid";
+    case MOE_ROW_WORKSPACE_EXHAUSTED: return "row does not fit the sampler workspace";
+    default: return "unknown row status";
+    }
+}
+
+int moe_row_status_error_code(int row_status)
+{
+    if (row_status == MOE_ROW_OK)
+        return MOE_STATUS_OK;
+    if (row_status == MOE_ROW_WORKSPACE_EXHAUSTED)
+        return MOE_STATUS_INTERNAL_ERROR;
+    return MOE_STATUS_INVALID_ARGUMENT;
+}
+
+float moe_philox_uniform(uint64_t seed, uint64_t row_id, uint64_t step)
+{
+    return philox_uniform(seed, row_id, step);
+}
+
+int moe_host_alloc(size_t bytes, void** out)
+{
+    if (out == nullptr)
+        return MOE_STATUS_INVALID_ARGUMENT;
+    return cudaMallocHost(out, bytes > 0 ? bytes : 1) == cudaSuccess ? MOE_STATUS_OK : MOE_STATUS_CUDA_ERROR;
+}
+
+void moe_host_free(void* pointer)
+{
+    if (pointer != nullptr)
+        cudaFreeHost(pointer);
+}
+
+int moe_sample_batch(moe_sampler* sampler, void* stream_handle, const void* logits, int dtype, uint32_t rows, uint32_t vocab, size_t row_stride,
+                     const moe_row_params* params, uint64_t step_offset, const int32_t* stop_offsets, const int32_t* stop_tokens,
+                     int32_t* token_id, float* probability, uint32_t* row_flags, int32_t* row_status, int32_t* topk_index, uint32_t topk_stride)
+{
+    if (int status = check_shape(sampler, dtype, rows, vocab, row_stride))
+        return status;
+    if (rows == 0)
+        return MOE_STATUS_OK;
+    if (logits == nullptr || token_id == nullptr || probability == nullptr)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "logits, token_id and probability must not be null");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+    DeviceGuard guard(sampler->device);
+    if (params != nullptr)
+    {
+        if (int status = upload_rows(sampler, stream, rows, params, stop_offsets, stop_tokens))
+            return status;
+    }
+    else if (sampler->resident_rows != rows)
+    {
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "params is null but no parameters for this row count are resident");
+    }
+    SampleArgs args = {};
+    args.logits = logits;
+    args.dtype = dtype;
+    args.rows = rows;
+    args.vocab = vocab;
+    args.row_stride = row_stride;
+    args.params = sampler->params_dev;
+    args.step_offset = step_offset;
+    args.stop_offsets = sampler->resident_has_stops ? sampler->stop_offsets_dev : nullptr;
+    args.stop_tokens = sampler->resident_has_stops ? sampler->stop_tokens_dev : nullptr;
+    args.token_id = token_id;
+    args.probability = probability;
+    args.row_flags = row_flags;
+    args.row_status = row_status;
+    args.topk_index = topk_index;
+    args.topk_stride = topk_index != nullptr ? topk_stride : 0;
+    const uint32_t splits = choose_splits(rows, vocab, dtype, sampler->sm_count);
+    MOE_CUDA_CHECK(sampler, launch_sample_rows(args, sampler->ws, splits, stream));
+    if (sampler->resident_needs_exact)
+        MOE_CUDA_CHECK(sampler, launch_sample_exact(args, sampler->ws, stream));
+    return MOE_STATUS_OK;
+}
+
+int moe_sample_batch_host(moe_sampler* sampler, const void* logits, int dtype, uint32_t rows, uint32_t vocab, size_t row_stride,
+                          const moe_row_params* params, const int32_t* stop_offsets, const int32_t* stop_tokens, int32_t* token_id,
+                          float* probability, uint32_t* row_flags, int32_t* row_status, int32_t* topk_index, uint32_t topk_stride)
+{
+    if (int status = check_shape(sampler, dtype, rows, vocab, row_stride))
+        return status;
+    if (rows == 0)
+        return MOE_STATUS_OK;
+    if (logits == nullptr || params == nullptr || token_id == nullptr || probability == nullptr)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "logits, params, token_id and probability must not be null");
+    DeviceGuard guard(sampler->device);
+    cudaStream_t stream = sampler->stream;
+    const size_t element = dtype == MOE_DTYPE_F32 ? 4 : 2;
+    const size_t bytes = ((static_cast<size_t>(rows) - 1) * row_stride + vocab) * element;
+    if (bytes > sampler->logits_dev_bytes)
+    {
+        unsigned char* pointer = static_cast<unsigned char*>(sampler->logits_dev);
+        MOE_CUDA_CHECK(sampler, grow(pointer, sampler->logits_dev_bytes, bytes));
+        sampler->logits_dev = pointer;
+    }
+    const size_t topk_entries = topk_index != nullptr ? static_cast<size_t>(rows) * topk_stride : 0;
+    if (topk_entries > sampler->topk_dev_entries)
+        MOE_CUDA_CHECK(sampler, grow(sampler->topk_dev, sampler->topk_dev_entries, topk_entries));
+    MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(sampler->logits_dev, logits, bytes, cudaMemcpyHostToDevice, stream));
+    const int status = moe_sample_batch(sampler, stream, sampler->logits_dev, dtype, rows, vocab, row_stride, params, 0, stop_offsets, stop_tokens,
+                                        sampler->token_dev, sampler->probability_dev, sampler->flags_dev, sampler->status_dev,
+                                        topk_entries > 0 ? sampler->topk_dev : nullptr, topk_stride);
+    if (status != MOE_STATUS_OK)
+        return status;
+    MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(token_id, sampler->token_dev, sizeof(int32_t) * rows, cudaMemcpyDeviceToHost, stream));
+    MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(probability, sampler->probability_dev, sizeof(float) * rows, cudaMemcpyDeviceToHost, stream));
+    if (row_flags != nullptr)
+        MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(row_flags, sampler->flags_dev, sizeof(uint32_t) * rows, cudaMemcpyDeviceToHost, stream));
+    if (row_status != nullptr)
+        MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(row_status, sampler->status_dev, sizeof(int32_t) * rows, cudaMemcpyDeviceToHost, stream));
+    if (topk_entries > 0)
+        MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(topk_index, sampler->topk_dev, sizeof(int32_t) * topk_entries, cudaMemcpyDeviceToHost, stream));
+    MOE_CUDA_CHECK(sampler, cudaStreamSynchronize(stream));
+    return MOE_STATUS_OK;
+}
+
+int moe_sample_local_candidates(moe_sampler* sampler, void* stream_handle, const void* logits, int dtype, uint32_t rows, uint32_t vocab,
+                                size_t row_stride, uint32_t vocab_begin, uint32_t top_k, uint64_t* candidates)
+{
+    if (int status = check_shape(sampler, dtype, rows, vocab, row_stride))
+        return status;
+    if (top_k == 0 || top_k > MOE_SAMPLER_TOPK_FAST_MAX)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "vocabulary-sharded sampling needs 0 < top_k <= MOE_SAMPLER_TOPK_FAST_MAX");
+    if (logits == nullptr || candidates == nullptr)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "logits and candidates must not be null");
+    if (rows == 0)
+        return MOE_STATUS_OK;
+    DeviceGuard guard(sampler->device);
+    SampleArgs args = {};
+    args.logits = logits;
+    args.dtype = dtype;
+    args.rows = rows;
+    args.vocab = vocab;
+    args.row_stride = row_stride;
+    args.candidates_out = candidates;
+    args.candidates_k = top_k;
+    args.vocab_begin = vocab_begin;
+    const uint32_t splits = choose_splits(rows, vocab, dtype, sampler->sm_count);
+    MOE_CUDA_CHECK(sampler, launch_sample_rows(args, sampler->ws, splits, static_cast<cudaStream_t>(stream_handle)));
+    return MOE_STATUS_OK;
+}
+
+int moe_sample_merge_candidates(moe_sampler* sampler, void* stream_handle, const uint64_t* gathered, uint32_t shards, uint32_t rows, uint32_t top_k,
+                                const moe_row_params* params, uint64_t step_offset, int32_t* token_id, float* probability, uint32_t* row_flags,
+                                int32_t* row_status, int32_t* topk_index, uint32_t topk_stride)
+{
+    if (sampler == nullptr)
+        return MOE_STATUS_INVALID_ARGUMENT;
+    if (rows > sampler->max_rows)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "rows exceed the max_rows the sampler was created with");
+    if (top_k == 0 || top_k > MOE_SAMPLER_TOPK_FAST_MAX || shards == 0)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "vocabulary-sharded sampling needs shards > 0 and 0 < top_k <= MOE_SAMPLER_TOPK_FAST_MAX");
+    if (gathered == nullptr || token_id == nullptr || probability == nullptr)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "gathered, token_id and probability must not be null");
+    if (rows == 0)
+        return MOE_STATUS_OK;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+    DeviceGuard guard(sampler->device);
+    if (params != nullptr)
+    {
+        if (int status = upload_rows(sampler, stream, rows, params, nullptr, nullptr))
+            return status;
+    }
+    else if (sampler->resident_rows != rows)
+    {
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "params is null but no parameters for this row count are resident");
+    }
+    MOE_CUDA_CHECK(sampler, launch_merge_candidates(gathered, shards, rows, top_k, sampler->params_dev, step_offset, token_id, probability, row_flags,
+                                                    row_status, topk_index, topk_index != nullptr ? topk_stride : 0, stream));
+    return MOE_STATUS_OK;
+}
+
+const char* moe_router_status_message(int plan_status)
+{
+    switch (plan_status)
+    {
+    case 0: return "";
+    case 101: return "router logits must be finite";
+    case 102: return "explicit expert id is out of range";
+    case 103: return "selected router weights have a non-positive sum";
+    case 104: return "expert dispatch requires at least one token";
+    case 105: return "expert dispatch requires 0 < top_k <= expert_count";
+    case 106: return "router logits shape does not match token and expert counts";
+    case 107: return "router selection bias must match expert_count";
+    case 108: return "explicit expert ids must match token_count * top_k";
+    case 109: return "routed scaling factor must be finite and positive";
+    case 110: return "expert_count exceeds the router kernel's limit of 4096";
+    default: return "unknown router status";
+    }
+}
+
+int moe_router_status_error_code(int plan_status)
+{
+    if (plan_status == 0)
+        return MOE_STATUS_OK;
+    if (plan_status == 103)
+        return MOE_STATUS_INVALID_MODEL;
+    if (plan_status == 110)
+        return MOE_STATUS_UNSUPPORTED_MODEL;
+    return MOE_STATUS_INVALID_ARGUMENT;
+}
+
+int moe_router_check_options(uint32_t token_count, const moe_router_options* options)
+{
+    // the data-independent checks of expert_dispatcher.cpp:81-96, in its order
+    if (options == nullptr)
+        return 105;
+    if (token_count == 0)
+        return 104;
+    if (options->expert_count == 0 || options->top_k == 0 || options->top_k > options->expert_count)
+        return 105;
+    const float scaling = options->routed_scaling_factor;
+    if (!(scaling - scaling == 0.0f) || scaling <= 0.0f)
+        return 109;
+    if (options->expert_count > 4096)
+        return 110;
+    return 0;
+}
+
+int moe_router_dispatch(moe_sampler* sampler, void* stream_handle, const float* router_logits, uint32_t token_count,
+                        const moe_router_options* options, uint32_t* expert_offsets, uint32_t* route_token, uint32_t* route_rank,
+                        float* route_weight, int32_t* plan_status)
+{
+    if (sampler == nullptr)
+        return MOE_STATUS_INVALID_ARGUMENT;
+    const int precheck = moe_router_check_options(token_count, options);
+    if (precheck != 0)
+        return fail(sampler, moe_router_status_error_code(precheck), moe_router_status_message(precheck));
+    if (router_logits == nullptr || expert_offsets == nullptr || route_token == nullptr || route_rank == nullptr || route_weight == nullptr ||
+        plan_status == nullptr)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "router buffers must not be null");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+    DeviceGuard guard(sampler->device);
+    const size_t routes = static_cast<size_t>(token_count) * options->top_k;
+    if (routes > sampler->selected_capacity || options->expert_count > sampler->expert_counts_capacity)
+    {
+        MOE_CUDA_CHECK(sampler, cudaStreamSynchronize(stream));
+        if (routes > sampler->selected_capacity)
+        {
+            size_t capacity = sampler->selected_capacity;
+            MOE_CUDA_CHECK(sampler, grow(sampler->selected_expert, capacity, routes));
+            MOE_CUDA_CHECK(sampler, grow(sampler->selected_weight, sampler->selected_capacity, routes));
+        }
+        if (options->expert_count > sampler->expert_counts_capacity)
+        {
+            MOE_CUDA_CHECK(sampler, grow(sampler->expert_counts, sampler->expert_counts_capacity, options->expert_count));
+            MOE_CUDA_CHECK(sampler, cudaMemset(sampler->expert_counts, 0, sizeof(uint32_t) * sampler->expert_counts_capacity));
+        }
+    }
+    RouterArgs args = {};
+    args.logits = router_logits;
+    args.token_count = token_count;
+    args.options = *options;
+    args.expert_offsets = expert_offsets;
+    args.route_token = route_token;
+    args.route_rank = route_rank;
+    args.route_weight = route_weight;
+    args.plan_status = plan_status;
+    args.selected_expert = sampler->selected_expert;
+    args.selected_weight = sampler->selected_weight;
+    MOE_CUDA_CHECK(sampler, launch_router_dispatch_kernels(args, sampler->expert_counts, sampler->router_error, stream));
+    return MOE_STATUS_OK;
+}
+
+int moe_router_dispatch_host(moe_sampler* sampler, const float* router_logits, uint32_t token_count, const moe_router_options* options,
+                             uint32_t* expert_offsets, uint32_t* route_token, uint32_t* route_rank, float* route_weight, int32_t* plan_status)
+{
+    if (sampler == nullptr)
+        return MOE_STATUS_INVALID_ARGUMENT;
+    const int precheck = moe_router_check_options(token_count, options);
+    if (precheck != 0)
+    {
+        if (plan_status != nullptr)
+            *plan_status = precheck;
+        return fail(sampler, moe_router_status_error_code(precheck), moe_router_status_message(precheck));
+    }
+    if (router_logits == nullptr || expert_offsets == nullptr || route_token == nullptr || route_rank == nullptr || route_weight == nullptr ||
+        plan_status == nullptr)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "router buffers must not be null");
+    DeviceGuard guard(sampler->device);
+    cudaStream_t stream = sampler->stream;
+    const uint32_t experts = options->expert_count;
+    const size_t logit_count = static_cast<size_t>(token_count) * experts;
+    const size_t routes = static_cast<size_t>(token_count) * options->top_k;
+    MOE_CUDA_CHECK(sampler, grow(sampler->router_logits_dev, sampler->router_logits_capacity, logit_count));
+    MOE_CUDA_CHECK(sampler, grow(sampler->router_offsets_dev, sampler->router_offsets_capacity, static_cast<size_t>(experts) + 1));
+    if (routes > sampler->router_route_capacity)
+    {
+        size_t a = sampler->router_route_capacity, b = sampler->router_route_capacity;
+        MOE_CUDA_CHECK(sampler, grow(sampler->router_token_dev, a, routes));
+        MOE_CUDA_CHECK(sampler, grow(sampler->router_rank_dev, b, routes));
+        MOE_CUDA_CHECK(sampler, grow(sampler->router_weight_dev, sampler->router_route_capacity, routes));
+    }
+    moe_router_options device_options = *options;
+    MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(sampler->router_logits_dev, router_logits, sizeof(float) * logit_count, cudaMemcpyHostToDevice, stream));
+    if (options->selection_bias != nullptr)
+    {
+        MOE_CUDA_CHECK(sampler, grow(sampler->router_bias_dev, sampler->router_bias_capacity, experts));
+        MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(sampler->router_bias_dev, options->selection_bias, sizeof(float) * experts, cudaMemcpyHostToDevice, stream));
+        device_options.selection_bias = sampler->router_bias_dev;
+    }
+    if (options->explicit_expert_ids != nullptr)
+    {
+        MOE_CUDA_CHECK(sampler, grow(sampler->router_explicit_dev, sampler->router_explicit_capacity, routes));
+        MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(sampler->router_explicit_dev, options->explicit_expert_ids, sizeof(uint32_t) * routes, cudaMemcpyHostToDevice, stream));
+        device_options.explicit_expert_ids = sampler->router_explicit_dev;
+    }
+    const int status = moe_router_dispatch(sampler, stream, sampler->router_logits_dev, token_count, &device_options, sampler->router_offsets_dev,
+                                           sampler->router_token_dev, sampler->router_rank_dev, sampler->router_weight_dev, sampler->router_status_dev);
+    if (status != MOE_STATUS_OK)
+        return status;
+    MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(plan_status, sampler->router_status_dev, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+    MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(expert_offsets, sampler->router_offsets_dev, sizeof(uint32_t) * (experts + 1), cudaMemcpyDeviceToHost, stream));
+    MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(route_token, sampler->router_token_dev, sizeof(uint32_t) * routes, cudaMemcpyDeviceToHost, stream));
+    MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(route_rank, sampler->router_rank_dev, sizeof(uint32_t) * routes, cudaMemcpyDeviceToHost, stream));
+    MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(route_weight, sampler->router_weight_dev, sizeof(float) * routes, cudaMemcpyDeviceToHost, stream));
+    MOE_CUDA_CHECK(sampler, cudaStreamSynchronize(stream));
+    if (*plan_status != 0)
+        return fail(sampler, moe_router_status_error_code(*plan_status), moe_router_status_message(*plan_status));
+    return MOE_STATUS_OK;
+}
+
+int moe_regroup_gather(moe_sampler* sampler, void* stream_handle, const float* hidden, uint32_t token_count, uint32_t columns,
+                       const uint32_t* route_token, uint32_t route_count, float* gathered)
+{
+    if (sampler == nullptr)
+        return MOE_STATUS_INVALID_ARGUMENT;
+    (void)token_count;
+    if (route_count == 0 || columns == 0)
+        return MOE_STATUS_OK;
+    if (hidden == nullptr || route_token == nullptr || gathered == nullptr)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "gather buffers must not be null");
+    DeviceGuard guard(sampler->device);
+    MOE_CUDA_CHECK(sampler, launch_regroup_gather(hidden, columns, route_token, route_count, gathered, static_cast<cudaStream_t>(stream_handle)));
+    return MOE_STATUS_OK;
+}
+
+} // extern "C"

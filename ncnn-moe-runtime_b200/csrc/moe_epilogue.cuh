@@ -1,0 +1,189 @@
+// The arithmetic tail of the sampler, executed by ONE warp over candidates that
+// are already in the reference rank order (logit descending, token id
+// ascending).  It reproduces src/engine/session.cpp:89-136 and :429-442 step by
+// step: every sum is a left-to-right fp32 accumulation in rank order, because
+// the reference's results (the Top-P cut in particular) depend on that order.
+// The expensive per-candidate work (exp, divisions) is done one candidate per
+// lane; the running sums are replayed lane by lane through shuffles so that all
+// 32 lanes hold the same accumulator and take the same branches.
+#pragma once
+
+#include "moe_common.cuh"
+
+namespace moe {
+
+struct RowOutcome
+{
+    int32_t status;
+    int32_t token;
+    float probability;
+    uint32_t flags;
+    // The draw ran past every candidate this warp was given although further
+    // (numerically dead) candidates exist in the row: the exact path must
+    // finish the row.
+    bool defer;
+};
+
+// records[0..count): sorted descending.  work[0..count): scratch floats.
+// tail_may_exist: the list is only the numerically live prefix of the row's
+// candidates (every omitted candidate has exp(x - peak) < 2^-26, so it cannot
+// change any of the four running sums, but it could still be the fall-back
+// "last candidate" of session.cpp:441-442).
+__device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, uint32_t count, float* work, float temperature,
+                                                       uint32_t top_k, float top_p, float min_p, float uniform, bool tail_may_exist)
+{
+    const int lane = threadIdx.x & 31;
+    RowOutcome out{MOE_ROW_OK, -1, 0.0f, 0u, false};
+    if (count == 0)
+    {
+        out.status = MOE_ROW_NO_FINITE_LOGIT;
+        return out;
+    }
+    const uint32_t head_key = record_key(records[0]);
+    if (head_key >= kKeyPosInf || head_key <= kKeyNegInf)
+    {
+        out.status = MOE_ROW_NO_FINITE_LOGIT; // session.cpp:84-85
+        return out;
+    }
+    uint32_t considered = count;
+    bool list_is_complete = !tail_may_exist;
+    if (top_k > 0 && top_k <= count)
+    {
+        considered = top_k; // session.cpp:86-87
+        list_is_complete = true;
+    }
+    // -inf logits sort last and are skipped (session.cpp:96-97)
+    uint32_t finite = 0;
+    for (uint32_t base = 0; base < considered; base += 32)
+    {
+        const uint32_t i = base + lane;
+        const bool is_finite = (i < considered) && (record_key(records[i]) > kKeyNegInf);
+        finite += __popc(__ballot_sync(kFullMask, is_finite));
+    }
+
+    // softmax numerators and their sequential sum (session.cpp:89-101)
+    const float peak = __fdiv_rn(key_to_float(head_key), temperature);
+    float total = 0.0f;
+    for (uint32_t base = 0; base < finite; base += 32)
+    {
+        const uint32_t i = base + lane;
+        float weight = 0.0f;
+        if (i < finite)
+        {
+            weight = exact_expf(scaled_offset(key_to_float(record_key(records[i])), temperature, peak));
+            work[i] = weight;
+        }
+        const uint32_t steps = min(32u, finite - base);
+        for (uint32_t j = 0; j < steps; ++j)
+            total = __fadd_rn(total, __shfl_sync(kFullMask, weight, j));
+    }
+    __syncwarp();
+    if (finite == 0 || !(total - total == 0.0f) || total <= 0.0f)
+    {
+        out.status = MOE_ROW_INVALID_DISTRIBUTION; // session.cpp:102-103
+        return out;
+    }
+
+    // probabilities, Min-P floor, Top-P prefix (session.cpp:104-128)
+    const float floor_probability = __fmul_rn(__fdiv_rn(work[0], total), min_p);
+    __syncwarp();
+    float running = 0.0f;
+    uint32_t kept = 0;
+    bool cut = false; // Min-P or Top-P closed the list: no omitted candidate can follow it
+    for (uint32_t base = 0; base < finite; base += 32)
+    {
+        const uint32_t i = base + lane;
+        float probability = 0.0f;
+        bool passes = false;
+        if (i < finite)
+        {
+            probability = __fdiv_rn(work[i], total);
+            work[i] = probability;
+            passes = (min_p > 0.0f) ? (probability >= floor_probability) : true;
+        }
+        const unsigned pass_mask = __ballot_sync(kFullMask, passes);
+        const uint32_t steps = (pass_mask == kFullMask) ? 32u : static_cast<uint32_t>(__ffs(~pass_mask) - 1);
+        bool reached = false;
+        for (uint32_t j = 0; j < steps; ++j)
+        {
+            running = __fadd_rn(running, __shfl_sync(kFullMask, probability, j));
+            ++kept;
+            if (running >= top_p)
+            {
+                reached = true;
+                break;
+            }
+        }
+        if (reached)
+        {
+            cut = true;
+            break;
+        }
+        if (steps < 32)
+        {
+            cut = cut || (base + steps < finite);
+            break;
+        }
+    }
+    __syncwarp();
+
+    // renormaliser (session.cpp:130-134)
+    float kept_total = 0.0f;
+    for (uint32_t base = 0; base < kept; base += 32)
+    {
+        const uint32_t i = base + lane;
+        const float probability = (i < kept) ? work[i] : 0.0f;
+        const uint32_t steps = min(32u, kept - base);
+        for (uint32_t j = 0; j < steps; ++j)
+            kept_total = __fadd_rn(kept_total, __shfl_sync(kFullMask, probability, j));
+    }
+
+    if (kept == 1)
+    {
+        out.token = static_cast<int32_t>(record_index(records[0])); // session.cpp:429-430: no uniform drawn
+        out.probability = 1.0f;
+        return out;
+    }
+    out.flags |= MOE_ROW_FLAG_USED_UNIFORM;
+
+    // inverse CDF (session.cpp:432-442)
+    running = 0.0f;
+    for (uint32_t base = 0; base < kept; base += 32)
+    {
+        const uint32_t i = base + lane;
+        const float probability = (i < kept) ? __fdiv_rn(work[i], kept_total) : 0.0f;
+        const uint32_t steps = min(32u, kept - base);
+        for (uint32_t j = 0; j < steps; ++j)
+        {
+            const float q = __shfl_sync(kFullMask, probability, j);
+            running = __fadd_rn(running, q);
+            if (uniform < running)
+            {
+                out.token = static_cast<int32_t>(record_index(records[base + j]));
+                out.probability = q;
+                return out;
+            }
+        }
+    }
+    if (!list_is_complete && !cut)
+    {
+        out.defer = true;
+        return out;
+    }
+    out.token = static_cast<int32_t>(record_index(records[kept - 1]));
+    out.probability = __fdiv_rn(work[kept - 1], kept_total);
+    return out;
+}
+
+// Linear search of the row's stop list (src/engine/session.cpp:60-63).
+__device__ __forceinline__ bool is_stop_token(const int32_t* stop_offsets, const int32_t* stop_tokens, uint32_t row, int32_t token)
+{
+    if (stop_offsets == nullptr || stop_tokens == nullptr)
+        return false;
+    for (int32_t i = stop_offsets[row]; i < stop_offsets[row + 1]; ++i)
+        if (stop_tokens[i] == token)
+            return true;
+    return false;
+}
+
+} // namespace moe

@@ -1,0 +1,78 @@
+// Host-side declarations shared by the translation units of the library.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/moe_b200_sampler.h"
+
+namespace moe {
+
+// Device workspace shared by the kernels of one handle.
+struct Workspace
+{
+    // rows the streaming kernel could not finish; consumed (and reset to 0) by
+    // the exact kernel of the same call
+    uint32_t* exact_count = nullptr;   // [1]
+    uint32_t* exact_done = nullptr;    // [1] CTAs of the exact kernel that have finished
+    uint32_t* exact_rows = nullptr;    // [max_rows]
+    // per-slot scratch of the exact kernel: (keys, index) pair 0 then pair 1,
+    // each array `max_vocab` rounded up to a multiple of 4 entries
+    uint32_t* sort_keys = nullptr;     // [slots][4][stride]
+    uint32_t slots = 0;
+    uint32_t max_rows = 0;
+    uint32_t max_vocab = 0;
+};
+
+struct SampleArgs
+{
+    const void* logits;
+    int dtype;
+    uint32_t rows;
+    uint32_t vocab;
+    size_t row_stride;
+    const moe_row_params* params; // device
+    uint64_t step_offset;
+    const int32_t* stop_offsets; // device or null
+    const int32_t* stop_tokens;  // device or null
+    int32_t* token_id;
+    float* probability;
+    uint32_t* row_flags;   // may be null
+    int32_t* row_status;   // may be null
+    int32_t* topk_index;   // may be null
+    uint32_t topk_stride;
+    // vocabulary-sharded local pass: write the slice's Top-K records instead of sampling
+    uint64_t* candidates_out; // may be null
+    uint32_t candidates_k;
+    uint32_t vocab_begin;
+};
+
+cudaError_t launch_sample_rows(const SampleArgs& args, const Workspace& ws, uint32_t splits, cudaStream_t stream);
+cudaError_t launch_sample_exact(const SampleArgs& args, const Workspace& ws, cudaStream_t stream);
+cudaError_t launch_merge_candidates(const uint64_t* gathered, uint32_t shards, uint32_t rows, uint32_t top_k, const moe_row_params* params,
+                                    uint64_t step_offset, int32_t* token_id, float* probability, uint32_t* row_flags, int32_t* row_status,
+                                    int32_t* topk_index, uint32_t topk_stride, cudaStream_t stream);
+
+struct RouterArgs
+{
+    const float* logits;
+    uint32_t token_count;
+    moe_router_options options; // pointers are device pointers
+    uint32_t* expert_offsets;
+    uint32_t* route_token;
+    uint32_t* route_rank;
+    float* route_weight;
+    int32_t* plan_status;
+    // scratch
+    uint32_t* selected_expert; // [token_count * top_k]
+    float* selected_weight;    // [token_count * top_k]
+};
+cudaError_t launch_router_dispatch_kernels(const RouterArgs& args, uint32_t* expert_counts, unsigned long long* error_word, cudaStream_t stream);
+cudaError_t launch_regroup_gather(const float* hidden, uint32_t columns, const uint32_t* route_token, uint32_t route_count, float* gathered,
+                                  cudaStream_t stream);
+
+uint32_t choose_splits(uint32_t rows, uint32_t vocab, int dtype, int sm_count);
+
+} // namespace moe

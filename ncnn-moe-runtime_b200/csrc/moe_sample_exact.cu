@@ -1,0 +1,332 @@
+// Exact full-vocabulary sampler for the rows the streaming kernel hands over:
+// rows without Top-K (or with top_k > MOE_SAMPLER_TOPK_FAST_MAX) whose
+// numerically live candidate set does not fit in shared memory.
+//
+// The reference's result for such a row depends on the complete rank order
+// (src/engine/session.cpp:80-82) because its softmax normaliser, Top-P
+// cumulative, renormaliser and inverse CDF are all left-to-right fp32 sums in
+// that order (:92-101,119-134,434-440).  One CTA therefore builds the order of
+// all finite logits of the row with a stable least-significant-digit radix
+// sort in a per-CTA global scratch slot (L2 resident), and one warp replays the
+// sums over it (moe_epilogue.cuh).
+//
+// CTAs take rows round-robin from the hand-over list; nobody waits on another
+// CTA.  The last CTA to finish clears the list for the next call.
+
+#include "moe_common.cuh"
+#include "moe_epilogue.cuh"
+#include "moe_internal.h"
+
+namespace moe {
+
+namespace {
+
+constexpr int kExactThreads = 1024;
+constexpr int kExactWarps = kExactThreads / 32;
+
+struct ExactShared
+{
+    uint32_t warp_hist[kExactWarps][256];
+    uint32_t digit_total[256];
+    uint32_t warp_count[kExactWarps];
+    uint32_t warp_or[kExactWarps];
+    uint32_t warp_and[kExactWarps];
+    uint32_t flag_pos_inf;
+    uint32_t total;
+};
+
+template<typename T>
+__device__ __forceinline__ float load_logit(const T* row, uint32_t index)
+{
+    return LogitTraits<T>::widen(row, index);
+}
+
+// Stable compaction of the finite logits of a row into (inverted key, index)
+// arrays, index ascending.  Returns the count; sets sh.flag_pos_inf when a
+// +inf logit was seen (the row is then an error, session.cpp:84-85).
+template<typename T>
+__device__ uint32_t compact_finite(const T* row, uint32_t vocab, uint32_t* keys, uint32_t* index, ExactShared& sh)
+{
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const uint32_t segment = ((vocab + kExactThreads - 1) / kExactThreads) * 32u; // per warp, multiple of 32
+    const uint32_t begin = min(vocab, warp * segment);
+    const uint32_t end = min(vocab, begin + segment);
+    if (tid == 0)
+        sh.flag_pos_inf = 0;
+    __syncthreads();
+    uint32_t mine = 0;
+    bool saw_pos_inf = false;
+    for (uint32_t base = begin; base < end; base += 32)
+    {
+        const uint32_t i = base + lane;
+        const float v = (i < end) ? load_logit(row, i) : __uint_as_float(0x7FC00000u);
+        saw_pos_inf |= (v == INFINITY);
+        mine += __popc(__ballot_sync(kFullMask, fabsf(v) < INFINITY));
+    }
+    if (__any_sync(kFullMask, saw_pos_inf) && lane == 0)
+        sh.flag_pos_inf = 1;
+    if (lane == 0)
+        sh.warp_count[warp] = mine;
+    __syncthreads();
+    if (warp == 0)
+    {
+        const uint32_t value = sh.warp_count[lane];
+        uint32_t inclusive = value;
+#pragma unroll
+        for (int offset = 1; offset < 32; offset <<= 1)
+        {
+            const uint32_t other = __shfl_up_sync(kFullMask, inclusive, offset);
+            if (lane >= offset)
+                inclusive += other;
+        }
+        sh.warp_count[lane] = inclusive - value;
+        if (lane == 31)
+            sh.total = inclusive;
+    }
+    __syncthreads();
+    uint32_t cursor = sh.warp_count[warp];
+    for (uint32_t base = begin; base < end; base += 32)
+    {
+        const uint32_t i = base + lane;
+        const float v = (i < end) ? load_logit(row, i) : __uint_as_float(0x7FC00000u);
+        const bool keep = fabsf(v) < INFINITY;
+        const unsigned voters = __ballot_sync(kFullMask, keep);
+        if (keep)
+        {
+            const uint32_t slot = cursor + __popc(voters & ((1u << lane) - 1u));
+            keys[slot] = ~ordered_key(v); // ascending sort of this = descending logits
+            index[slot] = i;
+        }
+        cursor += __popc(voters);
+    }
+    __syncthreads();
+    return sh.total;
+}
+
+// One stable counting-sort pass on an 8-bit digit.  Each warp owns a contiguous
+// segment of the input, so input order is preserved inside every digit.
+__device__ void radix_pass(const uint32_t* keys_in, const uint32_t* index_in, uint32_t* keys_out, uint32_t* index_out, uint32_t n, int shift,
+                           ExactShared& sh)
+{
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const uint32_t segment = ((n + kExactThreads - 1) / kExactThreads) * 32u;
+    const uint32_t begin = min(n, warp * segment);
+    const uint32_t end = min(n, begin + segment);
+
+    for (int d = lane; d < 256; d += 32)
+        sh.warp_hist[warp][d] = 0;
+    __syncwarp();
+    for (uint32_t base = begin; base < end; base += 32)
+    {
+        const uint32_t i = base + lane;
+        const bool valid = i < end;
+        const uint32_t digit = valid ? ((keys_in[i] >> shift) & 0xFFu) : 0xFFFFFFFFu;
+        const unsigned peers = __match_any_sync(kFullMask, digit);
+        if (valid && lane == (__ffs(peers) - 1))
+            sh.warp_hist[warp][digit] += __popc(peers);
+        __syncwarp();
+    }
+    __syncthreads();
+    // exclusive offsets: digit-major, then warp order
+    if (tid < 256)
+    {
+        uint32_t running = 0;
+        for (int w = 0; w < kExactWarps; ++w)
+        {
+            const uint32_t value = sh.warp_hist[w][tid];
+            sh.warp_hist[w][tid] = running;
+            running += value;
+        }
+        sh.digit_total[tid] = running;
+    }
+    __syncthreads();
+    if (warp == 0)
+    {
+        uint32_t local[8];
+        uint32_t sum = 0;
+#pragma unroll
+        for (int b = 0; b < 8; ++b)
+        {
+            local[b] = sh.digit_total[lane * 8 + b];
+            sum += local[b];
+        }
+        uint32_t inclusive = sum;
+#pragma unroll
+        for (int offset = 1; offset < 32; offset <<= 1)
+        {
+            const uint32_t other = __shfl_up_sync(kFullMask, inclusive, offset);
+            if (lane >= offset)
+                inclusive += other;
+        }
+        uint32_t running = inclusive - sum;
+#pragma unroll
+        for (int b = 0; b < 8; ++b)
+        {
+            sh.digit_total[lane * 8 + b] = running;
+            running += local[b];
+        }
+    }
+    __syncthreads();
+    if (tid < 256)
+    {
+        const uint32_t digit_base = sh.digit_total[tid];
+        for (int w = 0; w < kExactWarps; ++w)
+            sh.warp_hist[w][tid] += digit_base;
+    }
+    __syncthreads();
+    for (uint32_t base = begin; base < end; base += 32)
+    {
+        const uint32_t i = base + lane;
+        const bool valid = i < end;
+        const uint32_t key = valid ? keys_in[i] : 0u;
+        const uint32_t digit = valid ? ((key >> shift) & 0xFFu) : 0xFFFFFFFFu;
+        const unsigned peers = __match_any_sync(kFullMask, digit);
+        if (valid)
+        {
+            const uint32_t slot = sh.warp_hist[warp][digit] + __popc(peers & ((1u << lane) - 1u));
+            keys_out[slot] = key;
+            index_out[slot] = index_in[i];
+        }
+        __syncwarp();
+        if (valid && lane == (__ffs(peers) - 1))
+            sh.warp_hist[warp][digit] += __popc(peers);
+        __syncwarp();
+    }
+    __syncthreads();
+}
+
+template<typename T>
+__device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys, uint32_t* slot_index, uint32_t slot_stride, ExactShared& sh)
+{
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const moe_row_params p = a.params[row];
+    const T* row_pointer = static_cast<const T*>(a.logits) + static_cast<size_t>(row) * a.row_stride;
+
+    // pair q = (slot_keys + q*slot_stride, slot_index + q*slot_stride); the two
+    // arrays of a pair are adjacent so that a pair can also hold 64-bit records
+    uint32_t* keys[2] = {slot_keys, slot_keys + 2 * static_cast<size_t>(slot_stride)};
+    uint32_t* index[2] = {slot_keys + slot_stride, slot_keys + 3 * static_cast<size_t>(slot_stride)};
+    (void)slot_index;
+
+    const uint32_t n = compact_finite<T>(row_pointer, a.vocab, keys[0], index[0], sh);
+    const bool has_pos_inf = sh.flag_pos_inf != 0;
+
+    int source = 0;
+    if (n > 1 && !has_pos_inf)
+    {
+        // digits on which all keys agree need no pass (bf16 logits: the two low bytes)
+        uint32_t any_bits = 0;
+        uint32_t all_bits = 0xFFFFFFFFu;
+        for (uint32_t i = tid; i < n; i += kExactThreads)
+        {
+            const uint32_t key = keys[0][i];
+            any_bits |= key;
+            all_bits &= key;
+        }
+        any_bits = __reduce_or_sync(kFullMask, any_bits);
+        all_bits = __reduce_and_sync(kFullMask, all_bits);
+        if (lane == 0)
+        {
+            sh.warp_or[warp] = any_bits;
+            sh.warp_and[warp] = all_bits;
+        }
+        __syncthreads();
+        any_bits = 0;
+        all_bits = 0xFFFFFFFFu;
+        for (int w = 0; w < kExactWarps; ++w)
+        {
+            any_bits |= sh.warp_or[w];
+            all_bits &= sh.warp_and[w];
+        }
+        const uint32_t varying = any_bits ^ all_bits;
+        __syncthreads();
+        for (int shift = 0; shift < 32; shift += 8)
+        {
+            if (((varying >> shift) & 0xFFu) == 0)
+                continue;
+            radix_pass(keys[source], index[source], keys[1 - source], index[1 - source], n, shift, sh);
+            source = 1 - source;
+        }
+    }
+
+    // records of the sorted order go to the other pair, the floats of the
+    // epilogue to this pair's key array (free once the records are built)
+    uint64_t* records = reinterpret_cast<uint64_t*>(keys[1 - source]);
+    float* work = reinterpret_cast<float*>(keys[source]);
+    if (!has_pos_inf)
+    {
+        for (uint32_t i = tid; i < n; i += kExactThreads)
+            records[i] = make_record(~keys[source][i], index[source][i]);
+    }
+    __syncthreads();
+
+    if (warp == 0)
+    {
+        RowOutcome out{MOE_ROW_OK, -1, 0.0f, 0u, false};
+        if (has_pos_inf || n == 0)
+        {
+            out.status = MOE_ROW_NO_FINITE_LOGIT;
+        }
+        else
+        {
+            const float uniform = philox_uniform(p.seed, p.row_id, p.step + a.step_offset);
+            out = finish_row_warp(records, n, work, p.temperature, p.top_k, p.top_p, p.min_p, uniform, false);
+        }
+        if (lane == 0)
+        {
+            if (out.status == MOE_ROW_OK && is_stop_token(a.stop_offsets, a.stop_tokens, row, out.token))
+                out.flags |= MOE_ROW_FLAG_STOP_TOKEN;
+            a.token_id[row] = out.token;
+            a.probability[row] = out.probability;
+            if (a.row_flags != nullptr)
+                a.row_flags[row] = out.flags;
+            if (a.row_status != nullptr)
+                a.row_status[row] = out.status;
+        }
+    }
+    __syncthreads();
+}
+
+template<typename T>
+__global__ void __launch_bounds__(kExactThreads, 1) sample_exact_kernel(const SampleArgs a, Workspace ws)
+{
+    __shared__ ExactShared sh;
+    const uint32_t pending = *ws.exact_count;
+    const uint32_t slot_stride = (ws.max_vocab + 3u) & ~3u;
+    uint32_t* slot_keys = ws.sort_keys + static_cast<size_t>(blockIdx.x) * 4u * slot_stride;
+    for (uint32_t i = blockIdx.x; i < pending; i += gridDim.x)
+        exact_row<T>(a, ws.exact_rows[i], slot_keys, nullptr, slot_stride, sh);
+    __syncthreads();
+    if (threadIdx.x == 0)
+    {
+        __threadfence();
+        if (atomicAdd(ws.exact_done, 1u) == gridDim.x - 1)
+        {
+            *ws.exact_count = 0; // every CTA has read it: ready for the next call
+            *ws.exact_done = 0;
+            __threadfence();
+        }
+    }
+}
+
+} // namespace
+
+cudaError_t launch_sample_exact(const SampleArgs& args, const Workspace& ws, cudaStream_t stream)
+{
+    if (args.rows == 0 || ws.slots == 0)
+        return cudaSuccess;
+    const uint32_t grid = ws.slots < args.rows ? ws.slots : args.rows;
+    if (args.dtype == MOE_DTYPE_F32)
+        sample_exact_kernel<float><<<grid, kExactThreads, 0, stream>>>(args, ws);
+    else
+        sample_exact_kernel<__nv_bfloat16><<<grid, kExactThreads, 0, stream>>>(args, ws);
+    return cudaGetLastError();
+}
+
+} // namespace moe

@@ -1,0 +1,743 @@
+// Streaming sampler kernel: one pass over each logit row.
+//
+// A row is cut into `splits` contiguous slices, one CTA each; the CTAs of a row
+// form a thread-block cluster.  A CTA streams its slice with 128-bit loads and
+// keeps, in shared memory, only the records that can still matter:
+//   greedy rows      the best finite logit so far              (session.cpp:404-424)
+//   Top-K rows       the k best records so far                 (session.cpp:80-87)
+//   full-vocab rows  the records whose softmax numerator could be >= 2^-26
+//                    relative to the running maximum ("live" records)
+// A record passes a single float compare against a threshold held in a register;
+// the threshold is tightened by a shared-memory radix select (Top-K) or by
+// re-testing against the running maximum (live) whenever the buffer fills.
+// After the stream the slices are merged over distributed shared memory by the
+// cluster's first CTA, the survivors are sorted into the reference rank order
+// and one warp replays the reference's sequential softmax / Min-P / Top-P /
+// renormalise / inverse-CDF arithmetic on them (moe_epilogue.cuh).
+//
+// Rows whose live set does not fit on chip, and draws that fall through to a
+// numerically dead candidate, are appended to a list that the exact kernel
+// (moe_sample_exact.cu) finishes.
+
+#include <cooperative_groups.h>
+
+#include "moe_common.cuh"
+#include "moe_epilogue.cuh"
+#include "moe_internal.h"
+#include "moe_select.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace moe {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kCap = 4096;                // records a CTA can hold
+constexpr int kItems = kCap / kThreads;   // records per thread in block-wide passes
+constexpr int kGroupsPerTile = 4;         // 128-bit loads in flight per thread
+constexpr uint32_t kLiveFlush = 2048;     // live mode: re-test the buffer at this fill
+constexpr uint32_t kLiveAbort = 1536;     // live mode: more survivors than this -> exact kernel
+// A candidate whose (logit/T - peak) is below this has exp() < 2^-26 and is
+// absorbed by every running fp32 sum that starts at the head candidate.
+constexpr float kDeadOffset = -18.1f;
+
+enum Mode : int
+{
+    kGreedy = 0,
+    kTopK = 1,
+    kLive = 2
+};
+
+struct __align__(16) RowShared
+{
+    uint64_t rec[kCap];
+    float work[kCap];
+    SelectShared<kThreads> sel;
+    uint32_t count;
+    uint32_t maxkey;
+    uint32_t abort_flag;
+};
+
+struct Ctx
+{
+    RowShared& s;
+    Mode mode;
+    uint32_t k;
+    uint32_t flush_level;
+    float temperature;
+    float tau;
+    bool primed;
+    bool aborted;
+};
+
+__device__ __forceinline__ float live_threshold(uint32_t maxkey, float temperature)
+{
+    if (maxkey == 0)
+        return -INFINITY;
+    const float peak_logit = key_to_float(maxkey);
+    // Lower than every logit whose (logit/T - peak/T), evaluated in fp32 as
+    // the reference does, can reach kDeadOffset: 0.1*T of slack plus 2^-20 of
+    // the peak's magnitude covers the three roundings involved.
+    return __fsub_rn(__fsub_rn(peak_logit, __fmul_rn(18.2f, temperature)), __fmul_rn(9.5367431640625e-07f, fabsf(peak_logit)));
+}
+
+template<typename T>
+struct Unpack;
+
+template<>
+struct Unpack<float>
+{
+    static constexpr int kWidth = 4;
+    __device__ static __forceinline__ void values(const uint4& v, float (&x)[4])
+    {
+        x[0] = __uint_as_float(v.x);
+        x[1] = __uint_as_float(v.y);
+        x[2] = __uint_as_float(v.z);
+        x[3] = __uint_as_float(v.w);
+    }
+    __device__ static __forceinline__ float maximum(const uint4& v)
+    {
+        return fmaxf(fmaxf(__uint_as_float(v.x), __uint_as_float(v.y)), fmaxf(__uint_as_float(v.z), __uint_as_float(v.w)));
+    }
+    __device__ static __forceinline__ uint4 nan_vector()
+    {
+        return make_uint4(0x7FC00000u, 0x7FC00000u, 0x7FC00000u, 0x7FC00000u);
+    }
+};
+
+template<>
+struct Unpack<__nv_bfloat16>
+{
+    static constexpr int kWidth = 8;
+    __device__ static __forceinline__ void values(const uint4& v, float (&x)[8])
+    {
+        x[0] = __uint_as_float(v.x << 16);
+        x[1] = __uint_as_float(v.x & 0xFFFF0000u);
+        x[2] = __uint_as_float(v.y << 16);
+        x[3] = __uint_as_float(v.y & 0xFFFF0000u);
+        x[4] = __uint_as_float(v.z << 16);
+        x[5] = __uint_as_float(v.z & 0xFFFF0000u);
+        x[6] = __uint_as_float(v.w << 16);
+        x[7] = __uint_as_float(v.w & 0xFFFF0000u);
+    }
+    __device__ static __forceinline__ float maximum(const uint4& v)
+    {
+        // packed bf16 max ignores NaN operands exactly like fmaxf
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+        const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(&v.z);
+        const __nv_bfloat162 d = *reinterpret_cast<const __nv_bfloat162*>(&v.w);
+        const __nv_bfloat162 m = __hmax2(__hmax2(a, b), __hmax2(c, d));
+        const uint32_t bits = *reinterpret_cast<const uint32_t*>(&m);
+        return fmaxf(__uint_as_float(bits << 16), __uint_as_float(bits & 0xFFFF0000u));
+    }
+    __device__ static __forceinline__ uint4 nan_vector()
+    {
+        return make_uint4(0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u);
+    }
+};
+
+// Tests `kWidth` consecutive logits of every lane against the threshold and
+// appends the passing ones to the record buffer.  Called by whole warps.
+// Returns true when the buffer needs a flush (fill level reached, enough
+// records to establish a first threshold, or overflow).
+template<int kWidth>
+__device__ __forceinline__ bool push_values(Ctx& c, const float (&x)[kWidth], uint32_t first_index, bool retry, uint32_t& stored, int bit_base)
+{
+    RowShared& s = c.s;
+    const int lane = threadIdx.x & 31;
+    bool want_flush = false;
+#pragma unroll
+    for (int e = 0; e < kWidth; ++e)
+    {
+        const float v = x[e];
+        bool pass;
+        if (c.mode == kLive)
+        {
+            pass = v > c.tau;
+        }
+        else
+        {
+            pass = c.primed ? (retry ? (v >= c.tau) : (v > c.tau)) : (v >= -INFINITY);
+            if (c.mode == kGreedy)
+                pass = pass && (fabsf(v) < INFINITY);
+        }
+        pass = pass && (((stored >> (bit_base + e)) & 1u) == 0u);
+        const unsigned voters = __ballot_sync(kFullMask, pass);
+        if (voters == 0)
+            continue;
+        const int leader = __ffs(voters) - 1;
+        const uint32_t votes = __popc(voters);
+        const uint32_t key = pass ? ordered_key(v) : 0u;
+        uint32_t base = 0;
+        if (lane == leader)
+            base = atomicAdd(&s.count, votes);
+        base = __shfl_sync(kFullMask, base, leader);
+        const uint32_t slot = base + __popc(voters & ((1u << lane) - 1u));
+        if (pass && slot < kCap)
+        {
+            s.rec[slot] = make_record(key, first_index + e);
+            stored |= 1u << (bit_base + e);
+        }
+        if (c.mode == kLive)
+        {
+            const uint32_t best = __reduce_max_sync(kFullMask, key);
+            if (lane == leader)
+                atomicMax(&s.maxkey, best);
+        }
+        const uint32_t filled = base + votes;
+        if (filled >= c.flush_level || (!c.primed && filled >= c.k))
+            want_flush = true;
+    }
+    return want_flush;
+}
+
+// Tightens the buffer: Top-K keeps the k best records and sets the threshold
+// to the k-th logit; live mode drops records that fell out of the live window
+// of the (larger) running maximum.  Returns true when records had been dropped
+// for lack of space, i.e. the current tile must be offered again.
+__device__ __noinline__ bool flush_buffer(Ctx& c)
+{
+    RowShared& s = c.s;
+    const uint32_t raw = s.count;
+    const bool overflowed = raw > kCap;
+    uint32_t n = overflowed ? static_cast<uint32_t>(kCap) : raw;
+    __syncthreads();
+    if (c.mode == kLive)
+    {
+        const uint32_t maxkey = s.maxkey;
+        const float temperature = c.temperature;
+        const float peak = __fdiv_rn(key_to_float(maxkey), temperature);
+        n = block_compact<kThreads, kItems>(s.rec, n, s.sel, [=](uint64_t record) {
+            const float offset = scaled_offset(key_to_float(record_key(record)), temperature, peak);
+            return !(offset < kDeadOffset); // keeps NaN offsets: the epilogue reports them
+        });
+        c.tau = live_threshold(maxkey, temperature);
+        if (n > kLiveAbort)
+            c.aborted = true;
+    }
+    else if (n > c.k)
+    {
+        const uint64_t smallest = block_radix_select<kThreads, kItems>(s.rec, n, c.k, s.sel);
+        n = c.k;
+        c.tau = key_to_float(record_key(smallest));
+        c.primed = true;
+    }
+    else if (n == c.k)
+    {
+        const uint64_t smallest = block_min_record<kThreads>(s.rec, n, s.sel);
+        c.tau = key_to_float(record_key(smallest));
+        c.primed = true;
+    }
+    if (threadIdx.x == 0)
+        s.count = n;
+    __syncthreads();
+    return overflowed;
+}
+
+template<typename T, int kGroups>
+__device__ __forceinline__ bool emit_tile(Ctx& c, const uint4 (&v)[kGroups], uint32_t first_group, uint32_t head, bool retry, uint32_t& stored)
+{
+    using U = Unpack<T>;
+    bool want_flush = false;
+#pragma unroll
+    for (int g = 0; g < kGroups; ++g)
+    {
+        const float top = U::maximum(v[g]);
+        bool interesting;
+        if (c.mode == kLive)
+            interesting = top > c.tau;
+        else
+            interesting = c.primed ? (retry ? (top >= c.tau) : (top > c.tau)) : (top >= -INFINITY);
+        if (__any_sync(kFullMask, interesting))
+        {
+            float x[U::kWidth];
+            U::values(v[g], x);
+            const uint32_t first_index = head + ((first_group + g) * kThreads + threadIdx.x) * U::kWidth;
+            want_flush |= push_values<U::kWidth>(c, x, first_index, retry, stored, g * U::kWidth);
+        }
+    }
+    return want_flush;
+}
+
+// Offers one tile, then resolves fills and overflows until every record of
+// the tile has either been stored or beaten.
+template<typename T, int kGroups>
+__device__ __forceinline__ void run_tile(Ctx& c, const uint4 (&v)[kGroups], uint32_t first_group, uint32_t head)
+{
+    uint32_t stored = 0;
+    bool want = emit_tile<T, kGroups>(c, v, first_group, head, false, stored);
+    bool flush = __syncthreads_or(want) != 0;
+    while (flush)
+    {
+        const bool overflowed = flush_buffer(c);
+        if (!overflowed || c.aborted)
+            break;
+        want = emit_tile<T, kGroups>(c, v, first_group, head, true, stored);
+        flush = __syncthreads_or(want) != 0;
+    }
+    if (c.mode == kLive)
+        c.tau = fmaxf(c.tau, live_threshold(c.s.maxkey, c.temperature));
+}
+
+// Sorts the surviving records into rank order and finishes the row: writes the
+// Top-K index list, runs the sequential arithmetic on one warp, flags stop
+// tokens, or hands the row to the exact kernel.  Called by the whole block.
+__device__ __forceinline__ void finish_row_block(const SampleArgs& a, RowShared& s, Ctx& c, const moe_row_params& p, uint32_t row,
+                                                 uint32_t* exact_count, uint32_t* exact_rows)
+{
+    const int tid = threadIdx.x;
+    const bool candidates_only = a.candidates_out != nullptr;
+    if (c.aborted)
+    {
+        if (tid == 0)
+            exact_rows[atomicAdd(exact_count, 1u)] = row;
+        return;
+    }
+    const uint32_t n = s.count;
+    const uint32_t padded = next_pow2(n);
+    for (uint32_t i = n + tid; i < padded; i += kThreads)
+        s.rec[i] = 0ull;
+    __syncthreads();
+    block_sort_descending<kThreads>(s.rec, padded);
+
+    if (candidates_only)
+    {
+        for (uint32_t i = tid; i < a.candidates_k; i += kThreads)
+        {
+            uint64_t record = 0ull;
+            if (i < n)
+                record = make_record(record_key(s.rec[i]), record_index(s.rec[i]) + a.vocab_begin);
+            a.candidates_out[static_cast<size_t>(row) * a.candidates_k + i] = record;
+        }
+        return;
+    }
+
+    if (a.topk_index != nullptr)
+    {
+        const uint32_t listed = (c.mode == kTopK) ? min(n, c.k) : 0u;
+        for (uint32_t i = tid; i < a.topk_stride; i += kThreads)
+            a.topk_index[static_cast<size_t>(row) * a.topk_stride + i] = (i < listed) ? static_cast<int32_t>(record_index(s.rec[i])) : -1;
+    }
+
+    if (tid < 32)
+    {
+        RowOutcome out{MOE_ROW_OK, -1, 0.0f, 0u, false};
+        if (c.mode == kGreedy)
+        {
+            if (n == 0)
+            {
+                out.status = MOE_ROW_NO_FINITE_LOGIT;
+            }
+            else
+            {
+                out.token = static_cast<int32_t>(record_index(s.rec[0]));
+                out.probability = 1.0f;
+            }
+        }
+        else
+        {
+            const float uniform = philox_uniform(p.seed, p.row_id, p.step + a.step_offset);
+            out = finish_row_warp(s.rec, n, s.work, p.temperature, p.top_k, p.top_p, p.min_p, uniform, c.mode == kLive);
+        }
+        if (tid == 0)
+        {
+            if (out.defer)
+            {
+                exact_rows[atomicAdd(exact_count, 1u)] = row;
+            }
+            else
+            {
+                if (out.status == MOE_ROW_OK && is_stop_token(a.stop_offsets, a.stop_tokens, row, out.token))
+                    out.flags |= MOE_ROW_FLAG_STOP_TOKEN;
+                a.token_id[row] = out.token;
+                a.probability[row] = out.probability;
+                if (a.row_flags != nullptr)
+                    a.row_flags[row] = out.flags;
+                if (a.row_status != nullptr)
+                    a.row_status[row] = out.status;
+            }
+        }
+    }
+}
+
+template<typename T>
+__global__ void __launch_bounds__(kThreads, 4) sample_rows_kernel(const SampleArgs a, uint32_t* exact_count, uint32_t* exact_rows)
+{
+    using U = Unpack<T>;
+    extern __shared__ __align__(16) unsigned char shared_raw[];
+    RowShared& s = *reinterpret_cast<RowShared*>(shared_raw);
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t splits = cluster.num_blocks();
+    const uint32_t rank = cluster.block_rank();
+    const uint32_t row = blockIdx.x / splits;
+    const int tid = threadIdx.x;
+    const bool candidates_only = a.candidates_out != nullptr;
+
+    moe_row_params p;
+    if (candidates_only)
+    {
+        p.temperature = 1.0f;
+        p.top_k = a.candidates_k;
+        p.top_p = 1.0f;
+        p.min_p = 0.0f;
+        p.seed = p.row_id = p.step = 0;
+    }
+    else
+    {
+        p = a.params[row];
+    }
+    const int invalid = validate_row(p);
+    if (invalid != MOE_ROW_OK)
+    {
+        // every CTA of the cluster takes this branch, so nobody waits on a cluster barrier
+        if (rank == 0)
+        {
+            if (tid == 0)
+            {
+                a.token_id[row] = -1;
+                a.probability[row] = 0.0f;
+                if (a.row_flags != nullptr)
+                    a.row_flags[row] = 0;
+                if (a.row_status != nullptr)
+                    a.row_status[row] = invalid;
+            }
+            if (a.topk_index != nullptr)
+                for (uint32_t i = tid; i < a.topk_stride; i += kThreads)
+                    a.topk_index[static_cast<size_t>(row) * a.topk_stride + i] = -1;
+        }
+        return;
+    }
+
+    Ctx c{s, kLive, 0xFFFFFFFFu, kLiveFlush, p.temperature, -INFINITY, true, false};
+    if (p.temperature == 0.0f)
+    {
+        c.mode = kGreedy;
+        c.k = 1;
+    }
+    else if (p.top_k > 0 && p.top_k <= MOE_SAMPLER_TOPK_FAST_MAX)
+    {
+        c.mode = kTopK;
+        c.k = p.top_k;
+    }
+    if (c.mode != kLive)
+    {
+        c.primed = false;
+        const uint32_t level = max(2u * c.k, c.k + 512u);
+        c.flush_level = min(level, static_cast<uint32_t>(kCap - 1024));
+    }
+
+    if (tid == 0)
+    {
+        s.count = 0;
+        s.maxkey = 0;
+        s.abort_flag = 0;
+    }
+    __syncthreads();
+
+    // ---- the slice of this CTA -------------------------------------------------
+    const T* row_pointer = static_cast<const T*>(a.logits) + static_cast<size_t>(row) * a.row_stride;
+    const uint32_t vocab = a.vocab;
+    const uint32_t misaligned = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(row_pointer) & 15u);
+    uint32_t head = ((16u - misaligned) & 15u) / static_cast<uint32_t>(sizeof(T));
+    head = min(head, vocab);
+    const uint32_t vectors = (vocab - head) / U::kWidth;
+    const uint32_t tail_begin = head + vectors * U::kWidth;
+    const uint32_t groups = (vectors + kThreads - 1) / kThreads;
+    const uint32_t group_begin = static_cast<uint32_t>(static_cast<uint64_t>(rank) * groups / splits);
+    const uint32_t group_end = static_cast<uint32_t>(static_cast<uint64_t>(rank + 1) * groups / splits);
+    const uint4* vector_base = reinterpret_cast<const uint4*>(row_pointer + head);
+
+    // unaligned leading logits (lowest indices: first, by the first CTA)
+    if (rank == 0 && head > 0)
+    {
+        float x[1] = {tid < static_cast<int>(head) ? LogitTraits<T>::widen(row_pointer, tid) : __uint_as_float(0x7FC00000u)};
+        uint32_t stored = 0;
+        const bool want = push_values<1>(c, x, static_cast<uint32_t>(tid), false, stored, 0);
+        if (__syncthreads_or(want))
+            flush_buffer(c);
+    }
+
+    uint32_t g = group_begin;
+    // a short first tile establishes the threshold cheaply
+    if (g < group_end && !c.aborted)
+    {
+        uint4 v[1];
+        const uint32_t vi = g * kThreads + tid;
+        v[0] = (vi < vectors) ? load_stream_16(vector_base + vi) : U::nan_vector();
+        run_tile<T, 1>(c, v, g, head);
+        g += 1;
+    }
+    // full tiles, next tile's loads in flight while this one is filtered
+    const uint32_t full_groups = vectors / kThreads; // groups with all kThreads vectors present
+    const uint32_t full_end = min(group_end, full_groups);
+    if (g + kGroupsPerTile <= full_end && !c.aborted)
+    {
+        uint4 current[kGroupsPerTile];
+#pragma unroll
+        for (int j = 0; j < kGroupsPerTile; ++j)
+            current[j] = load_stream_16(vector_base + (g + j) * kThreads + tid);
+        while (true)
+        {
+            const bool has_next = (g + 2 * kGroupsPerTile <= full_end);
+            uint4 next[kGroupsPerTile];
+            if (has_next)
+            {
+#pragma unroll
+                for (int j = 0; j < kGroupsPerTile; ++j)
+                    next[j] = load_stream_16(vector_base + (g + kGroupsPerTile + j) * kThreads + tid);
+            }
+            run_tile<T, kGroupsPerTile>(c, current, g, head);
+            g += kGroupsPerTile;
+            if (!has_next || c.aborted)
+                break;
+#pragma unroll
+            for (int j = 0; j < kGroupsPerTile; ++j)
+                current[j] = next[j];
+        }
+    }
+    // leftover groups (fewer than a tile, or the ragged last group)
+    while (g < group_end && !c.aborted)
+    {
+        uint4 v[1];
+        const uint32_t vi = g * kThreads + tid;
+        v[0] = (vi < vectors) ? load_stream_16(vector_base + vi) : U::nan_vector();
+        run_tile<T, 1>(c, v, g, head);
+        g += 1;
+    }
+    // unaligned trailing logits (highest indices: last, by the last CTA)
+    if (rank == splits - 1 && tail_begin < vocab && !c.aborted)
+    {
+        const uint32_t index = tail_begin + tid;
+        float x[1] = {index < vocab ? LogitTraits<T>::widen(row_pointer, index) : __uint_as_float(0x7FC00000u)};
+        uint32_t stored = 0;
+        const bool want = push_values<1>(c, x, index, false, stored, 0);
+        if (__syncthreads_or(want))
+            flush_buffer(c);
+    }
+    __syncthreads();
+    if (!c.aborted)
+        flush_buffer(c); // exact k best / exact live set of this slice
+    if (tid == 0)
+        s.abort_flag = c.aborted ? 1u : 0u;
+
+    // ---- merge the slices of the row over distributed shared memory ---------------
+    if (splits > 1)
+    {
+        cluster.sync();
+        if (rank == 0)
+        {
+            for (uint32_t peer = 1; peer < splits; ++peer)
+            {
+                const RowShared* remote = cluster.map_shared_rank(&s, peer);
+                const uint32_t remote_count = remote->count;
+                if (remote->abort_flag != 0)
+                    c.aborted = true;
+                if (c.aborted)
+                    continue;
+                if (s.count + remote_count > kCap)
+                {
+                    flush_buffer(c);
+                    if (s.count + remote_count > kCap)
+                    {
+                        c.aborted = true;
+                        continue;
+                    }
+                }
+                const uint32_t local_count = s.count;
+                for (uint32_t i = tid; i < remote_count; i += kThreads)
+                    s.rec[local_count + i] = remote->rec[i];
+                const uint32_t remote_max = remote->maxkey;
+                __syncthreads();
+                if (tid == 0)
+                {
+                    s.count = local_count + remote_count;
+                    s.maxkey = max(s.maxkey, remote_max);
+                }
+                __syncthreads();
+            }
+            if (!c.aborted)
+                flush_buffer(c);
+        }
+        cluster.sync(); // peers leave only after their shared memory has been read
+        if (rank != 0)
+            return;
+    }
+
+    finish_row_block(a, s, c, p, row, exact_count, exact_rows);
+}
+
+// Vocabulary-sharded sampling, second step: after the caller's all-gather each
+// row has shards * top_k records (one rank-ordered list per GPU, global token
+// ids).  The k best of their union are the row's global Top-K
+// (session.cpp:80-87); the reference normalises over exactly those, so no
+// partial softmax sums cross GPUs.  One CTA per row.
+__global__ void __launch_bounds__(kThreads, 4) merge_candidates_kernel(const uint64_t* gathered, uint32_t shards, uint32_t rows, uint32_t top_k,
+                                                                        const SampleArgs a)
+{
+    extern __shared__ __align__(16) unsigned char shared_raw[];
+    RowShared& s = *reinterpret_cast<RowShared*>(shared_raw);
+    const uint32_t row = blockIdx.x;
+    const int tid = threadIdx.x;
+    const moe_row_params p = a.params[row];
+    int invalid = validate_row(p);
+    if (invalid == MOE_ROW_OK && p.temperature != 0.0f && p.top_k != top_k)
+        invalid = MOE_ROW_WORKSPACE_EXHAUSTED; // the gathered lists were built for another k
+    if (invalid != MOE_ROW_OK)
+    {
+        if (tid == 0)
+        {
+            a.token_id[row] = -1;
+            a.probability[row] = 0.0f;
+            if (a.row_flags != nullptr)
+                a.row_flags[row] = 0;
+            if (a.row_status != nullptr)
+                a.row_status[row] = invalid;
+        }
+        if (a.topk_index != nullptr)
+            for (uint32_t i = tid; i < a.topk_stride; i += kThreads)
+                a.topk_index[static_cast<size_t>(row) * a.topk_stride + i] = -1;
+        return;
+    }
+    Ctx c{s, kTopK, top_k, 0xFFFFFFFFu, p.temperature, -INFINITY, false, false};
+    if (tid == 0)
+    {
+        s.count = 0;
+        s.maxkey = 0;
+        s.abort_flag = 0;
+    }
+    __syncthreads();
+    for (uint32_t shard = 0; shard < shards; ++shard)
+    {
+        if (s.count + top_k > kCap)
+            flush_buffer(c);
+        const uint32_t local_count = s.count;
+        const uint64_t* list = gathered + (static_cast<size_t>(shard) * rows + row) * top_k;
+        // a shard's list is dense from the front; empty slots hold 0
+        uint32_t mine = 0;
+        for (uint32_t i = tid; i < top_k; i += kThreads)
+        {
+            const uint64_t record = list[i];
+            if (record != 0ull)
+            {
+                s.rec[local_count + i] = record;
+                ++mine;
+            }
+        }
+        // number of non-empty records of this shard (block reduction through the selector's counter)
+        if (tid == 0)
+            s.sel.out_count = 0;
+        __syncthreads();
+        mine = __reduce_add_sync(kFullMask, mine);
+        if ((tid & 31) == 0 && mine != 0)
+            atomicAdd(&s.sel.out_count, mine);
+        __syncthreads();
+        if (tid == 0)
+            s.count = local_count + s.sel.out_count;
+        __syncthreads();
+    }
+    flush_buffer(c);
+    if (p.temperature == 0.0f)
+    {
+        // greedy over the merged candidates: best finite record (session.cpp:404-424)
+        const uint32_t n = s.count;
+        const uint32_t kept = block_compact<kThreads, kItems>(s.rec, n, s.sel, [](uint64_t record) {
+            const uint32_t key = record_key(record);
+            return key > kKeyNegInf && key < kKeyPosInf;
+        });
+        if (tid == 0)
+            s.count = kept;
+        __syncthreads();
+        c.mode = kGreedy;
+        c.k = 1;
+        flush_buffer(c);
+    }
+    finish_row_block(a, s, c, p, row, nullptr, nullptr);
+}
+
+template<typename T>
+cudaError_t launch_typed(const SampleArgs& args, const Workspace& ws, uint32_t splits, cudaStream_t stream)
+{
+    static bool configured = false; // per type; the attribute is per device function
+    const size_t shared_bytes = sizeof(RowShared);
+    if (!configured)
+    {
+        cudaError_t status = cudaFuncSetAttribute(sample_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared_bytes));
+        if (status != cudaSuccess)
+            return status;
+        configured = true;
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(args.rows * splits, 1, 1);
+    config.blockDim = dim3(kThreads, 1, 1);
+    config.dynamicSmemBytes = shared_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = splits;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, sample_rows_kernel<T>, args, ws.exact_count, ws.exact_rows);
+}
+
+} // namespace
+
+cudaError_t launch_sample_rows(const SampleArgs& args, const Workspace& ws, uint32_t splits, cudaStream_t stream)
+{
+    if (args.rows == 0)
+        return cudaSuccess;
+    if (args.dtype == MOE_DTYPE_F32)
+        return launch_typed<float>(args, ws, splits, stream);
+    return launch_typed<__nv_bfloat16>(args, ws, splits, stream);
+}
+
+cudaError_t launch_merge_candidates(const uint64_t* gathered, uint32_t shards, uint32_t rows, uint32_t top_k, const moe_row_params* params,
+                                    uint64_t step_offset, int32_t* token_id, float* probability, uint32_t* row_flags, int32_t* row_status,
+                                    int32_t* topk_index, uint32_t topk_stride, cudaStream_t stream)
+{
+    if (rows == 0)
+        return cudaSuccess;
+    static bool configured = false;
+    const size_t shared_bytes = sizeof(RowShared);
+    if (!configured)
+    {
+        cudaError_t status = cudaFuncSetAttribute(merge_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared_bytes));
+        if (status != cudaSuccess)
+            return status;
+        configured = true;
+    }
+    SampleArgs a = {};
+    a.rows = rows;
+    a.params = params;
+    a.step_offset = step_offset;
+    a.token_id = token_id;
+    a.probability = probability;
+    a.row_flags = row_flags;
+    a.row_status = row_status;
+    a.topk_index = topk_index;
+    a.topk_stride = topk_stride;
+    merge_candidates_kernel<<<rows, kThreads, shared_bytes, stream>>>(gathered, shards, rows, top_k, a);
+    return cudaGetLastError();
+}
+
+uint32_t choose_splits(uint32_t rows, uint32_t vocab, int dtype, int sm_count)
+{
+    const uint64_t row_bytes = static_cast<uint64_t>(vocab) * (dtype == MOE_DTYPE_F32 ? 4u : 2u);
+    const uint64_t by_size = row_bytes / (64u * 1024u);          // at least 64 KiB per slice
+    const uint64_t resident = static_cast<uint64_t>(sm_count) * 4u; // CTAs the GPU holds at once
+    const uint64_t wanted = (2u * resident + rows - 1) / (rows ? rows : 1u);
+    uint64_t limit = 8; // portable cluster size
+    if (by_size < limit)
+        limit = by_size;
+    if (wanted < limit)
+        limit = wanted;
+    uint32_t splits = 1;
+    while (splits * 2u <= limit)
+        splits *= 2u;
+    return splits;
+}
+
+} // namespace moe

@@ -1,0 +1,168 @@
+"""GPU parity of the batched sampler against the CPU oracle, through the C ABI.
+
+Bar: token ids, Top-K index sets, row status and RNG consumption bit-exact;
+probabilities within 1e-5 relative of the reference arithmetic and bit-exact
+against the oracle port run with the device's exp rounding.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def test_reference_unit_vectors(pkg, parity):
+    # tests/test_runtime.cpp:4333-4362 of the reference
+    cases = [
+        (np.array([[1, 2, 3]], dtype=np.float32), dict(temperature=0.0), 2, 0),
+        (np.array([[3, np.nan, 3]], dtype=np.float32), dict(temperature=0.0), 0, 0),
+        (np.array([[np.nan, np.inf]], dtype=np.float32), dict(temperature=0.0), -1, 5),
+        (np.array([[1, 2, 3]], dtype=np.float32), dict(top_k=1), 2, 0),
+        (np.array([[1, 2, 3]], dtype=np.float32), dict(top_p=0.0), -1, 3),
+    ]
+    for logits, options, token, status in cases:
+        params = pkg.make_row_params(1, **options)
+        out = parity.run(logits, params)
+        assert out["token"][0] == token and out["status"][0] == status
+        if status == 0:
+            assert out["probability"][0] == 1.0
+
+
+def test_config1_single_row(pkg, workloads, parity):
+    logits, params = workloads.config1_row(pkg.ROW_PARAMS_DTYPE, rows=1)
+    parity.check(logits, params, topk_stride=50)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_headline_shape_small_batch(pkg, workloads, parity, dtype):
+    logits, params = workloads.config1_row(pkg.ROW_PARAMS_DTYPE, rows=32, dtype=dtype, seed=11)
+    parity.check(logits, params, topk_stride=50)
+
+
+def test_config2_greedy_and_temperature(pkg, workloads, parity):
+    logits, params = workloads.config2_greedy_temperature(pkg.ROW_PARAMS_DTYPE, rows=24)
+    parity.check(logits, params)
+
+
+def test_config3_mixed_parameters(pkg, workloads, parity):
+    logits, params = workloads.config3_mixed(pkg.ROW_PARAMS_DTYPE, rows=48)
+    parity.check(logits, params, topk_stride=100)
+
+
+def test_config4_heavy_tail(pkg, workloads, parity):
+    logits, params = workloads.config4_heavy_tail(pkg.ROW_PARAMS_DTYPE, rows=64)
+    parity.check(logits, params)
+
+
+def test_config5a_large_vocab_single_gpu(pkg, workloads, parity):
+    logits, params = workloads.config5a_large_vocab(pkg.ROW_PARAMS_DTYPE, rows=4)
+    parity.check(logits, params, topk_stride=64)
+
+
+@pytest.mark.parametrize("vocab", [1, 2, 3, 7, 33, 255, 256, 257, 1023, 1025, 4099, 8191])
+def test_ragged_small_vocabularies(pkg, parity, vocab):
+    rng = np.random.default_rng(vocab)
+    rows = 16
+    logits = (3 * rng.standard_normal((rows, vocab))).astype(np.float32)
+    logits[rng.random((rows, vocab)) < 0.2] = logits[0, 0]      # many exact duplicates
+    params = pkg.make_row_params(rows, temperature=rng.uniform(0.3, 1.5, rows).astype(np.float32),
+                                 top_k=rng.choice([0, 1, 2, 5, 50, 2000], rows).astype(np.uint32),
+                                 top_p=rng.uniform(0.5, 1.0, rows).astype(np.float32),
+                                 min_p=rng.choice([0, 0.05], rows).astype(np.float32), seed=vocab)
+    params["temperature"][::5] = 0.0
+    parity.check(logits, params, topk_stride=64)
+    parity.check(logits, params, topk_stride=64, host=True)
+
+
+def test_unaligned_rows_and_bf16_tail(pkg, parity, torch_cuda):
+    torch = torch_cuda
+    rng = np.random.default_rng(5)
+    rows, vocab, stride = 6, 5003, 5009       # odd stride: every row has a different 16-byte phase
+    block = (3 * rng.standard_normal((rows, stride))).astype(np.float32)
+    params = pkg.make_row_params(rows, temperature=0.8, top_k=[0, 10, 40, 0, 1, 300], top_p=0.9, seed=5)
+    for dtype in ("f32", "bf16"):
+        if dtype == "bf16":
+            from_bits = __import__("ncnn_moe_runtime_b200.workloads", fromlist=["x"]).to_bf16_bits(block)
+            device = torch.from_numpy(from_bits.view(np.int16)).cuda().view(torch.bfloat16)
+            logical = from_bits[:, :vocab].copy()
+        else:
+            device = torch.from_numpy(block).cuda()
+            logical = block[:, :vocab].copy()
+        out = parity.sampler.sample_batch(device, params, vocab=vocab, topk_stride=16)
+        torch.cuda.synchronize()
+        uniforms = parity.uniforms(params)
+        want = parity.checker.sample_batch(logical, params["temperature"], params["top_k"], params["top_p"], params["min_p"], uniforms)
+        np.testing.assert_array_equal(out["token"].cpu().numpy(), want["token"])
+
+
+def test_non_finite_logits(pkg, parity):
+    rng = np.random.default_rng(9)
+    vocab = 3000
+    base = (2 * rng.standard_normal(vocab)).astype(np.float32)
+    rows = []
+    a = base.copy(); a[rng.integers(0, vocab, 500)] = -np.inf; rows.append(a)            # masked logits are legal
+    b = np.full(vocab, -np.inf, dtype=np.float32); rows.append(b)                          # nothing finite
+    c = base.copy(); c[17] = np.inf; rows.append(c)                                        # +inf at the head is an error
+    d = np.full(vocab, -np.inf, dtype=np.float32); d[5] = 1.0; rows.append(d)             # a single finite logit
+    logits = np.stack(rows)
+    for options in (dict(temperature=0.0), dict(top_k=40, top_p=0.9), dict(top_p=0.95), dict(top_k=5000)):
+        params = pkg.make_row_params(len(rows), seed=3, **options)
+        parity.check(logits, params, topk_stride=40)
+
+
+def test_invalid_parameters_per_row(pkg, parity):
+    logits = np.tile(np.arange(100, dtype=np.float32), (6, 1))
+    params = pkg.make_row_params(6, temperature=[1, -1, np.nan, 1, 1, 1], top_p=[1, 1, 1, 0, 1.5, 1], min_p=[0, 0, 0, 0, 0, -0.1])
+    out = parity.run(logits, params)
+    assert out["status"].tolist() == [0, 2, 2, 3, 3, 4]
+    assert [pkg.row_status_message(s) for s in out["status"][1:]] == [
+        "temperature must be finite and non-negative", "temperature must be finite and non-negative",
+        "top_p must be in the range (0, 1]", "top_p must be in the range (0, 1]", "min_p must be in the range [0, 1]"]
+
+
+def test_extreme_temperatures(pkg, parity):
+    rng = np.random.default_rng(21)
+    logits = (3 * rng.standard_normal((8, 4096))).astype(np.float32)
+    params = pkg.make_row_params(8, temperature=[1e-30, 1e-6, 1e-3, 50.0, 1e6, 1e30, 3e38, 0.01], top_k=[0, 0, 10, 0, 20, 0, 0, 0], top_p=0.9, seed=4)
+    parity.check(logits, params)
+
+
+def test_top_p_one_still_truncates(pkg, parity):
+    # the cumulative reaches 1.0f before the last candidate; ids beyond are unreachable (session.cpp:119-128)
+    rng = np.random.default_rng(33)
+    logits = (3 * rng.standard_normal((4, 60000))).astype(np.float32)
+    params = pkg.make_row_params(4, temperature=[1.0, 0.7, 1.3, 1.0], top_p=1.0, seed=8)
+    parity.check(logits, params)
+
+
+def test_stop_tokens_and_resident_parameters(pkg, parity, torch_cuda):
+    torch = torch_cuda
+    rng = np.random.default_rng(2)
+    rows, vocab = 8, 3001
+    logits = (3 * rng.standard_normal((rows, vocab))).astype(np.float32)
+    params = pkg.make_row_params(rows, temperature=0.0)
+    greedy = logits.argmax(axis=1)
+    stops = [[int(greedy[r]), 7] if r % 2 == 0 else [int((greedy[r] + 1) % vocab)] for r in range(rows)]
+    out = parity.run(logits, params, stop_lists=stops)
+    flagged = (out["flags"] & pkg.ROW_FLAG_STOP_TOKEN) != 0
+    assert flagged.tolist() == [r % 2 == 0 for r in range(rows)]
+    # resident parameters + step offset: same uniforms as explicit steps
+    params = pkg.make_row_params(rows, temperature=1.0, top_k=50, seed=77)
+    device = torch.from_numpy(logits).cuda()
+    parity.sampler.sample_batch(device, params)
+    for step in (1, 2, 5):
+        out = parity.sampler.sample_batch(device, None, step_offset=step)
+        torch.cuda.synchronize()
+        explicit = params.copy(); explicit["step"] = step
+        want = parity.checker.sample_batch(logits, explicit["temperature"], explicit["top_k"], explicit["top_p"], explicit["min_p"], parity.uniforms(explicit))
+        np.testing.assert_array_equal(out["token"].cpu().numpy(), want["token"])
+
+
+def test_adversarial_orderings(pkg, parity):
+    vocab = 70000
+    ascending = np.arange(vocab, dtype=np.float32) * 1e-3
+    constant = np.zeros(vocab, dtype=np.float32)
+    plateau = np.concatenate([np.full(vocab // 2, 5.0, dtype=np.float32), np.arange(vocab - vocab // 2, dtype=np.float32) * 1e-4 + 5.0])
+    logits = np.stack([ascending, ascending[::-1].copy(), constant, plateau])
+    for options in (dict(top_k=50, top_p=0.9), dict(top_k=1024), dict(temperature=0.0), dict(top_p=0.9)):
+        params = pkg.make_row_params(4, seed=6, **options)
+        parity.check(logits, params, topk_stride=64)
