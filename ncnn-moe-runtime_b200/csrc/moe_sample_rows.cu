@@ -57,6 +57,7 @@ struct __align__(16) RowShared
     uint32_t count;
     uint32_t maxkey;
     uint32_t abort_flag;
+    uint32_t overflow;
 };
 
 struct Ctx
@@ -281,6 +282,248 @@ __device__ __forceinline__ void run_tile(Ctx& c, const uint4 (&v)[kGroups], uint
         c.tau = fmaxf(c.tau, live_threshold(c.s.maxkey, c.temperature));
 }
 
+// The careful streaming loop: a block barrier after every tile, exact radix
+// selects whenever the buffer fills, and a retry of the tile when records had to
+// be dropped.  It makes no assumption about the order of the logits (ascending
+// rows, constant rows and plateaus all work) and is what a slice falls back to
+// when the barrier-free loop below could not finish it.
+template<typename T>
+__device__ __noinline__ void stream_slice_safe(Ctx& c, const T* row_pointer, uint32_t vocab, uint32_t head, uint32_t vectors, uint32_t tail_begin,
+                                               uint32_t group_begin, uint32_t group_end, uint32_t rank, uint32_t splits)
+{
+    using U = Unpack<T>;
+    RowShared& s = c.s;
+    const int tid = threadIdx.x;
+    const uint4* vector_base = reinterpret_cast<const uint4*>(row_pointer + head);
+    // unaligned leading logits (lowest indices: first, by the first CTA)
+    if (rank == 0 && head > 0)
+    {
+        float x[1] = {tid < static_cast<int>(head) ? LogitTraits<T>::widen(row_pointer, tid) : __uint_as_float(0x7FC00000u)};
+        uint32_t stored = 0;
+        const bool want = push_values<1>(c, x, static_cast<uint32_t>(tid), false, stored, 0);
+        if (__syncthreads_or(want))
+            flush_buffer(c);
+    }
+
+    uint32_t g = group_begin;
+    // a short first tile establishes the threshold cheaply
+    if (g < group_end && !c.aborted)
+    {
+        uint4 v[1];
+        const uint32_t vi = g * kThreads + tid;
+        v[0] = (vi < vectors) ? load_stream_16(vector_base + vi) : U::nan_vector();
+        run_tile<T, 1>(c, v, g, head);
+        g += 1;
+    }
+    // full tiles, next tile's loads in flight while this one is filtered
+    const uint32_t full_groups = vectors / kThreads; // groups with all kThreads vectors present
+    const uint32_t full_end = min(group_end, full_groups);
+    if (g + kGroupsPerTile <= full_end && !c.aborted)
+    {
+        uint4 current[kGroupsPerTile];
+#pragma unroll
+        for (int j = 0; j < kGroupsPerTile; ++j)
+            current[j] = load_stream_16(vector_base + (g + j) * kThreads + tid);
+        while (true)
+        {
+            const bool has_next = (g + 2 * kGroupsPerTile <= full_end);
+            uint4 next[kGroupsPerTile];
+            if (has_next)
+            {
+#pragma unroll
+                for (int j = 0; j < kGroupsPerTile; ++j)
+                    next[j] = load_stream_16(vector_base + (g + kGroupsPerTile + j) * kThreads + tid);
+            }
+            run_tile<T, kGroupsPerTile>(c, current, g, head);
+            g += kGroupsPerTile;
+            if (!has_next || c.aborted)
+                break;
+#pragma unroll
+            for (int j = 0; j < kGroupsPerTile; ++j)
+                current[j] = next[j];
+        }
+    }
+    // leftover groups (fewer than a tile, or the ragged last group)
+    while (g < group_end && !c.aborted)
+    {
+        uint4 v[1];
+        const uint32_t vi = g * kThreads + tid;
+        v[0] = (vi < vectors) ? load_stream_16(vector_base + vi) : U::nan_vector();
+        run_tile<T, 1>(c, v, g, head);
+        g += 1;
+    }
+    // unaligned trailing logits (highest indices: last, by the last CTA)
+    if (rank == splits - 1 && tail_begin < vocab && !c.aborted)
+    {
+        const uint32_t index = tail_begin + tid;
+        float x[1] = {index < vocab ? LogitTraits<T>::widen(row_pointer, index) : __uint_as_float(0x7FC00000u)};
+        uint32_t stored = 0;
+        const bool want = push_values<1>(c, x, index, false, stored, 0);
+        if (__syncthreads_or(want))
+            flush_buffer(c);
+    }
+    __syncthreads();
+    if (!c.aborted)
+        flush_buffer(c); // exact k best / exact live set of this slice
+}
+
+// Appends the logits of one lane that reach the threshold.  Runs divergently:
+// only lanes whose vector maximum reached the threshold get here.
+template<int kWidth>
+__device__ __forceinline__ void offer_values(RowShared& s, Mode mode, float tau, const float (&x)[kWidth], uint32_t first_index)
+{
+#pragma unroll
+    for (int e = 0; e < kWidth; ++e)
+    {
+        const float v = x[e];
+        bool pass = v >= tau; // false for NaN
+        if (mode == kGreedy)
+            pass = pass && (fabsf(v) < INFINITY);
+        if (pass)
+        {
+            const uint32_t key = ordered_key(v);
+            const uint32_t slot = atomicAdd(&s.count, 1u);
+            if (slot < kCap)
+                s.rec[slot] = make_record(key, first_index + e);
+            else
+                s.overflow = 1u;
+            if (mode == kLive)
+                atomicMax(&s.maxkey, key);
+        }
+    }
+}
+
+// The barrier-free streaming loop.  The first tile of the slice estimates a
+// threshold from the per-thread maxima (their r-th largest, r chosen so that a
+// few times k logits of the whole slice are expected above it; live mode uses
+// the tile maximum), then every other tile is filtered against that threshold
+// with one packed max and one compare per 128-bit load and no block barrier.
+// All logits >= threshold end up in the buffer, so if at least k were found the
+// slice's k best are among them regardless of the order of the logits.  Returns
+// false (buffer reset) when fewer than k were found or the buffer overflowed;
+// the caller then runs the careful loop.
+template<typename T>
+__device__ __forceinline__ bool stream_slice_fast(RowShared& s, Mode mode, uint32_t k, float temperature, const T* row_pointer, uint32_t vocab,
+                                                  uint32_t head, uint32_t vectors, uint32_t tail_begin, uint32_t group_begin, uint32_t group_end,
+                                                  bool first_rank, bool last_rank)
+{
+    using U = Unpack<T>;
+    const int tid = threadIdx.x;
+    const uint4* vector_base = reinterpret_cast<const uint4*>(row_pointer + head);
+    const uint32_t full_groups = vectors / kThreads;
+    const uint32_t full_end = min(group_end, full_groups);
+    if (group_begin + kGroupsPerTile > full_end)
+        return false; // not even one full tile
+
+    // rank r of the thread maximum that becomes the threshold
+    uint32_t r = 1;
+    if (mode == kTopK)
+    {
+        const float slice_elements = static_cast<float>(group_end - group_begin) * (kThreads * U::kWidth);
+        const float wanted = 3.0f * static_cast<float>(k) + 64.0f;
+        const float p_element = fminf(1.0f, wanted / slice_elements);
+        const float p_thread = 1.0f - __expf(static_cast<float>(kGroupsPerTile * U::kWidth) * log1pf(-fminf(p_element, 0.999f)));
+        r = static_cast<uint32_t>(ceilf(p_thread * kThreads));
+        r = max(r, min(k, 4u));
+        if (r > (3u * kThreads) / 4u)
+            return false; // the threshold would pass nearly everything
+    }
+
+    uint4 v[kGroupsPerTile];
+#pragma unroll
+    for (int j = 0; j < kGroupsPerTile; ++j)
+        v[j] = load_stream_16(vector_base + (group_begin + j) * kThreads + tid);
+    float top = U::maximum(v[0]);
+#pragma unroll
+    for (int j = 1; j < kGroupsPerTile; ++j)
+        top = fmaxf(top, U::maximum(v[j]));
+    const uint32_t my_key = (top == top) ? ordered_key(top) : 0u;
+    // r-th largest key of the block, one bit per barrier
+    uint32_t threshold_key = 0;
+#pragma unroll 1
+    for (int bit = 31; bit >= 0; --bit)
+    {
+        const uint32_t candidate = threshold_key | (1u << bit);
+        if (static_cast<uint32_t>(__syncthreads_count(my_key >= candidate)) >= r)
+            threshold_key = candidate;
+    }
+    if (threshold_key <= kKeyNegInf)
+        return false; // the tile holds (almost) nothing finite
+    float tau;
+    if (mode == kLive)
+    {
+        if (tid == 0)
+            atomicMax(&s.maxkey, threshold_key);
+        tau = live_threshold(threshold_key, temperature);
+    }
+    else
+    {
+        tau = key_to_float(threshold_key);
+    }
+
+    uint32_t g = group_begin;
+    for (;;)
+    {
+#pragma unroll
+        for (int j = 0; j < kGroupsPerTile; ++j)
+        {
+            if (U::maximum(v[j]) >= tau)
+            {
+                float x[U::kWidth];
+                U::values(v[j], x);
+                offer_values<U::kWidth>(s, mode, tau, x, head + ((g + j) * kThreads + tid) * U::kWidth);
+            }
+        }
+        g += kGroupsPerTile;
+        if (g + kGroupsPerTile > full_end)
+            break;
+#pragma unroll
+        for (int j = 0; j < kGroupsPerTile; ++j)
+            v[j] = load_stream_16(vector_base + (g + j) * kThreads + tid);
+        if (mode == kLive)
+            tau = fmaxf(tau, live_threshold(*reinterpret_cast<volatile uint32_t*>(&s.maxkey), temperature));
+    }
+    // full groups that do not fill a tile, then the ragged last group
+    for (; g < group_end; ++g)
+    {
+        const uint32_t vi = g * kThreads + tid;
+        const uint4 one = (vi < vectors) ? load_stream_16(vector_base + vi) : U::nan_vector();
+        if (U::maximum(one) >= tau)
+        {
+            float x[U::kWidth];
+            U::values(one, x);
+            offer_values<U::kWidth>(s, mode, tau, x, head + vi * U::kWidth);
+        }
+    }
+    // logits before / after the 16-byte aligned body of the row
+    if (first_rank && tid < static_cast<int>(head))
+    {
+        const float x[1] = {LogitTraits<T>::widen(row_pointer, tid)};
+        offer_values<1>(s, mode, tau, x, static_cast<uint32_t>(tid));
+    }
+    if (last_rank && tail_begin + tid < vocab)
+    {
+        const float x[1] = {LogitTraits<T>::widen(row_pointer, tail_begin + tid)};
+        offer_values<1>(s, mode, tau, x, tail_begin + tid);
+    }
+    __syncthreads();
+    const uint32_t found = s.count;
+    const bool overflow = s.overflow != 0;
+    __syncthreads();
+    if (overflow || (mode != kLive && found < k))
+    {
+        if (tid == 0)
+        {
+            s.count = 0;
+            s.maxkey = 0;
+            s.overflow = 0;
+        }
+        __syncthreads();
+        return false;
+    }
+    return true;
+}
+
 // Sorts the surviving records into rank order and finishes the row: writes the
 // Top-K index list, runs the sequential arithmetic on one warp, flags stop
 // tokens, or hands the row to the exact kernel.  Called by the whole block.
@@ -433,6 +676,7 @@ __global__ void __launch_bounds__(kThreads, 4) sample_rows_kernel(const SampleAr
         s.count = 0;
         s.maxkey = 0;
         s.abort_flag = 0;
+        s.overflow = 0;
     }
     __syncthreads();
 
@@ -447,77 +691,13 @@ __global__ void __launch_bounds__(kThreads, 4) sample_rows_kernel(const SampleAr
     const uint32_t groups = (vectors + kThreads - 1) / kThreads;
     const uint32_t group_begin = static_cast<uint32_t>(static_cast<uint64_t>(rank) * groups / splits);
     const uint32_t group_end = static_cast<uint32_t>(static_cast<uint64_t>(rank + 1) * groups / splits);
-    const uint4* vector_base = reinterpret_cast<const uint4*>(row_pointer + head);
 
-    // unaligned leading logits (lowest indices: first, by the first CTA)
-    if (rank == 0 && head > 0)
-    {
-        float x[1] = {tid < static_cast<int>(head) ? LogitTraits<T>::widen(row_pointer, tid) : __uint_as_float(0x7FC00000u)};
-        uint32_t stored = 0;
-        const bool want = push_values<1>(c, x, static_cast<uint32_t>(tid), false, stored, 0);
-        if (__syncthreads_or(want))
-            flush_buffer(c);
-    }
-
-    uint32_t g = group_begin;
-    // a short first tile establishes the threshold cheaply
-    if (g < group_end && !c.aborted)
-    {
-        uint4 v[1];
-        const uint32_t vi = g * kThreads + tid;
-        v[0] = (vi < vectors) ? load_stream_16(vector_base + vi) : U::nan_vector();
-        run_tile<T, 1>(c, v, g, head);
-        g += 1;
-    }
-    // full tiles, next tile's loads in flight while this one is filtered
-    const uint32_t full_groups = vectors / kThreads; // groups with all kThreads vectors present
-    const uint32_t full_end = min(group_end, full_groups);
-    if (g + kGroupsPerTile <= full_end && !c.aborted)
-    {
-        uint4 current[kGroupsPerTile];
-#pragma unroll
-        for (int j = 0; j < kGroupsPerTile; ++j)
-            current[j] = load_stream_16(vector_base + (g + j) * kThreads + tid);
-        while (true)
-        {
-            const bool has_next = (g + 2 * kGroupsPerTile <= full_end);
-            uint4 next[kGroupsPerTile];
-            if (has_next)
-            {
-#pragma unroll
-                for (int j = 0; j < kGroupsPerTile; ++j)
-                    next[j] = load_stream_16(vector_base + (g + kGroupsPerTile + j) * kThreads + tid);
-            }
-            run_tile<T, kGroupsPerTile>(c, current, g, head);
-            g += kGroupsPerTile;
-            if (!has_next || c.aborted)
-                break;
-#pragma unroll
-            for (int j = 0; j < kGroupsPerTile; ++j)
-                current[j] = next[j];
-        }
-    }
-    // leftover groups (fewer than a tile, or the ragged last group)
-    while (g < group_end && !c.aborted)
-    {
-        uint4 v[1];
-        const uint32_t vi = g * kThreads + tid;
-        v[0] = (vi < vectors) ? load_stream_16(vector_base + vi) : U::nan_vector();
-        run_tile<T, 1>(c, v, g, head);
-        g += 1;
-    }
-    // unaligned trailing logits (highest indices: last, by the last CTA)
-    if (rank == splits - 1 && tail_begin < vocab && !c.aborted)
-    {
-        const uint32_t index = tail_begin + tid;
-        float x[1] = {index < vocab ? LogitTraits<T>::widen(row_pointer, index) : __uint_as_float(0x7FC00000u)};
-        uint32_t stored = 0;
-        const bool want = push_values<1>(c, x, index, false, stored, 0);
-        if (__syncthreads_or(want))
-            flush_buffer(c);
-    }
-    __syncthreads();
-    if (!c.aborted)
+    bool streamed = false;
+    streamed = stream_slice_fast<T>(s, c.mode, c.k, p.temperature, row_pointer, vocab, head, vectors, tail_begin, group_begin, group_end,
+                                        rank == 0, rank == splits - 1);
+    if (!streamed)
+        stream_slice_safe<T>(c, row_pointer, vocab, head, vectors, tail_begin, group_begin, group_end, rank, splits);
+    else
         flush_buffer(c); // exact k best / exact live set of this slice
     if (tid == 0)
         s.abort_flag = c.aborted ? 1u : 0u;
