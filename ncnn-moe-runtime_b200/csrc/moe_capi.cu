@@ -220,6 +220,10 @@ int moe_sampler_create(int device, uint32_t max_rows, uint32_t max_vocab, moe_sa
     allocate(reinterpret_cast<void**>(&counters), 2 * sizeof(uint32_t));
     allocate(reinterpret_cast<void**>(&ws.exact_rows), sizeof(uint32_t) * max_rows);
     allocate(reinterpret_cast<void**>(&ws.sort_keys), sizeof(uint32_t) * 4u * stride * ws.slots);
+    ws.slice_slots = static_cast<uint32_t>(sampler->sm_count) * 4u * 4u + 64u;
+    allocate(reinterpret_cast<void**>(&ws.slice_records), sizeof(uint64_t) * MOE_SLICE_SLOT_RECORDS * ws.slice_slots);
+    allocate(reinterpret_cast<void**>(&ws.slice_header), sizeof(uint32_t) * 4u * ws.slice_slots);
+    allocate(reinterpret_cast<void**>(&ws.row_arrivals), sizeof(uint32_t) * max_rows);
     allocate(reinterpret_cast<void**>(&sampler->params_dev), sizeof(moe_row_params) * max_rows);
     allocate(reinterpret_cast<void**>(&sampler->stop_offsets_dev), sizeof(int32_t) * (static_cast<size_t>(max_rows) + 1));
     allocate(reinterpret_cast<void**>(&sampler->token_dev), sizeof(int32_t) * max_rows);
@@ -230,6 +234,8 @@ int moe_sampler_create(int device, uint32_t max_rows, uint32_t max_vocab, moe_sa
     allocate(reinterpret_cast<void**>(&sampler->router_status_dev), sizeof(int32_t));
     if (status == cudaSuccess)
         status = cudaMemset(counters, 0, 2 * sizeof(uint32_t));
+    if (status == cudaSuccess)
+        status = cudaMemset(ws.row_arrivals, 0, sizeof(uint32_t) * max_rows);
     if (status == cudaSuccess)
         status = cudaMemset(sampler->router_error, 0xFF, sizeof(unsigned long long));
     if (status == cudaSuccess)
@@ -253,7 +259,8 @@ void moe_sampler_destroy(moe_sampler* sampler)
         return;
     DeviceGuard guard(sampler->device);
     cudaDeviceSynchronize();
-    void* pointers[] = {sampler->ws.exact_count, sampler->ws.exact_rows, sampler->ws.sort_keys, sampler->params_dev, sampler->stop_offsets_dev,
+    void* pointers[] = {sampler->ws.exact_count, sampler->ws.exact_rows, sampler->ws.sort_keys, sampler->ws.slice_records,
+                        sampler->ws.slice_header, sampler->ws.row_arrivals, sampler->params_dev, sampler->stop_offsets_dev,
                         sampler->stop_tokens_dev, sampler->logits_dev, sampler->token_dev, sampler->probability_dev, sampler->flags_dev,
                         sampler->status_dev, sampler->topk_dev, sampler->selected_expert, sampler->selected_weight, sampler->expert_counts,
                         sampler->router_error, sampler->router_logits_dev, sampler->router_bias_dev, sampler->router_explicit_dev,
@@ -352,7 +359,7 @@ int moe_sample_batch(moe_sampler* sampler, void* stream_handle, const void* logi
     args.row_status = row_status;
     args.topk_index = topk_index;
     args.topk_stride = topk_index != nullptr ? topk_stride : 0;
-    const uint32_t splits = choose_splits(rows, vocab, dtype, sampler->sm_count);
+    const uint32_t splits = choose_splits(rows, vocab, dtype, sampler->sm_count, sampler->ws.slice_slots);
     MOE_CUDA_CHECK(sampler, launch_sample_rows(args, sampler->ws, splits, stream));
     if (sampler->resident_needs_exact)
         MOE_CUDA_CHECK(sampler, launch_sample_exact(args, sampler->ws, stream));
@@ -421,7 +428,7 @@ int moe_sample_local_candidates(moe_sampler* sampler, void* stream_handle, const
     args.candidates_out = candidates;
     args.candidates_k = top_k;
     args.vocab_begin = vocab_begin;
-    const uint32_t splits = choose_splits(rows, vocab, dtype, sampler->sm_count);
+    const uint32_t splits = choose_splits(rows, vocab, dtype, sampler->sm_count, sampler->ws.slice_slots);
     MOE_CUDA_CHECK(sampler, launch_sample_rows(args, sampler->ws, splits, static_cast<cudaStream_t>(stream_handle)));
     return MOE_STATUS_OK;
 }

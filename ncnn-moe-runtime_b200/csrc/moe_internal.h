@@ -8,6 +8,8 @@
 
 #include "../../include/moe_b200_sampler.h"
 
+#define MOE_SLICE_SLOT_RECORDS 1024u
+
 namespace moe {
 
 // Device workspace shared by the kernels of one handle.
@@ -21,6 +23,12 @@ struct Workspace
     // per-slot scratch of the exact kernel: (keys, index) pair 0 then pair 1,
     // each array `max_vocab` rounded up to a multiple of 4 entries
     uint32_t* sort_keys = nullptr;     // [slots][4][stride]
+    // publication slots of the streaming kernel when a row is cut into slices:
+    // one per CTA, MOE_SLICE_SLOT_RECORDS records and a 4-word header each
+    uint64_t* slice_records = nullptr; // [slice_slots][MOE_SLICE_SLOT_RECORDS]
+    uint32_t* slice_header = nullptr;  // [slice_slots][4]: count, needs-exact flag, max key, pad
+    uint32_t* row_arrivals = nullptr;  // [max_rows] slices of the row that have published (self-resetting)
+    uint32_t slice_slots = 0;
     uint32_t slots = 0;
     uint32_t max_rows = 0;
     uint32_t max_vocab = 0;
@@ -73,6 +81,6 @@ cudaError_t launch_router_dispatch_kernels(const RouterArgs& args, uint32_t* exp
 cudaError_t launch_regroup_gather(const float* hidden, uint32_t columns, const uint32_t* route_token, uint32_t route_count, float* gathered,
                                   cudaStream_t stream);
 
-uint32_t choose_splits(uint32_t rows, uint32_t vocab, int dtype, int sm_count);
+uint32_t choose_splits(uint32_t rows, uint32_t vocab, int dtype, int sm_count, uint32_t slice_slots);
 
 } // namespace moe

@@ -1,8 +1,8 @@
 // Streaming sampler kernel: one pass over each logit row.
 //
-// A row is cut into `splits` contiguous slices, one CTA each; the CTAs of a row
-// form a thread-block cluster.  A CTA streams its slice with 128-bit loads and
-// keeps, in shared memory, only the records that can still matter:
+// A row is cut into `splits` contiguous slices, one CTA each.  A CTA streams its
+// slice with 128-bit loads and keeps, in shared memory, only the records that
+// can still matter:
 //   greedy rows      the best finite logit so far              (session.cpp:404-424)
 //   Top-K rows       the k best records so far                 (session.cpp:80-87)
 //   full-vocab rows  the records whose softmax numerator could be >= 2^-26
@@ -10,23 +10,49 @@
 // A record passes a single float compare against a threshold held in a register;
 // the threshold is tightened by a shared-memory radix select (Top-K) or by
 // re-testing against the running maximum (live) whenever the buffer fills.
-// After the stream the slices are merged over distributed shared memory by the
-// cluster's first CTA, the survivors are sorted into the reference rank order
-// and one warp replays the reference's sequential softmax / Min-P / Top-P /
-// renormalise / inverse-CDF arithmetic on them (moe_epilogue.cuh).
+// After the stream a CTA publishes its survivors to a small global scratch slot
+// and counts itself in; nobody waits.  The CTA that arrives last for a row
+// gathers the row's slots, selects the k best (or the live set), sorts them into
+// the reference rank order, and one warp replays the reference's sequential
+// softmax / Min-P / Top-P / renormalise / inverse-CDF arithmetic on them
+// (moe_epilogue.cuh) while the other CTAs of the SM keep streaming other rows.
 //
 // Rows whose live set does not fit on chip, and draws that fall through to a
 // numerically dead candidate, are appended to a list that the exact kernel
 // (moe_sample_exact.cu) finishes.
-
-#include <cooperative_groups.h>
 
 #include "moe_common.cuh"
 #include "moe_epilogue.cuh"
 #include "moe_internal.h"
 #include "moe_select.cuh"
 
-namespace cg = cooperative_groups;
+#ifdef MOE_PHASE_TIMERS
+// Debug builds only: cycles spent per kernel phase, summed over CTAs.
+__device__ unsigned long long g_phase_cycles[16];
+extern "C" void moe_debug_phase_cycles(unsigned long long* out, int reset)
+{
+    cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(unsigned long long) * 16);
+    if (reset)
+    {
+        unsigned long long zeros[16] = {};
+        cudaMemcpyToSymbol(g_phase_cycles, zeros, sizeof(zeros));
+    }
+}
+#define MOE_PHASE_MARK(slot)                                                      \
+    do                                                                            \
+    {                                                                             \
+        if (threadIdx.x == 0)                                                     \
+        {                                                                         \
+            const long long moe_now = clock64();                                  \
+            atomicAdd(&g_phase_cycles[slot], static_cast<unsigned long long>(moe_now - moe_phase_start)); \
+            moe_phase_start = moe_now;                                            \
+        }                                                                         \
+    } while (0)
+#define MOE_PHASE_BEGIN() long long moe_phase_start = clock64()
+#else
+#define MOE_PHASE_MARK(slot) do {} while (0)
+#define MOE_PHASE_BEGIN() do {} while (0)
+#endif
 
 namespace moe {
 
@@ -37,7 +63,8 @@ constexpr int kCap = 4096;                // records a CTA can hold
 constexpr int kItems = kCap / kThreads;   // records per thread in block-wide passes
 constexpr int kGroupsPerTile = 4;         // 128-bit loads in flight per thread
 constexpr uint32_t kLiveFlush = 2048;     // live mode: re-test the buffer at this fill
-constexpr uint32_t kLiveAbort = 1536;     // live mode: more survivors than this -> exact kernel
+constexpr uint32_t kLiveAbort = 1024;     // live mode: more survivors than this -> exact kernel
+constexpr uint32_t kSliceCap = MOE_SLICE_SLOT_RECORDS; // records a slice may publish
 // A candidate whose (logit/T - peak) is below this has exp() < 2^-26 and is
 // absorbed by every running fp32 sum that starts at the head candidate.
 constexpr float kDeadOffset = -18.1f;
@@ -136,6 +163,69 @@ struct Unpack<__nv_bfloat16>
     __device__ static __forceinline__ uint4 nan_vector()
     {
         return make_uint4(0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u);
+    }
+};
+
+// 256-bit vectors of the barrier-free loop.
+template<typename T>
+struct Wide;
+
+template<>
+struct Wide<float>
+{
+    static constexpr int kWidth = 8;
+    __device__ static __forceinline__ void values(const Vec32& v, float (&x)[8])
+    {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            x[i] = __uint_as_float(v.w[i]);
+    }
+    __device__ static __forceinline__ float maximum(const Vec32& v)
+    {
+        const float a = fmaxf(fmaxf(__uint_as_float(v.w[0]), __uint_as_float(v.w[1])), fmaxf(__uint_as_float(v.w[2]), __uint_as_float(v.w[3])));
+        const float b = fmaxf(fmaxf(__uint_as_float(v.w[4]), __uint_as_float(v.w[5])), fmaxf(__uint_as_float(v.w[6]), __uint_as_float(v.w[7])));
+        return fmaxf(a, b);
+    }
+    __device__ static __forceinline__ Vec32 nan_vector()
+    {
+        Vec32 v;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            v.w[i] = 0x7FC00000u;
+        return v;
+    }
+};
+
+template<>
+struct Wide<__nv_bfloat16>
+{
+    static constexpr int kWidth = 16;
+    __device__ static __forceinline__ void values(const Vec32& v, float (&x)[16])
+    {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+        {
+            x[2 * i] = __uint_as_float(v.w[i] << 16);
+            x[2 * i + 1] = __uint_as_float(v.w[i] & 0xFFFF0000u);
+        }
+    }
+    __device__ static __forceinline__ float maximum(const Vec32& v)
+    {
+        // packed bf16 max ignores NaN operands exactly like fmaxf
+        __nv_bfloat162 m = *reinterpret_cast<const __nv_bfloat162*>(&v.w[0]);
+#pragma unroll
+        for (int i = 1; i < 8; ++i)
+            m = __hmax2(m, *reinterpret_cast<const __nv_bfloat162*>(&v.w[i]));
+        const uint32_t bits = *reinterpret_cast<const uint32_t*>(&m);
+        return fmaxf(__uint_as_float(bits << 16), __uint_as_float(bits & 0xFFFF0000u));
+    }
+    __device__ static __forceinline__ Vec32 nan_vector()
+    {
+        Vec32 v;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            v.w[i] = 0x7FC07FC0u;
+        return v;
     }
 };
 
@@ -407,9 +497,9 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, Mode mode, uint3
                                                   uint32_t head, uint32_t vectors, uint32_t tail_begin, uint32_t group_begin, uint32_t group_end,
                                                   bool first_rank, bool last_rank)
 {
-    using U = Unpack<T>;
+    using W = Wide<T>;
     const int tid = threadIdx.x;
-    const uint4* vector_base = reinterpret_cast<const uint4*>(row_pointer + head);
+    const Vec32* vector_base = reinterpret_cast<const Vec32*>(row_pointer + head);
     const uint32_t full_groups = vectors / kThreads;
     const uint32_t full_end = min(group_end, full_groups);
     if (group_begin + kGroupsPerTile > full_end)
@@ -419,33 +509,81 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, Mode mode, uint3
     uint32_t r = 1;
     if (mode == kTopK)
     {
-        const float slice_elements = static_cast<float>(group_end - group_begin) * (kThreads * U::kWidth);
+        const float slice_elements = static_cast<float>(group_end - group_begin) * (kThreads * W::kWidth);
         const float wanted = 3.0f * static_cast<float>(k) + 64.0f;
         const float p_element = fminf(1.0f, wanted / slice_elements);
-        const float p_thread = 1.0f - __expf(static_cast<float>(kGroupsPerTile * U::kWidth) * log1pf(-fminf(p_element, 0.999f)));
+        const float p_thread = 1.0f - __expf(static_cast<float>(kGroupsPerTile * W::kWidth) * log1pf(-fminf(p_element, 0.999f)));
         r = static_cast<uint32_t>(ceilf(p_thread * kThreads));
         r = max(r, min(k, 4u));
         if (r > (3u * kThreads) / 4u)
             return false; // the threshold would pass nearly everything
     }
 
-    uint4 v[kGroupsPerTile];
+    Vec32 v[kGroupsPerTile];
 #pragma unroll
     for (int j = 0; j < kGroupsPerTile; ++j)
-        v[j] = load_stream_16(vector_base + (group_begin + j) * kThreads + tid);
-    float top = U::maximum(v[0]);
+        v[j] = load_stream_32(vector_base + (group_begin + j) * kThreads + tid);
+    float top = W::maximum(v[0]);
 #pragma unroll
     for (int j = 1; j < kGroupsPerTile; ++j)
-        top = fmaxf(top, U::maximum(v[j]));
+        top = fmaxf(top, W::maximum(v[j]));
     const uint32_t my_key = (top == top) ? ordered_key(top) : 0u;
-    // r-th largest key of the block, one bit per barrier
-    uint32_t threshold_key = 0;
-#pragma unroll 1
-    for (int bit = 31; bit >= 0; --bit)
+    // Threshold = the r-th largest of the block's thread maxima: at least r
+    // logits of the tile reach it.  Each warp sorts its 32 maxima with a
+    // shuffle network; a thread's block-wide rank is its warp rank plus, for
+    // every other warp, the number of larger maxima found by binary search.
+    uint32_t threshold_key;
     {
-        const uint32_t candidate = threshold_key | (1u << bit);
-        if (static_cast<uint32_t>(__syncthreads_count(my_key >= candidate)) >= r)
-            threshold_key = candidate;
+        const int lane = tid & 31;
+        const int warp = tid >> 5;
+        uint32_t sorted_key = my_key; // descending by lane after the network
+#pragma unroll
+        for (int size = 2; size <= 32; size <<= 1)
+        {
+#pragma unroll
+            for (int stride = size >> 1; stride > 0; stride >>= 1)
+            {
+                const uint32_t other = __shfl_xor_sync(kFullMask, sorted_key, stride);
+                const bool descending = (lane & size) == 0;
+                const bool lower_lane = (lane & stride) == 0;
+                const bool take_max = (descending == lower_lane);
+                sorted_key = take_max ? max(sorted_key, other) : min(sorted_key, other);
+            }
+        }
+        uint32_t* lists = s.sel.hist; // kThreads entries
+        lists[tid] = sorted_key;
+        if (tid == 0)
+            s.sel.bucket = 0;
+        __syncthreads();
+        if (static_cast<uint32_t>(lane) < r)
+        {
+            // keys strictly greater, plus equal keys of earlier warps, precede this one
+            uint32_t rank_in_block = lane;
+            for (int w = 0; w < kThreads / 32; ++w)
+            {
+                if (w == warp)
+                    continue;
+                const uint32_t* list = lists + w * 32;
+                // count of entries that precede sorted_key in a descending list
+                uint32_t lo = 0, hi = 32;
+                while (lo < hi)
+                {
+                    const uint32_t mid = (lo + hi) >> 1;
+                    const uint32_t value = list[mid];
+                    const bool precedes = (value > sorted_key) || (value == sorted_key && w < warp);
+                    if (precedes)
+                        lo = mid + 1;
+                    else
+                        hi = mid;
+                }
+                rank_in_block += lo;
+            }
+            if (rank_in_block == r - 1)
+                s.sel.bucket = sorted_key;
+        }
+        __syncthreads();
+        threshold_key = s.sel.bucket;
+        __syncthreads(); // hist / bucket are reused by the selects
     }
     if (threshold_key <= kKeyNegInf)
         return false; // the tile holds (almost) nothing finite
@@ -467,11 +605,11 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, Mode mode, uint3
 #pragma unroll
         for (int j = 0; j < kGroupsPerTile; ++j)
         {
-            if (U::maximum(v[j]) >= tau)
+            if (W::maximum(v[j]) >= tau)
             {
-                float x[U::kWidth];
-                U::values(v[j], x);
-                offer_values<U::kWidth>(s, mode, tau, x, head + ((g + j) * kThreads + tid) * U::kWidth);
+                float x[W::kWidth];
+                W::values(v[j], x);
+                offer_values<W::kWidth>(s, mode, tau, x, head + ((g + j) * kThreads + tid) * W::kWidth);
             }
         }
         g += kGroupsPerTile;
@@ -479,7 +617,7 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, Mode mode, uint3
             break;
 #pragma unroll
         for (int j = 0; j < kGroupsPerTile; ++j)
-            v[j] = load_stream_16(vector_base + (g + j) * kThreads + tid);
+            v[j] = load_stream_32(vector_base + (g + j) * kThreads + tid);
         if (mode == kLive)
             tau = fmaxf(tau, live_threshold(*reinterpret_cast<volatile uint32_t*>(&s.maxkey), temperature));
     }
@@ -487,15 +625,15 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, Mode mode, uint3
     for (; g < group_end; ++g)
     {
         const uint32_t vi = g * kThreads + tid;
-        const uint4 one = (vi < vectors) ? load_stream_16(vector_base + vi) : U::nan_vector();
-        if (U::maximum(one) >= tau)
+        const Vec32 one = (vi < vectors) ? load_stream_32(vector_base + vi) : W::nan_vector();
+        if (W::maximum(one) >= tau)
         {
-            float x[U::kWidth];
-            U::values(one, x);
-            offer_values<U::kWidth>(s, mode, tau, x, head + vi * U::kWidth);
+            float x[W::kWidth];
+            W::values(one, x);
+            offer_values<W::kWidth>(s, mode, tau, x, head + vi * W::kWidth);
         }
     }
-    // logits before / after the 16-byte aligned body of the row
+    // logits before / after the 32-byte aligned body of the row
     if (first_rank && tid < static_cast<int>(head))
     {
         const float x[1] = {LogitTraits<T>::widen(row_pointer, tid)};
@@ -606,15 +744,13 @@ __device__ __forceinline__ void finish_row_block(const SampleArgs& a, RowShared&
 }
 
 template<typename T>
-__global__ void __launch_bounds__(kThreads, 4) sample_rows_kernel(const SampleArgs a, uint32_t* exact_count, uint32_t* exact_rows)
+__global__ void __launch_bounds__(kThreads, 4) sample_rows_kernel(const SampleArgs a, const Workspace ws, const uint32_t splits)
 {
     using U = Unpack<T>;
     extern __shared__ __align__(16) unsigned char shared_raw[];
     RowShared& s = *reinterpret_cast<RowShared*>(shared_raw);
-    cg::cluster_group cluster = cg::this_cluster();
-    const uint32_t splits = cluster.num_blocks();
-    const uint32_t rank = cluster.block_rank();
     const uint32_t row = blockIdx.x / splits;
+    const uint32_t rank = blockIdx.x - row * splits;
     const int tid = threadIdx.x;
     const bool candidates_only = a.candidates_out != nullptr;
 
@@ -631,10 +767,11 @@ __global__ void __launch_bounds__(kThreads, 4) sample_rows_kernel(const SampleAr
     {
         p = a.params[row];
     }
+    MOE_PHASE_BEGIN();
     const int invalid = validate_row(p);
     if (invalid != MOE_ROW_OK)
     {
-        // every CTA of the cluster takes this branch, so nobody waits on a cluster barrier
+        // every CTA of the row takes this branch, so the arrival counter stays untouched
         if (rank == 0)
         {
             if (tid == 0)
@@ -683,69 +820,107 @@ __global__ void __launch_bounds__(kThreads, 4) sample_rows_kernel(const SampleAr
     // ---- the slice of this CTA -------------------------------------------------
     const T* row_pointer = static_cast<const T*>(a.logits) + static_cast<size_t>(row) * a.row_stride;
     const uint32_t vocab = a.vocab;
-    const uint32_t misaligned = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(row_pointer) & 15u);
-    uint32_t head = ((16u - misaligned) & 15u) / static_cast<uint32_t>(sizeof(T));
+    // the row body is walked in 32-byte vectors from the first 32-byte boundary;
+    // `groups` of kThreads vectors are dealt to the row's CTAs in contiguous runs
+    const uint32_t misaligned = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(row_pointer) & 31u);
+    uint32_t head = ((32u - misaligned) & 31u) / static_cast<uint32_t>(sizeof(T));
     head = min(head, vocab);
-    const uint32_t vectors = (vocab - head) / U::kWidth;
-    const uint32_t tail_begin = head + vectors * U::kWidth;
+    const uint32_t vectors = (vocab - head) / Wide<T>::kWidth;
+    const uint32_t tail_begin = head + vectors * Wide<T>::kWidth;
     const uint32_t groups = (vectors + kThreads - 1) / kThreads;
     const uint32_t group_begin = static_cast<uint32_t>(static_cast<uint64_t>(rank) * groups / splits);
     const uint32_t group_end = static_cast<uint32_t>(static_cast<uint64_t>(rank + 1) * groups / splits);
 
-    bool streamed = false;
-    streamed = stream_slice_fast<T>(s, c.mode, c.k, p.temperature, row_pointer, vocab, head, vectors, tail_begin, group_begin, group_end,
-                                        rank == 0, rank == splits - 1);
-    if (!streamed)
-        stream_slice_safe<T>(c, row_pointer, vocab, head, vectors, tail_begin, group_begin, group_end, rank, splits);
-    else
-        flush_buffer(c); // exact k best / exact live set of this slice
+    MOE_PHASE_MARK(0);
+    const bool streamed = stream_slice_fast<T>(s, c.mode, c.k, p.temperature, row_pointer, vocab, head, vectors, tail_begin, group_begin,
+                                               group_end, rank == 0, rank == splits - 1);
+    MOE_PHASE_MARK(1);
+#ifdef MOE_PHASE_TIMERS
     if (tid == 0)
-        s.abort_flag = c.aborted ? 1u : 0u;
+    {
+        atomicAdd(&g_phase_cycles[10], static_cast<unsigned long long>(streamed ? s.count : 0u));
+        atomicAdd(&g_phase_cycles[9], streamed ? 0ull : 1ull);
+    }
+#endif
+    if (!streamed)
+        stream_slice_safe<T>(c, row_pointer, vocab, head, 2u * vectors, tail_begin, 2u * group_begin, min(2u * group_end, (2u * vectors + kThreads - 1) / kThreads),
+                             rank, splits); // the same logits in 16-byte vectors
+    MOE_PHASE_MARK(2);
 
-    // ---- merge the slices of the row over distributed shared memory ---------------
     if (splits > 1)
     {
-        cluster.sync();
-        if (rank == 0)
+        // ---- publish this slice, count in, and leave unless last -------------------
+        if (!c.aborted && s.count > kSliceCap)
+            flush_buffer(c); // Top-K: <= k records; live: re-tested against the slice maximum
+        const uint32_t mine = s.count;
+        const bool publishable = !c.aborted && mine <= kSliceCap;
+        uint64_t* slot_records = ws.slice_records + static_cast<size_t>(blockIdx.x) * kSliceCap;
+        uint32_t* slot_header = ws.slice_header + static_cast<size_t>(blockIdx.x) * 4u;
+        if (publishable)
+            for (uint32_t i = tid; i < mine; i += kThreads)
+                slot_records[i] = s.rec[i];
+        if (tid == 0)
         {
-            for (uint32_t peer = 1; peer < splits; ++peer)
-            {
-                const RowShared* remote = cluster.map_shared_rank(&s, peer);
-                const uint32_t remote_count = remote->count;
-                if (remote->abort_flag != 0)
-                    c.aborted = true;
-                if (c.aborted)
-                    continue;
-                if (s.count + remote_count > kCap)
-                {
-                    flush_buffer(c);
-                    if (s.count + remote_count > kCap)
-                    {
-                        c.aborted = true;
-                        continue;
-                    }
-                }
-                const uint32_t local_count = s.count;
-                for (uint32_t i = tid; i < remote_count; i += kThreads)
-                    s.rec[local_count + i] = remote->rec[i];
-                const uint32_t remote_max = remote->maxkey;
-                __syncthreads();
-                if (tid == 0)
-                {
-                    s.count = local_count + remote_count;
-                    s.maxkey = max(s.maxkey, remote_max);
-                }
-                __syncthreads();
-            }
-            if (!c.aborted)
-                flush_buffer(c);
+            slot_header[0] = publishable ? mine : 0u;
+            slot_header[1] = publishable ? 0u : 1u; // the row needs the exact kernel
+            slot_header[2] = s.maxkey;
         }
-        cluster.sync(); // peers leave only after their shared memory has been read
-        if (rank != 0)
+        __threadfence();
+        __syncthreads();
+        if (tid == 0)
+            s.sel.bucket = (atomicAdd(&ws.row_arrivals[row], 1u) == splits - 1) ? 1u : 0u;
+        __syncthreads();
+        const bool last = s.sel.bucket != 0;
+        MOE_PHASE_MARK(3);
+        if (!last)
             return;
+        __threadfence();
+        if (tid == 0)
+            ws.row_arrivals[row] = 0; // ready for the next launch
+        if (!publishable)
+            c.aborted = true;
+        // ---- gather the other slices of the row -------------------------------------
+        for (uint32_t peer = 0; peer < splits; ++peer)
+        {
+            if (peer == rank)
+                continue;
+            const uint32_t peer_block = row * splits + peer;
+            const uint32_t* peer_header = ws.slice_header + static_cast<size_t>(peer_block) * 4u;
+            const uint32_t remote_count = __ldcg(peer_header + 0);
+            const uint32_t remote_abort = __ldcg(peer_header + 1);
+            const uint32_t remote_max = __ldcg(peer_header + 2);
+            if (remote_abort != 0)
+                c.aborted = true;
+            if (c.aborted)
+                continue;
+            if (s.count + remote_count > kCap)
+            {
+                flush_buffer(c);
+                if (c.aborted || s.count + remote_count > kCap)
+                {
+                    c.aborted = true;
+                    continue;
+                }
+            }
+            const uint32_t local_count = s.count;
+            const uint64_t* remote_records = ws.slice_records + static_cast<size_t>(peer_block) * kSliceCap;
+            for (uint32_t i = tid; i < remote_count; i += kThreads)
+                s.rec[local_count + i] = __ldcg(reinterpret_cast<const unsigned long long*>(remote_records + i));
+            __syncthreads();
+            if (tid == 0)
+            {
+                s.count = local_count + remote_count;
+                s.maxkey = max(s.maxkey, remote_max);
+            }
+            __syncthreads();
+        }
+        MOE_PHASE_MARK(5);
     }
-
-    finish_row_block(a, s, c, p, row, exact_count, exact_rows);
+    if (!c.aborted)
+        flush_buffer(c); // the row's exact k best / exact live set
+    MOE_PHASE_MARK(6);
+    finish_row_block(a, s, c, p, row, ws.exact_count, ws.exact_rows);
+    MOE_PHASE_MARK(7);
 }
 
 // Vocabulary-sharded sampling, second step: after the caller's all-gather each
@@ -848,19 +1023,8 @@ cudaError_t launch_typed(const SampleArgs& args, const Workspace& ws, uint32_t s
             return status;
         configured = true;
     }
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(args.rows * splits, 1, 1);
-    config.blockDim = dim3(kThreads, 1, 1);
-    config.dynamicSmemBytes = shared_bytes;
-    config.stream = stream;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeClusterDimension;
-    attribute[0].val.clusterDim.x = splits;
-    attribute[0].val.clusterDim.y = 1;
-    attribute[0].val.clusterDim.z = 1;
-    config.attrs = attribute;
-    config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, sample_rows_kernel<T>, args, ws.exact_count, ws.exact_rows);
+    sample_rows_kernel<T><<<args.rows * splits, kThreads, shared_bytes, stream>>>(args, ws, splits);
+    return cudaGetLastError();
 }
 
 } // namespace
@@ -903,19 +1067,19 @@ cudaError_t launch_merge_candidates(const uint64_t* gathered, uint32_t shards, u
     return cudaGetLastError();
 }
 
-uint32_t choose_splits(uint32_t rows, uint32_t vocab, int dtype, int sm_count)
+uint32_t choose_splits(uint32_t rows, uint32_t vocab, int dtype, int sm_count, uint32_t slice_slots)
 {
     const uint64_t row_bytes = static_cast<uint64_t>(vocab) * (dtype == MOE_DTYPE_F32 ? 4u : 2u);
     const uint64_t by_size = row_bytes / (64u * 1024u);          // at least 64 KiB per slice
     const uint64_t resident = static_cast<uint64_t>(sm_count) * 4u; // CTAs the GPU holds at once
     const uint64_t wanted = (2u * resident + rows - 1) / (rows ? rows : 1u);
-    uint64_t limit = 8; // portable cluster size
+    uint64_t limit = 8;
     if (by_size < limit)
         limit = by_size;
     if (wanted < limit)
         limit = wanted;
     uint32_t splits = 1;
-    while (splits * 2u <= limit)
+    while (splits * 2u <= limit && static_cast<uint64_t>(rows) * splits * 2u <= slice_slots)
         splits *= 2u;
     return splits;
 }

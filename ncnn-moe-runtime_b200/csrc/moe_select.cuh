@@ -34,12 +34,15 @@ __device__ __noinline__ uint64_t block_radix_select(uint64_t* records, uint32_t 
     const int lane = tid & 31;
     const int warp = tid >> 5;
 
+    const int used = static_cast<int>((n + kThreads - 1) / kThreads); // item slots that hold anything
     uint64_t item[kItems];
     uint64_t any_bits = 0;
     uint64_t all_bits = ~0ull;
 #pragma unroll
     for (int j = 0; j < kItems; ++j)
     {
+        if (j >= used)
+            break;
         const uint32_t i = tid + j * kThreads;
         item[j] = (i < n) ? records[i] : 0ull;
         if (i < n)
@@ -82,6 +85,8 @@ __device__ __noinline__ uint64_t block_radix_select(uint64_t* records, uint32_t 
 #pragma unroll
         for (int j = 0; j < kItems; ++j)
         {
+            if (j >= used)
+                break;
             const uint32_t i = tid + j * kThreads;
             const bool live = (i < n) && ((item[j] & prefix_mask) == prefix_value);
             const uint32_t digit = live ? (static_cast<uint32_t>(item[j] >> low) & digit_mask) : 0xFFFFFFFFu;
@@ -151,6 +156,8 @@ __device__ __noinline__ uint64_t block_radix_select(uint64_t* records, uint32_t 
 #pragma unroll
     for (int j = 0; j < kItems; ++j)
     {
+        if (j >= used)
+            break;
         const uint32_t i = tid + j * kThreads;
         const bool keep = (i < n) && ((item[j] >> low) >= threshold);
         const unsigned voters = __ballot_sync(kFullMask, keep);
@@ -214,10 +221,13 @@ __device__ __forceinline__ uint32_t block_compact(uint64_t* records, uint32_t n,
 {
     const int tid = threadIdx.x;
     const int lane = tid & 31;
+    const int used = static_cast<int>((n + kThreads - 1) / kThreads);
     uint64_t item[kItems];
 #pragma unroll
     for (int j = 0; j < kItems; ++j)
     {
+        if (j >= used)
+            break;
         const uint32_t i = tid + j * kThreads;
         item[j] = (i < n) ? records[i] : 0ull;
     }
@@ -227,6 +237,8 @@ __device__ __forceinline__ uint32_t block_compact(uint64_t* records, uint32_t n,
 #pragma unroll
     for (int j = 0; j < kItems; ++j)
     {
+        if (j >= used)
+            break;
         const uint32_t i = tid + j * kThreads;
         const bool keep = (i < n) && keep_record(item[j]);
         const unsigned voters = __ballot_sync(kFullMask, keep);
