@@ -2,6 +2,7 @@
 // argument checks, parameter upload, kernel launches, host-buffer variants.
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -160,6 +161,19 @@ int upload_rows(moe_sampler* sampler, cudaStream_t stream, uint32_t rows, const 
     sampler->resident_rows = rows;
     sampler->resident_needs_exact = needs_exact;
     return MOE_STATUS_OK;
+}
+
+// Slices per row; MOE_B200_SPLITS (1, 2, 4 or 8) overrides the built-in policy for tuning runs.
+uint32_t pick_splits(const moe_sampler* sampler, uint32_t rows, uint32_t vocab, int dtype)
+{
+    uint32_t splits = pick_splits(sampler, rows, vocab, dtype);
+    if (const char* forced = std::getenv("MOE_B200_SPLITS"))
+    {
+        const long value = std::strtol(forced, nullptr, 10);
+        if ((value == 1 || value == 2 || value == 4 || value == 8) && static_cast<uint64_t>(rows) * value <= sampler->ws.slice_slots)
+            splits = static_cast<uint32_t>(value);
+    }
+    return splits;
 }
 
 int check_shape(moe_sampler* sampler, int dtype, uint32_t rows, uint32_t vocab, size_t row_stride)
@@ -359,7 +373,7 @@ int moe_sample_batch(moe_sampler* sampler, void* stream_handle, const void* logi
     args.row_status = row_status;
     args.topk_index = topk_index;
     args.topk_stride = topk_index != nullptr ? topk_stride : 0;
-    const uint32_t splits = choose_splits(rows, vocab, dtype, sampler->sm_count, sampler->ws.slice_slots);
+    const uint32_t splits = pick_splits(sampler, rows, vocab, dtype);
     MOE_CUDA_CHECK(sampler, launch_sample_rows(args, sampler->ws, splits, stream));
     if (sampler->resident_needs_exact)
         MOE_CUDA_CHECK(sampler, launch_sample_exact(args, sampler->ws, stream));
@@ -428,7 +442,7 @@ int moe_sample_local_candidates(moe_sampler* sampler, void* stream_handle, const
     args.candidates_out = candidates;
     args.candidates_k = top_k;
     args.vocab_begin = vocab_begin;
-    const uint32_t splits = choose_splits(rows, vocab, dtype, sampler->sm_count, sampler->ws.slice_slots);
+    const uint32_t splits = pick_splits(sampler, rows, vocab, dtype);
     MOE_CUDA_CHECK(sampler, launch_sample_rows(args, sampler->ws, splits, static_cast<cudaStream_t>(stream_handle)));
     return MOE_STATUS_OK;
 }

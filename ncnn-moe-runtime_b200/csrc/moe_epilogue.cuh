@@ -4,8 +4,10 @@
 // step: every sum is a left-to-right fp32 accumulation in rank order, because
 // the reference's results (the Top-P cut in particular) depend on that order.
 // The expensive per-candidate work (exp, divisions) is done one candidate per
-// lane; the running sums are replayed lane by lane through shuffles so that all
-// 32 lanes hold the same accumulator and take the same branches.
+// lane into a scratch array; the running sums are then replayed by every lane
+// redundantly over that array (broadcast loads, unrolled so that only the
+// dependent adds are on the critical path), so all 32 lanes hold the same
+// accumulator and take the same branches.
 #pragma once
 
 #include "moe_common.cuh"
@@ -63,21 +65,13 @@ __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, u
 
     // softmax numerators and their sequential sum (session.cpp:89-101)
     const float peak = __fdiv_rn(key_to_float(head_key), temperature);
-    float total = 0.0f;
-    for (uint32_t base = 0; base < finite; base += 32)
-    {
-        const uint32_t i = base + lane;
-        float weight = 0.0f;
-        if (i < finite)
-        {
-            weight = exact_expf(scaled_offset(key_to_float(record_key(records[i])), temperature, peak));
-            work[i] = weight;
-        }
-        const uint32_t steps = min(32u, finite - base);
-        for (uint32_t j = 0; j < steps; ++j)
-            total = __fadd_rn(total, __shfl_sync(kFullMask, weight, j));
-    }
+    for (uint32_t i = lane; i < finite; i += 32)
+        work[i] = exact_expf(scaled_offset(key_to_float(record_key(records[i])), temperature, peak));
     __syncwarp();
+    float total = 0.0f;
+#pragma unroll 8
+    for (uint32_t i = 0; i < finite; ++i)
+        total = __fadd_rn(total, work[i]);
     if (finite == 0 || !(total - total == 0.0f) || total <= 0.0f)
     {
         out.status = MOE_ROW_INVALID_DISTRIBUTION; // session.cpp:102-103
@@ -85,58 +79,37 @@ __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, u
     }
 
     // probabilities, Min-P floor, Top-P prefix (session.cpp:104-128)
-    const float floor_probability = __fmul_rn(__fdiv_rn(work[0], total), min_p);
     __syncwarp();
+    for (uint32_t i = lane; i < finite; i += 32)
+        work[i] = __fdiv_rn(work[i], total);
+    __syncwarp();
+    const float floor_probability = __fmul_rn(work[0], min_p);
     float running = 0.0f;
     uint32_t kept = 0;
     bool cut = false; // Min-P or Top-P closed the list: no omitted candidate can follow it
-    for (uint32_t base = 0; base < finite; base += 32)
+#pragma unroll 4
+    for (uint32_t i = 0; i < finite; ++i)
     {
-        const uint32_t i = base + lane;
-        float probability = 0.0f;
-        bool passes = false;
-        if (i < finite)
+        const float probability = work[i];
+        if (min_p > 0.0f && !(probability >= floor_probability))
         {
-            probability = __fdiv_rn(work[i], total);
-            work[i] = probability;
-            passes = (min_p > 0.0f) ? (probability >= floor_probability) : true;
+            cut = true; // probabilities are non-increasing: nothing after this passes either
+            break;
         }
-        const unsigned pass_mask = __ballot_sync(kFullMask, passes);
-        const uint32_t steps = (pass_mask == kFullMask) ? 32u : static_cast<uint32_t>(__ffs(~pass_mask) - 1);
-        bool reached = false;
-        for (uint32_t j = 0; j < steps; ++j)
-        {
-            running = __fadd_rn(running, __shfl_sync(kFullMask, probability, j));
-            ++kept;
-            if (running >= top_p)
-            {
-                reached = true;
-                break;
-            }
-        }
-        if (reached)
+        running = __fadd_rn(running, probability);
+        ++kept;
+        if (running >= top_p)
         {
             cut = true;
             break;
         }
-        if (steps < 32)
-        {
-            cut = cut || (base + steps < finite);
-            break;
-        }
     }
-    __syncwarp();
 
     // renormaliser (session.cpp:130-134)
     float kept_total = 0.0f;
-    for (uint32_t base = 0; base < kept; base += 32)
-    {
-        const uint32_t i = base + lane;
-        const float probability = (i < kept) ? work[i] : 0.0f;
-        const uint32_t steps = min(32u, kept - base);
-        for (uint32_t j = 0; j < steps; ++j)
-            kept_total = __fadd_rn(kept_total, __shfl_sync(kFullMask, probability, j));
-    }
+#pragma unroll 8
+    for (uint32_t i = 0; i < kept; ++i)
+        kept_total = __fadd_rn(kept_total, work[i]);
 
     if (kept == 1)
     {
@@ -147,22 +120,21 @@ __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, u
     out.flags |= MOE_ROW_FLAG_USED_UNIFORM;
 
     // inverse CDF (session.cpp:432-442)
+    __syncwarp();
+    for (uint32_t i = lane; i < kept; i += 32)
+        work[i] = __fdiv_rn(work[i], kept_total);
+    __syncwarp();
     running = 0.0f;
-    for (uint32_t base = 0; base < kept; base += 32)
+#pragma unroll 4
+    for (uint32_t i = 0; i < kept; ++i)
     {
-        const uint32_t i = base + lane;
-        const float probability = (i < kept) ? __fdiv_rn(work[i], kept_total) : 0.0f;
-        const uint32_t steps = min(32u, kept - base);
-        for (uint32_t j = 0; j < steps; ++j)
+        const float q = work[i];
+        running = __fadd_rn(running, q);
+        if (uniform < running)
         {
-            const float q = __shfl_sync(kFullMask, probability, j);
-            running = __fadd_rn(running, q);
-            if (uniform < running)
-            {
-                out.token = static_cast<int32_t>(record_index(records[base + j]));
-                out.probability = q;
-                return out;
-            }
+            out.token = static_cast<int32_t>(record_index(records[i]));
+            out.probability = q;
+            return out;
         }
     }
     if (!list_is_complete && !cut)
@@ -171,7 +143,7 @@ __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, u
         return out;
     }
     out.token = static_cast<int32_t>(record_index(records[kept - 1]));
-    out.probability = __fdiv_rn(work[kept - 1], kept_total);
+    out.probability = work[kept - 1];
     return out;
 }
 

@@ -97,6 +97,7 @@ struct Ctx
     float tau;
     bool primed;
     bool aborted;
+    bool sorted; // the buffer is already in rank order
 };
 
 __device__ __forceinline__ float live_threshold(uint32_t maxkey, float temperature)
@@ -510,7 +511,7 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, Mode mode, uint3
     if (mode == kTopK)
     {
         const float slice_elements = static_cast<float>(group_end - group_begin) * (kThreads * W::kWidth);
-        const float wanted = 3.0f * static_cast<float>(k) + 64.0f;
+        const float wanted = 2.0f * static_cast<float>(k) + 32.0f;
         const float p_element = fminf(1.0f, wanted / slice_elements);
         const float p_thread = 1.0f - __expf(static_cast<float>(kGroupsPerTile * W::kWidth) * log1pf(-fminf(p_element, 0.999f)));
         r = static_cast<uint32_t>(ceilf(p_thread * kThreads));
@@ -662,6 +663,37 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, Mode mode, uint3
     return true;
 }
 
+// Brings the buffer down to what the row can still need — the k best records
+// (Top-K, greedy) or the records live against the buffer's maximum — and, when
+// that is at most a block's worth, leaves it sorted in rank order.
+__device__ __forceinline__ void reduce_buffer(Ctx& c)
+{
+    RowShared& s = c.s;
+    c.sorted = false;
+    if (c.aborted)
+        return;
+    const uint32_t n = s.count;
+    if (c.mode != kLive && n <= kThreads)
+    {
+        // sort first, then the k best are simply the front of the buffer
+        block_rank_sort_descending<kThreads>(s.rec, n);
+        if (n > c.k)
+        {
+            if (threadIdx.x == 0)
+                s.count = c.k;
+            __syncthreads();
+        }
+        c.sorted = true;
+        return;
+    }
+    flush_buffer(c);
+    if (!c.aborted && s.count <= kThreads)
+    {
+        block_rank_sort_descending<kThreads>(s.rec, s.count);
+        c.sorted = true;
+    }
+}
+
 // Sorts the surviving records into rank order and finishes the row: writes the
 // Top-K index list, runs the sequential arithmetic on one warp, flags stop
 // tokens, or hands the row to the exact kernel.  Called by the whole block.
@@ -677,11 +709,21 @@ __device__ __forceinline__ void finish_row_block(const SampleArgs& a, RowShared&
         return;
     }
     const uint32_t n = s.count;
-    const uint32_t padded = next_pow2(n);
-    for (uint32_t i = n + tid; i < padded; i += kThreads)
-        s.rec[i] = 0ull;
-    __syncthreads();
-    block_sort_descending<kThreads>(s.rec, padded);
+    if (!c.sorted)
+    {
+        if (n <= kThreads)
+        {
+            block_rank_sort_descending<kThreads>(s.rec, n);
+        }
+        else
+        {
+            const uint32_t padded = next_pow2(n);
+            for (uint32_t i = n + tid; i < padded; i += kThreads)
+                s.rec[i] = 0ull;
+            __syncthreads();
+            block_sort_descending<kThreads>(s.rec, padded);
+        }
+    }
 
     if (candidates_only)
     {
@@ -790,7 +832,7 @@ __global__ void __launch_bounds__(kThreads, 4) sample_rows_kernel(const SampleAr
         return;
     }
 
-    Ctx c{s, kLive, 0xFFFFFFFFu, kLiveFlush, p.temperature, -INFINITY, true, false};
+    Ctx c{s, kLive, 0xFFFFFFFFu, kLiveFlush, p.temperature, -INFINITY, true, false, false};
     if (p.temperature == 0.0f)
     {
         c.mode = kGreedy;
@@ -850,8 +892,7 @@ __global__ void __launch_bounds__(kThreads, 4) sample_rows_kernel(const SampleAr
     if (splits > 1)
     {
         // ---- publish this slice, count in, and leave unless last -------------------
-        if (!c.aborted && s.count > kSliceCap)
-            flush_buffer(c); // Top-K: <= k records; live: re-tested against the slice maximum
+        reduce_buffer(c); // Top-K: the slice's k best; live: re-tested against the slice maximum
         const uint32_t mine = s.count;
         const bool publishable = !c.aborted && mine <= kSliceCap;
         uint64_t* slot_records = ws.slice_records + static_cast<size_t>(blockIdx.x) * kSliceCap;
@@ -916,8 +957,7 @@ __global__ void __launch_bounds__(kThreads, 4) sample_rows_kernel(const SampleAr
         }
         MOE_PHASE_MARK(5);
     }
-    if (!c.aborted)
-        flush_buffer(c); // the row's exact k best / exact live set
+    reduce_buffer(c); // the row's exact k best / exact live set
     MOE_PHASE_MARK(6);
     finish_row_block(a, s, c, p, row, ws.exact_count, ws.exact_rows);
     MOE_PHASE_MARK(7);
@@ -955,7 +995,7 @@ __global__ void __launch_bounds__(kThreads, 4) merge_candidates_kernel(const uin
                 a.topk_index[static_cast<size_t>(row) * a.topk_stride + i] = -1;
         return;
     }
-    Ctx c{s, kTopK, top_k, 0xFFFFFFFFu, p.temperature, -INFINITY, false, false};
+    Ctx c{s, kTopK, top_k, 0xFFFFFFFFu, p.temperature, -INFINITY, false, false, false};
     if (tid == 0)
     {
         s.count = 0;
@@ -1069,17 +1109,16 @@ cudaError_t launch_merge_candidates(const uint64_t* gathered, uint32_t shards, u
 
 uint32_t choose_splits(uint32_t rows, uint32_t vocab, int dtype, int sm_count, uint32_t slice_slots)
 {
+    // Cut rows into slices only while all CTAs of the launch stay resident at
+    // once (4 per SM): a single wave has no ragged second wave, and the fixed
+    // per-slice work (threshold estimate, select, publication) stays small
+    // next to a slice of at least 64 KiB.
     const uint64_t row_bytes = static_cast<uint64_t>(vocab) * (dtype == MOE_DTYPE_F32 ? 4u : 2u);
-    const uint64_t by_size = row_bytes / (64u * 1024u);          // at least 64 KiB per slice
-    const uint64_t resident = static_cast<uint64_t>(sm_count) * 4u; // CTAs the GPU holds at once
-    const uint64_t wanted = (2u * resident + rows - 1) / (rows ? rows : 1u);
-    uint64_t limit = 8;
-    if (by_size < limit)
-        limit = by_size;
-    if (wanted < limit)
-        limit = wanted;
+    const uint64_t by_size = row_bytes / (64u * 1024u);
+    const uint64_t resident = static_cast<uint64_t>(sm_count) * 4u;
     uint32_t splits = 1;
-    while (splits * 2u <= limit && static_cast<uint64_t>(rows) * splits * 2u <= slice_slots)
+    while (splits < 8u && static_cast<uint64_t>(rows) * splits * 2u <= resident && splits * 2u <= by_size &&
+           static_cast<uint64_t>(rows) * splits * 2u <= slice_slots)
         splits *= 2u;
     return splits;
 }

@@ -288,6 +288,33 @@ __device__ __noinline__ void block_sort_descending(uint64_t* records, uint32_t p
     }
 }
 
+// Sorts records[0..n) descending for n <= kThreads by counting, for every
+// record, the records that precede it (records are unique, so ranks are too).
+// Two barriers and no atomics: the cheapest order for the few hundred survivors
+// a slice or a row usually has.  Ends with a barrier.
+template<int kThreads>
+__device__ __noinline__ void block_rank_sort_descending(uint64_t* records, uint32_t n)
+{
+    const uint32_t tid = threadIdx.x;
+    const uint64_t mine = (tid < n) ? records[tid] : 0ull;
+    uint32_t rank = 0;
+    const uint32_t pairs = n >> 1;
+    const ulonglong2* two = reinterpret_cast<const ulonglong2*>(records); // records are 16-byte aligned
+#pragma unroll 4
+    for (uint32_t i = 0; i < pairs; ++i)
+    {
+        const ulonglong2 both = two[i];
+        rank += (both.x > mine) ? 1u : 0u;
+        rank += (both.y > mine) ? 1u : 0u;
+    }
+    if (n & 1u)
+        rank += (records[n - 1] > mine) ? 1u : 0u;
+    __syncthreads();
+    if (tid < n)
+        records[rank] = mine;
+    __syncthreads();
+}
+
 __device__ __forceinline__ uint32_t next_pow2(uint32_t v)
 {
     return (v <= 1) ? 1u : (1u << (32 - __clz(static_cast<int>(v - 1))));
