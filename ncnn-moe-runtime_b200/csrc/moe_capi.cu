@@ -29,6 +29,7 @@ struct moe_sampler
     size_t stop_tokens_capacity = 0;
     uint32_t resident_rows = 0;
     bool resident_needs_exact = false;
+    bool resident_large_top_k = false;
     bool resident_has_stops = false;
 
     // staging for the host-buffer entry points
@@ -131,6 +132,7 @@ int upload_rows(moe_sampler* sampler, cudaStream_t stream, uint32_t rows, const 
                 const int32_t* stop_tokens)
 {
     bool needs_exact = false;
+    bool large_top_k = false;
     for (uint32_t row = 0; row < rows; ++row)
     {
         const moe_row_params& p = params[row];
@@ -138,6 +140,8 @@ int upload_rows(moe_sampler* sampler, cudaStream_t stream, uint32_t rows, const 
             continue;
         if (p.top_k == 0 || p.top_k > MOE_SAMPLER_TOPK_FAST_MAX)
             needs_exact = true;
+        else if (p.top_k > MOE_SAMPLER_TOPK_SMALL_MAX)
+            large_top_k = true;
     }
     // pageable source: the runtime stages the bytes before returning, so the
     // caller's array may be reused at once
@@ -160,13 +164,14 @@ int upload_rows(moe_sampler* sampler, cudaStream_t stream, uint32_t rows, const 
     }
     sampler->resident_rows = rows;
     sampler->resident_needs_exact = needs_exact;
+    sampler->resident_large_top_k = large_top_k;
     return MOE_STATUS_OK;
 }
 
 // Slices per row; MOE_B200_SPLITS (1, 2, 4 or 8) overrides the built-in policy for tuning runs.
-uint32_t pick_splits(const moe_sampler* sampler, uint32_t rows, uint32_t vocab, int dtype)
+uint32_t pick_splits(const moe_sampler* sampler, uint32_t rows, uint32_t vocab, int dtype, bool large_top_k)
 {
-    uint32_t splits = pick_splits(sampler, rows, vocab, dtype);
+    uint32_t splits = choose_splits(rows, vocab, dtype, sampler->sm_count, sampler->ws.slice_slots, large_top_k);
     if (const char* forced = std::getenv("MOE_B200_SPLITS"))
     {
         const long value = std::strtol(forced, nullptr, 10);
@@ -234,7 +239,7 @@ int moe_sampler_create(int device, uint32_t max_rows, uint32_t max_vocab, moe_sa
     allocate(reinterpret_cast<void**>(&counters), 2 * sizeof(uint32_t));
     allocate(reinterpret_cast<void**>(&ws.exact_rows), sizeof(uint32_t) * max_rows);
     allocate(reinterpret_cast<void**>(&ws.sort_keys), sizeof(uint32_t) * 4u * stride * ws.slots);
-    ws.slice_slots = static_cast<uint32_t>(sampler->sm_count) * 4u * 4u + 64u;
+    ws.slice_slots = static_cast<uint32_t>(sampler->sm_count) * 6u * 2u + 64u;
     allocate(reinterpret_cast<void**>(&ws.slice_records), sizeof(uint64_t) * MOE_SLICE_SLOT_RECORDS * ws.slice_slots);
     allocate(reinterpret_cast<void**>(&ws.slice_header), sizeof(uint32_t) * 4u * ws.slice_slots);
     allocate(reinterpret_cast<void**>(&ws.row_arrivals), sizeof(uint32_t) * max_rows);
@@ -373,7 +378,8 @@ int moe_sample_batch(moe_sampler* sampler, void* stream_handle, const void* logi
     args.row_status = row_status;
     args.topk_index = topk_index;
     args.topk_stride = topk_index != nullptr ? topk_stride : 0;
-    const uint32_t splits = pick_splits(sampler, rows, vocab, dtype);
+    args.large_top_k = sampler->resident_large_top_k;
+    const uint32_t splits = pick_splits(sampler, rows, vocab, dtype, args.large_top_k);
     MOE_CUDA_CHECK(sampler, launch_sample_rows(args, sampler->ws, splits, stream));
     if (sampler->resident_needs_exact)
         MOE_CUDA_CHECK(sampler, launch_sample_exact(args, sampler->ws, stream));
@@ -442,7 +448,8 @@ int moe_sample_local_candidates(moe_sampler* sampler, void* stream_handle, const
     args.candidates_out = candidates;
     args.candidates_k = top_k;
     args.vocab_begin = vocab_begin;
-    const uint32_t splits = pick_splits(sampler, rows, vocab, dtype);
+    args.large_top_k = top_k > MOE_SAMPLER_TOPK_SMALL_MAX;
+    const uint32_t splits = pick_splits(sampler, rows, vocab, dtype, args.large_top_k);
     MOE_CUDA_CHECK(sampler, launch_sample_rows(args, sampler->ws, splits, static_cast<cudaStream_t>(stream_handle)));
     return MOE_STATUS_OK;
 }

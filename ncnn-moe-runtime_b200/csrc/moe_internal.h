@@ -9,6 +9,8 @@
 #include "../../include/moe_b200_sampler.h"
 
 #define MOE_SLICE_SLOT_RECORDS 1024u
+// largest top_k the small-buffer kernel instantiation serves (3 * k + 48 sampled records must fit 2048)
+#define MOE_SAMPLER_TOPK_SMALL_MAX 448u
 
 namespace moe {
 
@@ -55,6 +57,9 @@ struct SampleArgs
     uint64_t* candidates_out; // may be null
     uint32_t candidates_k;
     uint32_t vocab_begin;
+    // some row has a Top-K too large for the small record buffer: use the
+    // large-buffer instantiation (fewer CTAs per SM)
+    bool large_top_k;
 };
 
 cudaError_t launch_sample_rows(const SampleArgs& args, const Workspace& ws, uint32_t splits, cudaStream_t stream);
@@ -81,6 +86,6 @@ cudaError_t launch_router_dispatch_kernels(const RouterArgs& args, uint32_t* exp
 cudaError_t launch_regroup_gather(const float* hidden, uint32_t columns, const uint32_t* route_token, uint32_t route_count, float* gathered,
                                   cudaStream_t stream);
 
-uint32_t choose_splits(uint32_t rows, uint32_t vocab, int dtype, int sm_count, uint32_t slice_slots);
+uint32_t choose_splits(uint32_t rows, uint32_t vocab, int dtype, int sm_count, uint32_t slice_slots, bool large_top_k);
 
 } // namespace moe

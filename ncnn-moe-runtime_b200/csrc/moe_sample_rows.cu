@@ -59,11 +59,16 @@ namespace moe {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kCap = 4096;                // records a CTA can hold
-constexpr int kItems = kCap / kThreads;   // records per thread in block-wide passes
+constexpr int kCapSmall = 2048;           // records a CTA can hold: batches whose Top-K sizes are small (6 CTAs per SM)
+constexpr int kCapLarge = 4096;           // ... and batches with top_k up to MOE_SAMPLER_TOPK_FAST_MAX (4 CTAs per SM)
+constexpr int kItems = kCapLarge / kThreads; // most records per thread in block-wide passes
 constexpr int kGroupsPerTile = 4;         // 128-bit loads in flight per thread
-constexpr uint32_t kLiveFlush = 2048;     // live mode: re-test the buffer at this fill
-constexpr uint32_t kLiveAbort = 1024;     // live mode: more survivors than this -> exact kernel
+// live mode: the buffer is re-tested against the running maximum at half fill;
+// more survivors than live_abort(cap) send the row to the exact kernel
+__host__ __device__ constexpr uint32_t live_abort(uint32_t cap)
+{
+    return cap / 2u - 256u < 1024u ? cap / 2u - 256u : 1024u;
+}
 constexpr uint32_t kSliceCap = MOE_SLICE_SLOT_RECORDS; // records a slice may publish
 // A candidate whose (logit/T - peak) is below this has exp() < 2^-26 and is
 // absorbed by every running fp32 sum that starts at the head candidate.
@@ -76,10 +81,9 @@ enum Mode : int
     kLive = 2
 };
 
+// Fixed part of a CTA's shared memory; `cap` records and `cap` floats follow it.
 struct __align__(16) RowShared
 {
-    uint64_t rec[kCap];
-    float work[kCap];
     SelectShared<kThreads> sel;
     uint32_t count;
     uint32_t maxkey;
@@ -90,6 +94,9 @@ struct __align__(16) RowShared
 struct Ctx
 {
     RowShared& s;
+    uint64_t* rec;  // cap records
+    float* work;    // cap floats (epilogue scratch)
+    uint32_t cap;
     Mode mode;
     uint32_t k;
     uint32_t flush_level;
@@ -267,9 +274,9 @@ __device__ __forceinline__ bool push_values(Ctx& c, const float (&x)[kWidth], ui
             base = atomicAdd(&s.count, votes);
         base = __shfl_sync(kFullMask, base, leader);
         const uint32_t slot = base + __popc(voters & ((1u << lane) - 1u));
-        if (pass && slot < kCap)
+        if (pass && slot < c.cap)
         {
-            s.rec[slot] = make_record(key, first_index + e);
+            c.rec[slot] = make_record(key, first_index + e);
             stored |= 1u << (bit_base + e);
         }
         if (c.mode == kLive)
@@ -293,32 +300,32 @@ __device__ __noinline__ bool flush_buffer(Ctx& c)
 {
     RowShared& s = c.s;
     const uint32_t raw = s.count;
-    const bool overflowed = raw > kCap;
-    uint32_t n = overflowed ? static_cast<uint32_t>(kCap) : raw;
+    const bool overflowed = raw > c.cap;
+    uint32_t n = overflowed ? static_cast<uint32_t>(c.cap) : raw;
     __syncthreads();
     if (c.mode == kLive)
     {
         const uint32_t maxkey = s.maxkey;
         const float temperature = c.temperature;
         const float peak = __fdiv_rn(key_to_float(maxkey), temperature);
-        n = block_compact<kThreads, kItems>(s.rec, n, s.sel, [=](uint64_t record) {
+        n = block_compact<kThreads, kItems>(c.rec, n, s.sel, [=](uint64_t record) {
             const float offset = scaled_offset(key_to_float(record_key(record)), temperature, peak);
             return !(offset < kDeadOffset); // keeps NaN offsets: the epilogue reports them
         });
         c.tau = live_threshold(maxkey, temperature);
-        if (n > kLiveAbort)
+        if (n > live_abort(c.cap))
             c.aborted = true;
     }
     else if (n > c.k)
     {
-        const uint64_t smallest = block_radix_select<kThreads, kItems>(s.rec, n, c.k, s.sel);
+        const uint64_t smallest = block_radix_select<kThreads, kItems>(c.rec, n, c.k, s.sel);
         n = c.k;
         c.tau = key_to_float(record_key(smallest));
         c.primed = true;
     }
     else if (n == c.k)
     {
-        const uint64_t smallest = block_min_record<kThreads>(s.rec, n, s.sel);
+        const uint64_t smallest = block_min_record<kThreads>(c.rec, n, s.sel);
         c.tau = key_to_float(record_key(smallest));
         c.primed = true;
     }
@@ -461,7 +468,8 @@ __device__ __noinline__ void stream_slice_safe(Ctx& c, const T* row_pointer, uin
 // Appends the logits of one lane that reach the threshold.  Runs divergently:
 // only lanes whose vector maximum reached the threshold get here.
 template<int kWidth>
-__device__ __forceinline__ void offer_values(RowShared& s, Mode mode, float tau, const float (&x)[kWidth], uint32_t first_index)
+__device__ __forceinline__ void offer_values(RowShared& s, uint64_t* rec, uint32_t cap, Mode mode, float tau, const float (&x)[kWidth],
+                                             uint32_t first_index)
 {
 #pragma unroll
     for (int e = 0; e < kWidth; ++e)
@@ -474,8 +482,8 @@ __device__ __forceinline__ void offer_values(RowShared& s, Mode mode, float tau,
         {
             const uint32_t key = ordered_key(v);
             const uint32_t slot = atomicAdd(&s.count, 1u);
-            if (slot < kCap)
-                s.rec[slot] = make_record(key, first_index + e);
+            if (slot < cap)
+                rec[slot] = make_record(key, first_index + e);
             else
                 s.overflow = 1u;
             if (mode == kLive)
@@ -494,7 +502,7 @@ __device__ __forceinline__ void offer_values(RowShared& s, Mode mode, float tau,
 // false (buffer reset) when fewer than k were found or the buffer overflowed;
 // the caller then runs the careful loop.
 template<typename T>
-__device__ __forceinline__ bool stream_slice_fast(RowShared& s, Mode mode, uint32_t k, float temperature, const T* row_pointer, uint32_t vocab,
+__device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, uint32_t cap, Mode mode, uint32_t k, float temperature, const T* row_pointer, uint32_t vocab,
                                                   uint32_t head, uint32_t vectors, uint32_t tail_begin, uint32_t group_begin, uint32_t group_end,
                                                   bool first_rank, bool last_rank)
 {
@@ -511,7 +519,7 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, Mode mode, uint3
     if (mode == kTopK)
     {
         const float slice_elements = static_cast<float>(group_end - group_begin) * (kThreads * W::kWidth);
-        const float wanted = 2.0f * static_cast<float>(k) + 32.0f;
+        const float wanted = 3.0f * static_cast<float>(k) + 48.0f;
         const float p_element = fminf(1.0f, wanted / slice_elements);
         const float p_thread = 1.0f - __expf(static_cast<float>(kGroupsPerTile * W::kWidth) * log1pf(-fminf(p_element, 0.999f)));
         r = static_cast<uint32_t>(ceilf(p_thread * kThreads));
@@ -529,50 +537,47 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, Mode mode, uint3
     for (int j = 1; j < kGroupsPerTile; ++j)
         top = fmaxf(top, W::maximum(v[j]));
     const uint32_t my_key = (top == top) ? ordered_key(top) : 0u;
-    // Threshold = the r-th largest of the block's thread maxima: at least r
-    // logits of the tile reach it.  Each warp sorts its 32 maxima with a
-    // shuffle network; a thread's block-wide rank is its warp rank plus, for
-    // every other warp, the number of larger maxima found by binary search.
-    uint32_t threshold_key;
+    // Each warp sorts its 32 thread maxima with a shuffle network; the block-wide
+    // rank of a maximum is its warp rank plus, for every other warp, the number
+    // of larger maxima found by binary search in that warp's sorted list.
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    uint32_t sorted_key = my_key; // descending by lane after the network
+#pragma unroll
+    for (int size = 2; size <= 32; size <<= 1)
     {
-        const int lane = tid & 31;
-        const int warp = tid >> 5;
-        uint32_t sorted_key = my_key; // descending by lane after the network
 #pragma unroll
-        for (int size = 2; size <= 32; size <<= 1)
+        for (int stride = size >> 1; stride > 0; stride >>= 1)
         {
-#pragma unroll
-            for (int stride = size >> 1; stride > 0; stride >>= 1)
-            {
-                const uint32_t other = __shfl_xor_sync(kFullMask, sorted_key, stride);
-                const bool descending = (lane & size) == 0;
-                const bool lower_lane = (lane & stride) == 0;
-                const bool take_max = (descending == lower_lane);
-                sorted_key = take_max ? max(sorted_key, other) : min(sorted_key, other);
-            }
+            const uint32_t other = __shfl_xor_sync(kFullMask, sorted_key, stride);
+            const bool descending = (lane & size) == 0;
+            const bool lower_lane = (lane & stride) == 0;
+            sorted_key = (descending == lower_lane) ? max(sorted_key, other) : min(sorted_key, other);
         }
-        uint32_t* lists = s.sel.hist; // kThreads entries
-        lists[tid] = sorted_key;
+    }
+    uint32_t* lists = s.sel.hist; // kThreads entries, untouched while streaming
+    lists[tid] = sorted_key;
+
+    for (int attempt = 0;; ++attempt)
+    {
+        // Threshold = the r-th largest thread maximum: at least r logits of the tile reach it.
         if (tid == 0)
             s.sel.bucket = 0;
         __syncthreads();
         if (static_cast<uint32_t>(lane) < r)
         {
-            // keys strictly greater, plus equal keys of earlier warps, precede this one
-            uint32_t rank_in_block = lane;
+            uint32_t rank_in_block = lane; // keys strictly greater, plus equal keys of earlier warps, precede this one
             for (int w = 0; w < kThreads / 32; ++w)
             {
                 if (w == warp)
                     continue;
                 const uint32_t* list = lists + w * 32;
-                // count of entries that precede sorted_key in a descending list
                 uint32_t lo = 0, hi = 32;
                 while (lo < hi)
                 {
                     const uint32_t mid = (lo + hi) >> 1;
                     const uint32_t value = list[mid];
-                    const bool precedes = (value > sorted_key) || (value == sorted_key && w < warp);
-                    if (precedes)
+                    if ((value > sorted_key) || (value == sorted_key && w < warp))
                         lo = mid + 1;
                     else
                         hi = mid;
@@ -583,74 +588,81 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, Mode mode, uint3
                 s.sel.bucket = sorted_key;
         }
         __syncthreads();
-        threshold_key = s.sel.bucket;
-        __syncthreads(); // hist / bucket are reused by the selects
-    }
-    if (threshold_key <= kKeyNegInf)
-        return false; // the tile holds (almost) nothing finite
-    float tau;
-    if (mode == kLive)
-    {
-        if (tid == 0)
-            atomicMax(&s.maxkey, threshold_key);
-        tau = live_threshold(threshold_key, temperature);
-    }
-    else
-    {
-        tau = key_to_float(threshold_key);
-    }
-
-    uint32_t g = group_begin;
-    for (;;)
-    {
-#pragma unroll
-        for (int j = 0; j < kGroupsPerTile; ++j)
+        const uint32_t threshold_key = s.sel.bucket;
+        if (threshold_key <= kKeyNegInf)
+            return false; // the tile holds (almost) nothing finite
+        float tau;
+        if (mode == kLive)
         {
-            if (W::maximum(v[j]) >= tau)
+            if (tid == 0)
+                atomicMax(&s.maxkey, threshold_key);
+            tau = live_threshold(threshold_key, temperature);
+        }
+        else
+        {
+            tau = key_to_float(threshold_key);
+        }
+
+        uint32_t g = group_begin;
+        if (attempt > 0)
+        {
+#pragma unroll
+            for (int j = 0; j < kGroupsPerTile; ++j)
+                v[j] = load_stream_32(vector_base + (g + j) * kThreads + tid);
+        }
+        for (;;)
+        {
+#pragma unroll
+            for (int j = 0; j < kGroupsPerTile; ++j)
+            {
+                if (W::maximum(v[j]) >= tau)
+                {
+                    float x[W::kWidth];
+                    W::values(v[j], x);
+                    offer_values<W::kWidth>(s, rec, cap, mode, tau, x, head + ((g + j) * kThreads + tid) * W::kWidth);
+                }
+            }
+            g += kGroupsPerTile;
+            if (g + kGroupsPerTile > full_end)
+                break;
+#pragma unroll
+            for (int j = 0; j < kGroupsPerTile; ++j)
+                v[j] = load_stream_32(vector_base + (g + j) * kThreads + tid);
+            if (mode == kLive)
+                tau = fmaxf(tau, live_threshold(*reinterpret_cast<volatile uint32_t*>(&s.maxkey), temperature));
+        }
+        // full groups that do not fill a tile, then the ragged last group
+        for (; g < group_end; ++g)
+        {
+            const uint32_t vi = g * kThreads + tid;
+            const Vec32 one = (vi < vectors) ? load_stream_32(vector_base + vi) : W::nan_vector();
+            if (W::maximum(one) >= tau)
             {
                 float x[W::kWidth];
-                W::values(v[j], x);
-                offer_values<W::kWidth>(s, mode, tau, x, head + ((g + j) * kThreads + tid) * W::kWidth);
+                W::values(one, x);
+                offer_values<W::kWidth>(s, rec, cap, mode, tau, x, head + vi * W::kWidth);
             }
         }
-        g += kGroupsPerTile;
-        if (g + kGroupsPerTile > full_end)
-            break;
-#pragma unroll
-        for (int j = 0; j < kGroupsPerTile; ++j)
-            v[j] = load_stream_32(vector_base + (g + j) * kThreads + tid);
-        if (mode == kLive)
-            tau = fmaxf(tau, live_threshold(*reinterpret_cast<volatile uint32_t*>(&s.maxkey), temperature));
-    }
-    // full groups that do not fill a tile, then the ragged last group
-    for (; g < group_end; ++g)
-    {
-        const uint32_t vi = g * kThreads + tid;
-        const Vec32 one = (vi < vectors) ? load_stream_32(vector_base + vi) : W::nan_vector();
-        if (W::maximum(one) >= tau)
+        // logits before / after the 32-byte aligned body of the row
+        if (first_rank && tid < static_cast<int>(head))
         {
-            float x[W::kWidth];
-            W::values(one, x);
-            offer_values<W::kWidth>(s, mode, tau, x, head + vi * W::kWidth);
+            const float x[1] = {LogitTraits<T>::widen(row_pointer, tid)};
+            offer_values<1>(s, rec, cap, mode, tau, x, static_cast<uint32_t>(tid));
         }
-    }
-    // logits before / after the 32-byte aligned body of the row
-    if (first_rank && tid < static_cast<int>(head))
-    {
-        const float x[1] = {LogitTraits<T>::widen(row_pointer, tid)};
-        offer_values<1>(s, mode, tau, x, static_cast<uint32_t>(tid));
-    }
-    if (last_rank && tail_begin + tid < vocab)
-    {
-        const float x[1] = {LogitTraits<T>::widen(row_pointer, tail_begin + tid)};
-        offer_values<1>(s, mode, tau, x, tail_begin + tid);
-    }
-    __syncthreads();
-    const uint32_t found = s.count;
-    const bool overflow = s.overflow != 0;
-    __syncthreads();
-    if (overflow || (mode != kLive && found < k))
-    {
+        if (last_rank && tail_begin + tid < vocab)
+        {
+            const float x[1] = {LogitTraits<T>::widen(row_pointer, tail_begin + tid)};
+            offer_values<1>(s, rec, cap, mode, tau, x, tail_begin + tid);
+        }
+        __syncthreads();
+        const uint32_t found = s.count;
+        const bool overflow = s.overflow != 0;
+        __syncthreads();
+        if (!overflow && (mode == kLive || found >= k))
+            return true;
+        // Too few logits reached the sampled threshold (or far too many): forget
+        // them.  A short count is retried once or twice with a lower threshold —
+        // the slice is in L2 now — before the careful loop takes over.
         if (tid == 0)
         {
             s.count = 0;
@@ -658,9 +670,11 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, Mode mode, uint3
             s.overflow = 0;
         }
         __syncthreads();
-        return false;
+        const uint32_t limit = (3u * kThreads) / 4u;
+        if (overflow || r >= limit || attempt >= 2)
+            return false;
+        r = min(limit, 4u * r + 16u);
     }
-    return true;
 }
 
 // Brings the buffer down to what the row can still need — the k best records
@@ -676,7 +690,7 @@ __device__ __forceinline__ void reduce_buffer(Ctx& c)
     if (c.mode != kLive && n <= kThreads)
     {
         // sort first, then the k best are simply the front of the buffer
-        block_rank_sort_descending<kThreads>(s.rec, n);
+        block_rank_sort_descending<kThreads>(c.rec, n);
         if (n > c.k)
         {
             if (threadIdx.x == 0)
@@ -689,7 +703,7 @@ __device__ __forceinline__ void reduce_buffer(Ctx& c)
     flush_buffer(c);
     if (!c.aborted && s.count <= kThreads)
     {
-        block_rank_sort_descending<kThreads>(s.rec, s.count);
+        block_rank_sort_descending<kThreads>(c.rec, s.count);
         c.sorted = true;
     }
 }
@@ -713,15 +727,15 @@ __device__ __forceinline__ void finish_row_block(const SampleArgs& a, RowShared&
     {
         if (n <= kThreads)
         {
-            block_rank_sort_descending<kThreads>(s.rec, n);
+            block_rank_sort_descending<kThreads>(c.rec, n);
         }
         else
         {
             const uint32_t padded = next_pow2(n);
             for (uint32_t i = n + tid; i < padded; i += kThreads)
-                s.rec[i] = 0ull;
+                c.rec[i] = 0ull;
             __syncthreads();
-            block_sort_descending<kThreads>(s.rec, padded);
+            block_sort_descending<kThreads>(c.rec, padded);
         }
     }
 
@@ -731,7 +745,7 @@ __device__ __forceinline__ void finish_row_block(const SampleArgs& a, RowShared&
         {
             uint64_t record = 0ull;
             if (i < n)
-                record = make_record(record_key(s.rec[i]), record_index(s.rec[i]) + a.vocab_begin);
+                record = make_record(record_key(c.rec[i]), record_index(c.rec[i]) + a.vocab_begin);
             a.candidates_out[static_cast<size_t>(row) * a.candidates_k + i] = record;
         }
         return;
@@ -741,7 +755,7 @@ __device__ __forceinline__ void finish_row_block(const SampleArgs& a, RowShared&
     {
         const uint32_t listed = (c.mode == kTopK) ? min(n, c.k) : 0u;
         for (uint32_t i = tid; i < a.topk_stride; i += kThreads)
-            a.topk_index[static_cast<size_t>(row) * a.topk_stride + i] = (i < listed) ? static_cast<int32_t>(record_index(s.rec[i])) : -1;
+            a.topk_index[static_cast<size_t>(row) * a.topk_stride + i] = (i < listed) ? static_cast<int32_t>(record_index(c.rec[i])) : -1;
     }
 
     if (tid < 32)
@@ -755,14 +769,14 @@ __device__ __forceinline__ void finish_row_block(const SampleArgs& a, RowShared&
             }
             else
             {
-                out.token = static_cast<int32_t>(record_index(s.rec[0]));
+                out.token = static_cast<int32_t>(record_index(c.rec[0]));
                 out.probability = 1.0f;
             }
         }
         else
         {
             const float uniform = philox_uniform(p.seed, p.row_id, p.step + a.step_offset);
-            out = finish_row_warp(s.rec, n, s.work, p.temperature, p.top_k, p.top_p, p.min_p, uniform, c.mode == kLive);
+            out = finish_row_warp(c.rec, n, c.work, p.temperature, p.top_k, p.top_p, p.min_p, uniform, c.mode == kLive);
         }
         if (tid == 0)
         {
@@ -785,12 +799,19 @@ __device__ __forceinline__ void finish_row_block(const SampleArgs& a, RowShared&
     }
 }
 
-template<typename T>
-__global__ void __launch_bounds__(kThreads, 4) sample_rows_kernel(const SampleArgs a, const Workspace ws, const uint32_t splits)
+__host__ __device__ constexpr size_t shared_bytes_for(uint32_t cap)
 {
-    using U = Unpack<T>;
+    return sizeof(RowShared) + static_cast<size_t>(cap) * (sizeof(uint64_t) + sizeof(float));
+}
+
+template<typename T, int kResident>
+__global__ void __launch_bounds__(kThreads, kResident) sample_rows_kernel(const SampleArgs a, const Workspace ws, const uint32_t splits)
+{
     extern __shared__ __align__(16) unsigned char shared_raw[];
     RowShared& s = *reinterpret_cast<RowShared*>(shared_raw);
+    constexpr uint32_t kCapacity = (kResident >= 6) ? kCapSmall : kCapLarge;
+    uint64_t* const records = reinterpret_cast<uint64_t*>(shared_raw + sizeof(RowShared));
+    float* const scratch = reinterpret_cast<float*>(records + kCapacity);
     const uint32_t row = blockIdx.x / splits;
     const uint32_t rank = blockIdx.x - row * splits;
     const int tid = threadIdx.x;
@@ -832,7 +853,7 @@ __global__ void __launch_bounds__(kThreads, 4) sample_rows_kernel(const SampleAr
         return;
     }
 
-    Ctx c{s, kLive, 0xFFFFFFFFu, kLiveFlush, p.temperature, -INFINITY, true, false, false};
+    Ctx c{s, records, scratch, kCapacity, kLive, 0xFFFFFFFFu, kCapacity / 2u, p.temperature, -INFINITY, true, false, false};
     if (p.temperature == 0.0f)
     {
         c.mode = kGreedy;
@@ -847,7 +868,7 @@ __global__ void __launch_bounds__(kThreads, 4) sample_rows_kernel(const SampleAr
     {
         c.primed = false;
         const uint32_t level = max(2u * c.k, c.k + 512u);
-        c.flush_level = min(level, static_cast<uint32_t>(kCap - 1024));
+        c.flush_level = min(level, c.cap - 1024u);
     }
 
     if (tid == 0)
@@ -874,7 +895,7 @@ __global__ void __launch_bounds__(kThreads, 4) sample_rows_kernel(const SampleAr
     const uint32_t group_end = static_cast<uint32_t>(static_cast<uint64_t>(rank + 1) * groups / splits);
 
     MOE_PHASE_MARK(0);
-    const bool streamed = stream_slice_fast<T>(s, c.mode, c.k, p.temperature, row_pointer, vocab, head, vectors, tail_begin, group_begin,
+    const bool streamed = stream_slice_fast<T>(s, c.rec, c.cap, c.mode, c.k, p.temperature, row_pointer, vocab, head, vectors, tail_begin, group_begin,
                                                group_end, rank == 0, rank == splits - 1);
     MOE_PHASE_MARK(1);
 #ifdef MOE_PHASE_TIMERS
@@ -899,7 +920,7 @@ __global__ void __launch_bounds__(kThreads, 4) sample_rows_kernel(const SampleAr
         uint32_t* slot_header = ws.slice_header + static_cast<size_t>(blockIdx.x) * 4u;
         if (publishable)
             for (uint32_t i = tid; i < mine; i += kThreads)
-                slot_records[i] = s.rec[i];
+                slot_records[i] = c.rec[i];
         if (tid == 0)
         {
             slot_header[0] = publishable ? mine : 0u;
@@ -934,10 +955,10 @@ __global__ void __launch_bounds__(kThreads, 4) sample_rows_kernel(const SampleAr
                 c.aborted = true;
             if (c.aborted)
                 continue;
-            if (s.count + remote_count > kCap)
+            if (s.count + remote_count > c.cap)
             {
                 flush_buffer(c);
-                if (c.aborted || s.count + remote_count > kCap)
+                if (c.aborted || s.count + remote_count > c.cap)
                 {
                     c.aborted = true;
                     continue;
@@ -946,7 +967,7 @@ __global__ void __launch_bounds__(kThreads, 4) sample_rows_kernel(const SampleAr
             const uint32_t local_count = s.count;
             const uint64_t* remote_records = ws.slice_records + static_cast<size_t>(peer_block) * kSliceCap;
             for (uint32_t i = tid; i < remote_count; i += kThreads)
-                s.rec[local_count + i] = __ldcg(reinterpret_cast<const unsigned long long*>(remote_records + i));
+                c.rec[local_count + i] = __ldcg(reinterpret_cast<const unsigned long long*>(remote_records + i));
             __syncthreads();
             if (tid == 0)
             {
@@ -973,6 +994,8 @@ __global__ void __launch_bounds__(kThreads, 4) merge_candidates_kernel(const uin
 {
     extern __shared__ __align__(16) unsigned char shared_raw[];
     RowShared& s = *reinterpret_cast<RowShared*>(shared_raw);
+    uint64_t* const records = reinterpret_cast<uint64_t*>(shared_raw + sizeof(RowShared));
+    float* const scratch = reinterpret_cast<float*>(records + kCapLarge);
     const uint32_t row = blockIdx.x;
     const int tid = threadIdx.x;
     const moe_row_params p = a.params[row];
@@ -995,7 +1018,7 @@ __global__ void __launch_bounds__(kThreads, 4) merge_candidates_kernel(const uin
                 a.topk_index[static_cast<size_t>(row) * a.topk_stride + i] = -1;
         return;
     }
-    Ctx c{s, kTopK, top_k, 0xFFFFFFFFu, p.temperature, -INFINITY, false, false, false};
+    Ctx c{s, records, scratch, kCapLarge, kTopK, top_k, 0xFFFFFFFFu, p.temperature, -INFINITY, false, false, false};
     if (tid == 0)
     {
         s.count = 0;
@@ -1005,7 +1028,7 @@ __global__ void __launch_bounds__(kThreads, 4) merge_candidates_kernel(const uin
     __syncthreads();
     for (uint32_t shard = 0; shard < shards; ++shard)
     {
-        if (s.count + top_k > kCap)
+        if (s.count + top_k > c.cap)
             flush_buffer(c);
         const uint32_t local_count = s.count;
         const uint64_t* list = gathered + (static_cast<size_t>(shard) * rows + row) * top_k;
@@ -1016,7 +1039,7 @@ __global__ void __launch_bounds__(kThreads, 4) merge_candidates_kernel(const uin
             const uint64_t record = list[i];
             if (record != 0ull)
             {
-                s.rec[local_count + i] = record;
+                c.rec[local_count + i] = record;
                 ++mine;
             }
         }
@@ -1037,7 +1060,7 @@ __global__ void __launch_bounds__(kThreads, 4) merge_candidates_kernel(const uin
     {
         // greedy over the merged candidates: best finite record (session.cpp:404-424)
         const uint32_t n = s.count;
-        const uint32_t kept = block_compact<kThreads, kItems>(s.rec, n, s.sel, [](uint64_t record) {
+        const uint32_t kept = block_compact<kThreads, kItems>(c.rec, n, s.sel, [](uint64_t record) {
             const uint32_t key = record_key(record);
             return key > kKeyNegInf && key < kKeyPosInf;
         });
@@ -1051,19 +1074,19 @@ __global__ void __launch_bounds__(kThreads, 4) merge_candidates_kernel(const uin
     finish_row_block(a, s, c, p, row, nullptr, nullptr);
 }
 
-template<typename T>
+template<typename T, int kResident>
 cudaError_t launch_typed(const SampleArgs& args, const Workspace& ws, uint32_t splits, cudaStream_t stream)
 {
-    static bool configured = false; // per type; the attribute is per device function
-    const size_t shared_bytes = sizeof(RowShared);
+    static bool configured = false; // per instantiation; the attribute is per device function
+    const size_t shared_bytes = shared_bytes_for(kResident >= 6 ? kCapSmall : kCapLarge);
     if (!configured)
     {
-        cudaError_t status = cudaFuncSetAttribute(sample_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared_bytes));
+        cudaError_t status = cudaFuncSetAttribute(sample_rows_kernel<T, kResident>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared_bytes));
         if (status != cudaSuccess)
             return status;
         configured = true;
     }
-    sample_rows_kernel<T><<<args.rows * splits, kThreads, shared_bytes, stream>>>(args, ws, splits);
+    sample_rows_kernel<T, kResident><<<args.rows * splits, kThreads, shared_bytes, stream>>>(args, ws, splits);
     return cudaGetLastError();
 }
 
@@ -1073,9 +1096,15 @@ cudaError_t launch_sample_rows(const SampleArgs& args, const Workspace& ws, uint
 {
     if (args.rows == 0)
         return cudaSuccess;
+    if (args.large_top_k)
+    {
+        if (args.dtype == MOE_DTYPE_F32)
+            return launch_typed<float, 4>(args, ws, splits, stream);
+        return launch_typed<__nv_bfloat16, 4>(args, ws, splits, stream);
+    }
     if (args.dtype == MOE_DTYPE_F32)
-        return launch_typed<float>(args, ws, splits, stream);
-    return launch_typed<__nv_bfloat16>(args, ws, splits, stream);
+        return launch_typed<float, 6>(args, ws, splits, stream);
+    return launch_typed<__nv_bfloat16, 6>(args, ws, splits, stream);
 }
 
 cudaError_t launch_merge_candidates(const uint64_t* gathered, uint32_t shards, uint32_t rows, uint32_t top_k, const moe_row_params* params,
@@ -1085,7 +1114,7 @@ cudaError_t launch_merge_candidates(const uint64_t* gathered, uint32_t shards, u
     if (rows == 0)
         return cudaSuccess;
     static bool configured = false;
-    const size_t shared_bytes = sizeof(RowShared);
+    const size_t shared_bytes = shared_bytes_for(kCapLarge);
     if (!configured)
     {
         cudaError_t status = cudaFuncSetAttribute(merge_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared_bytes));
@@ -1107,15 +1136,15 @@ cudaError_t launch_merge_candidates(const uint64_t* gathered, uint32_t shards, u
     return cudaGetLastError();
 }
 
-uint32_t choose_splits(uint32_t rows, uint32_t vocab, int dtype, int sm_count, uint32_t slice_slots)
+uint32_t choose_splits(uint32_t rows, uint32_t vocab, int dtype, int sm_count, uint32_t slice_slots, bool large_top_k)
 {
     // Cut rows into slices only while all CTAs of the launch stay resident at
-    // once (4 per SM): a single wave has no ragged second wave, and the fixed
+    // once (6 per SM, 4 with the large record buffer): a single wave has no ragged second wave, and the fixed
     // per-slice work (threshold estimate, select, publication) stays small
     // next to a slice of at least 64 KiB.
     const uint64_t row_bytes = static_cast<uint64_t>(vocab) * (dtype == MOE_DTYPE_F32 ? 4u : 2u);
     const uint64_t by_size = row_bytes / (64u * 1024u);
-    const uint64_t resident = static_cast<uint64_t>(sm_count) * 4u;
+    const uint64_t resident = static_cast<uint64_t>(sm_count) * (large_top_k ? 4u : 6u);
     uint32_t splits = 1;
     while (splits < 8u && static_cast<uint64_t>(rows) * splits * 2u <= resident && splits * 2u <= by_size &&
            static_cast<uint64_t>(rows) * splits * 2u <= slice_slots)

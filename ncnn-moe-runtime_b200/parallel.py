@@ -41,6 +41,8 @@ def all_gather_candidates(local_candidates, group=None):
     import torch.distributed as dist
 
     world = dist.get_world_size(group)
-    gathered = torch.empty((world,) + tuple(local_candidates.shape), dtype=local_candidates.dtype, device=local_candidates.device)
+    rows = local_candidates.shape[0]
+    # concatenated along dim 0 (the form every backend accepts), then viewed per rank
+    gathered = torch.empty((world * rows,) + tuple(local_candidates.shape[1:]), dtype=local_candidates.dtype, device=local_candidates.device)
     dist.all_gather_into_tensor(gathered, local_candidates.contiguous(), group=group)
-    return gathered
+    return gathered.view((world, rows) + tuple(local_candidates.shape[1:]))
