@@ -118,6 +118,14 @@ __device__ __forceinline__ float live_threshold(uint32_t maxkey, float temperatu
     return __fsub_rn(__fsub_rn(peak_logit, __fmul_rn(18.2f, temperature)), __fmul_rn(9.5367431640625e-07f, fabsf(peak_logit)));
 }
 
+// max of two packed bf16 pairs; a NaN operand is ignored, exactly like fmaxf
+__device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b)
+{
+    uint32_t r;
+    asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
 template<typename T>
 struct Unpack;
 
@@ -159,13 +167,7 @@ struct Unpack<__nv_bfloat16>
     }
     __device__ static __forceinline__ float maximum(const uint4& v)
     {
-        // packed bf16 max ignores NaN operands exactly like fmaxf
-        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
-        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
-        const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(&v.z);
-        const __nv_bfloat162 d = *reinterpret_cast<const __nv_bfloat162*>(&v.w);
-        const __nv_bfloat162 m = __hmax2(__hmax2(a, b), __hmax2(c, d));
-        const uint32_t bits = *reinterpret_cast<const uint32_t*>(&m);
+        const uint32_t bits = max_bf16x2(max_bf16x2(v.x, v.y), max_bf16x2(v.z, v.w));
         return fmaxf(__uint_as_float(bits << 16), __uint_as_float(bits & 0xFFFF0000u));
     }
     __device__ static __forceinline__ uint4 nan_vector()
@@ -219,12 +221,9 @@ struct Wide<__nv_bfloat16>
     }
     __device__ static __forceinline__ float maximum(const Vec32& v)
     {
-        // packed bf16 max ignores NaN operands exactly like fmaxf
-        __nv_bfloat162 m = *reinterpret_cast<const __nv_bfloat162*>(&v.w[0]);
-#pragma unroll
-        for (int i = 1; i < 8; ++i)
-            m = __hmax2(m, *reinterpret_cast<const __nv_bfloat162*>(&v.w[i]));
-        const uint32_t bits = *reinterpret_cast<const uint32_t*>(&m);
+        const uint32_t a = max_bf16x2(max_bf16x2(v.w[0], v.w[1]), max_bf16x2(v.w[2], v.w[3]));
+        const uint32_t b = max_bf16x2(max_bf16x2(v.w[4], v.w[5]), max_bf16x2(v.w[6], v.w[7]));
+        const uint32_t bits = max_bf16x2(a, b);
         return fmaxf(__uint_as_float(bits << 16), __uint_as_float(bits & 0xFFFF0000u));
     }
     __device__ static __forceinline__ Vec32 nan_vector()
@@ -677,31 +676,18 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
     }
 }
 
-// Brings the buffer down to what the row can still need — the k best records
-// (Top-K, greedy) or the records live against the buffer's maximum — and, when
-// that is at most a block's worth, leaves it sorted in rank order.
-__device__ __forceinline__ void reduce_buffer(Ctx& c)
+// Brings the buffer down to what the row can still need: the k best records
+// (Top-K, greedy) or the records live against the buffer's maximum.  With
+// `sort` the survivors are also put in rank order when they fit one block-wide
+// counting sort; finish_row_block sorts larger sets itself.
+__device__ __forceinline__ void reduce_buffer(Ctx& c, bool sort)
 {
     RowShared& s = c.s;
     c.sorted = false;
     if (c.aborted)
         return;
-    const uint32_t n = s.count;
-    if (c.mode != kLive && n <= kThreads)
-    {
-        // sort first, then the k best are simply the front of the buffer
-        block_rank_sort_descending<kThreads>(c.rec, n);
-        if (n > c.k)
-        {
-            if (threadIdx.x == 0)
-                s.count = c.k;
-            __syncthreads();
-        }
-        c.sorted = true;
-        return;
-    }
     flush_buffer(c);
-    if (!c.aborted && s.count <= kThreads)
+    if (sort && !c.aborted && s.count <= kThreads)
     {
         block_rank_sort_descending<kThreads>(c.rec, s.count);
         c.sorted = true;
@@ -913,7 +899,7 @@ __global__ void __launch_bounds__(kThreads, kResident) sample_rows_kernel(const 
     if (splits > 1)
     {
         // ---- publish this slice, count in, and leave unless last -------------------
-        reduce_buffer(c); // Top-K: the slice's k best; live: re-tested against the slice maximum
+        reduce_buffer(c, false); // Top-K: the slice's k best; live: re-tested against the slice maximum
         const uint32_t mine = s.count;
         const bool publishable = !c.aborted && mine <= kSliceCap;
         uint64_t* slot_records = ws.slice_records + static_cast<size_t>(blockIdx.x) * kSliceCap;
@@ -978,7 +964,7 @@ __global__ void __launch_bounds__(kThreads, kResident) sample_rows_kernel(const 
         }
         MOE_PHASE_MARK(5);
     }
-    reduce_buffer(c); // the row's exact k best / exact live set
+    reduce_buffer(c, true); // the row's exact k best / exact live set, in rank order
     MOE_PHASE_MARK(6);
     finish_row_block(a, s, c, p, row, ws.exact_count, ws.exact_rows);
     MOE_PHASE_MARK(7);

@@ -1,0 +1,32 @@
+"""Builds the C++20 adapter test against the C-ABI library; runs it on a GPU."""
+import shutil
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+SOURCE = ROOT / "tests" / "cpp" / "adapter_test.cpp"
+
+
+def build(pkg, target: Path) -> None:
+    pkg.library()  # the shared library must exist
+    library_dir = pkg.LIBRARY_PATH.parent
+    compiler = shutil.which("g++")
+    if compiler is None:
+        pytest.skip("no g++ on this machine")
+    subprocess.run([compiler, "-std=c++20", "-O1", "-Wall", "-Wextra", str(SOURCE), "-o", str(target), f"-L{library_dir}",
+                    "-lmoe_b200_sampler", f"-Wl,-rpath,{library_dir}"], check=True)
+
+
+def test_adapter_compiles_and_links(pkg, tmp_path):
+    build(pkg, tmp_path / "adapter_test")
+
+
+@pytest.mark.gpu
+def test_adapter_runs_like_the_reference_tests(pkg, torch_cuda, tmp_path):
+    target = tmp_path / "adapter_test"
+    build(pkg, target)
+    result = subprocess.run([str(target)], capture_output=True, text=True, timeout=300)
+    assert result.returncode == 0, result.stdout + result.stderr
+    assert "all adapter tests passed" in result.stdout
