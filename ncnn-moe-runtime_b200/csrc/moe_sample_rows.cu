@@ -49,7 +49,36 @@ extern "C" void moe_debug_phase_cycles(unsigned long long* out, int reset)
         }                                                                         \
     } while (0)
 #define MOE_PHASE_BEGIN() long long moe_phase_start = clock64()
+// per-CTA wall-clock trace: SM id, start, end of stream, end (globaltimer ns)
+__device__ unsigned long long g_cta_trace[4 * 16384];
+extern "C" void moe_debug_cta_trace(unsigned long long* out, int entries)
+{
+    cudaMemcpyFromSymbol(out, g_cta_trace, sizeof(unsigned long long) * 4 * entries);
+}
+__device__ __forceinline__ unsigned long long moe_globaltimer()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define MOE_TRACE(slot)                                                                  \
+    do                                                                                   \
+    {                                                                                    \
+        if (threadIdx.x == 0 && blockIdx.x < 16384)                                      \
+        {                                                                                \
+            if ((slot) == 0)                                                             \
+            {                                                                            \
+                unsigned smid;                                                           \
+                asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));                        \
+                g_cta_trace[4 * blockIdx.x + 0] = smid;                                  \
+                g_cta_trace[4 * blockIdx.x + 1] = moe_globaltimer();                     \
+            }                                                                            \
+            else                                                                         \
+                g_cta_trace[4 * blockIdx.x + (slot) + 1] = moe_globaltimer();            \
+        }                                                                                \
+    } while (0)
 #else
+#define MOE_TRACE(slot) do {} while (0)
 #define MOE_PHASE_MARK(slot) do {} while (0)
 #define MOE_PHASE_BEGIN() do {} while (0)
 #endif
@@ -62,7 +91,8 @@ constexpr int kThreads = 256;
 constexpr int kCapSmall = 2048;           // records a CTA can hold: batches whose Top-K sizes are small (6 CTAs per SM)
 constexpr int kCapLarge = 4096;           // ... and batches with top_k up to MOE_SAMPLER_TOPK_FAST_MAX (4 CTAs per SM)
 constexpr int kItems = kCapLarge / kThreads; // most records per thread in block-wide passes
-constexpr int kGroupsPerTile = 4;         // 128-bit loads in flight per thread
+constexpr int kGroupsPerTile = 4;         // vector loads in flight per thread
+constexpr uint32_t kWarpHitCap = 128;      // vectors a warp of the barrier-free loop can queue per slice
 // live mode: the buffer is re-tested against the running maximum at half fill;
 // more survivors than live_abort(cap) send the row to the exact kernel
 __host__ __device__ constexpr uint32_t live_abort(uint32_t cap)
@@ -89,6 +119,10 @@ struct __align__(16) RowShared
     uint32_t maxkey;
     uint32_t abort_flag;
     uint32_t overflow;
+    // barrier-free loop: per warp, the indices of the 32-byte vectors whose
+    // maximum reached the threshold; each warp unpacks its own queue after its
+    // part of the stream, outside the hot loop
+    uint32_t hit_queue[kThreads / 32][kWarpHitCap];
 };
 
 struct Ctx
@@ -495,7 +529,11 @@ __device__ __forceinline__ void offer_values(RowShared& s, uint64_t* rec, uint32
 // threshold from the per-thread maxima (their r-th largest, r chosen so that a
 // few times k logits of the whole slice are expected above it; live mode uses
 // the tile maximum), then every other tile is filtered against that threshold
-// with one packed max and one compare per 128-bit load and no block barrier.
+// with one packed max, one compare and one warp vote per 256-bit load and no
+// block barrier.  A vector that reaches the threshold only has its index put
+// on its warp's queue (slot = running count + rank among the voting lanes: no
+// atomics, no divergence); each warp re-reads and unpacks its queued vectors
+// once its part of the stream is over.
 // All logits >= threshold end up in the buffer, so if at least k were found the
 // slice's k best are among them regardless of the order of the logits.  Returns
 // false (buffer reset) when fewer than k were found or the buffer overflowed;
@@ -556,6 +594,8 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
     }
     uint32_t* lists = s.sel.hist; // kThreads entries, untouched while streaming
     lists[tid] = sorted_key;
+    uint32_t* const my_queue = s.hit_queue[warp];
+    const unsigned lanes_below = (1u << lane) - 1u;
 
     for (int attempt = 0;; ++attempt)
     {
@@ -603,6 +643,7 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
         }
 
         uint32_t g = group_begin;
+        uint32_t my_hits = 0;
         if (attempt > 0)
         {
 #pragma unroll
@@ -614,11 +655,17 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
 #pragma unroll
             for (int j = 0; j < kGroupsPerTile; ++j)
             {
-                if (W::maximum(v[j]) >= tau)
+                const float best = W::maximum(v[j]);
+                const bool hit = best >= tau;
+                const unsigned voters = __ballot_sync(kFullMask, hit);
+                if (voters != 0)
                 {
-                    float x[W::kWidth];
-                    W::values(v[j], x);
-                    offer_values<W::kWidth>(s, rec, cap, mode, tau, x, head + ((g + j) * kThreads + tid) * W::kWidth);
+                    const uint32_t slot = my_hits + __popc(voters & lanes_below);
+                    if (hit && slot < kWarpHitCap)
+                        my_queue[slot] = (g + j) * kThreads + tid;
+                    my_hits += __popc(voters);
+                    if (mode == kLive && hit)
+                        atomicMax(&s.maxkey, ordered_key(best));
                 }
             }
             g += kGroupsPerTile;
@@ -635,11 +682,17 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
         {
             const uint32_t vi = g * kThreads + tid;
             const Vec32 one = (vi < vectors) ? load_stream_32(vector_base + vi) : W::nan_vector();
-            if (W::maximum(one) >= tau)
+            const float best = W::maximum(one);
+            const bool hit = best >= tau;
+            const unsigned voters = __ballot_sync(kFullMask, hit);
+            if (voters != 0)
             {
-                float x[W::kWidth];
-                W::values(one, x);
-                offer_values<W::kWidth>(s, rec, cap, mode, tau, x, head + vi * W::kWidth);
+                const uint32_t slot = my_hits + __popc(voters & lanes_below);
+                if (hit && slot < kWarpHitCap)
+                    my_queue[slot] = vi;
+                my_hits += __popc(voters);
+                if (mode == kLive && hit)
+                    atomicMax(&s.maxkey, ordered_key(best));
             }
         }
         // logits before / after the 32-byte aligned body of the row
@@ -652,6 +705,20 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
         {
             const float x[1] = {LogitTraits<T>::widen(row_pointer, tail_begin + tid)};
             offer_values<1>(s, rec, cap, mode, tau, x, tail_begin + tid);
+        }
+        // this warp's queued vectors: a re-read of 32 bytes each, unpacked against the latest threshold
+        __syncwarp();
+        if (mode == kLive)
+            tau = fmaxf(tau, live_threshold(*reinterpret_cast<volatile uint32_t*>(&s.maxkey), temperature));
+        if (my_hits > kWarpHitCap)
+            s.overflow = 1u;
+        for (uint32_t i = lane; i < min(my_hits, kWarpHitCap); i += 32)
+        {
+            const uint32_t vi = my_queue[i];
+            const Vec32 again = load_stream_32(vector_base + vi);
+            float x[W::kWidth];
+            W::values(again, x);
+            offer_values<W::kWidth>(s, rec, cap, mode, tau, x, head + vi * W::kWidth);
         }
         __syncthreads();
         const uint32_t found = s.count;
@@ -677,15 +744,29 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
 }
 
 // Brings the buffer down to what the row can still need: the k best records
-// (Top-K, greedy) or the records live against the buffer's maximum.  With
-// `sort` the survivors are also put in rank order when they fit one block-wide
-// counting sort; finish_row_block sorts larger sets itself.
+// (Top-K, greedy) or the records live against the buffer's maximum.  A Top-K
+// buffer of at most one block's worth is simply sorted (the k best are then
+// its front); larger ones go through the radix select first.  With `sort` the
+// result is left in rank order whenever it fits the block-wide sort.
 __device__ __forceinline__ void reduce_buffer(Ctx& c, bool sort)
 {
     RowShared& s = c.s;
     c.sorted = false;
     if (c.aborted)
         return;
+    if (c.mode != kLive && s.count <= kThreads)
+    {
+        const uint32_t n = s.count;
+        block_rank_sort_descending<kThreads>(c.rec, n);
+        if (n > c.k)
+        {
+            if (threadIdx.x == 0)
+                s.count = c.k;
+            __syncthreads();
+        }
+        c.sorted = true;
+        return;
+    }
     flush_buffer(c);
     if (sort && !c.aborted && s.count <= kThreads)
     {
@@ -817,6 +898,7 @@ __global__ void __launch_bounds__(kThreads, kResident) sample_rows_kernel(const 
         p = a.params[row];
     }
     MOE_PHASE_BEGIN();
+    MOE_TRACE(0);
     const int invalid = validate_row(p);
     if (invalid != MOE_ROW_OK)
     {
@@ -880,10 +962,25 @@ __global__ void __launch_bounds__(kThreads, kResident) sample_rows_kernel(const 
     const uint32_t group_begin = static_cast<uint32_t>(static_cast<uint64_t>(rank) * groups / splits);
     const uint32_t group_end = static_cast<uint32_t>(static_cast<uint64_t>(rank + 1) * groups / splits);
 
+    // Ask L2 for the first tiles of the slice now (one bulk prefetch, no
+    // registers, nothing to wait on): DRAM stays busy while the threshold of the
+    // first tile is being worked out.
+    if (tid == 0)
+    {
+        const uint32_t full_end = min(group_end, vectors / kThreads);
+        if (group_begin < full_end)
+        {
+            const uint32_t ahead = min(full_end - group_begin, 2u * kGroupsPerTile);
+            const Vec32* first = reinterpret_cast<const Vec32*>(row_pointer + head) + static_cast<size_t>(group_begin) * kThreads;
+            const uint32_t bytes = ahead * kThreads * static_cast<uint32_t>(sizeof(Vec32));
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(first), "r"(bytes) : "memory");
+        }
+    }
     MOE_PHASE_MARK(0);
     const bool streamed = stream_slice_fast<T>(s, c.rec, c.cap, c.mode, c.k, p.temperature, row_pointer, vocab, head, vectors, tail_begin, group_begin,
                                                group_end, rank == 0, rank == splits - 1);
     MOE_PHASE_MARK(1);
+    MOE_TRACE(1);
 #ifdef MOE_PHASE_TIMERS
     if (tid == 0)
     {
@@ -913,13 +1010,18 @@ __global__ void __launch_bounds__(kThreads, kResident) sample_rows_kernel(const 
             slot_header[1] = publishable ? 0u : 1u; // the row needs the exact kernel
             slot_header[2] = s.maxkey;
         }
-        __threadfence();
+        // one release for the whole CTA: the barrier orders every thread's stores
+        // before thread 0's fence, which makes them visible before the arrival count
         __syncthreads();
         if (tid == 0)
+        {
+            __threadfence();
             s.sel.bucket = (atomicAdd(&ws.row_arrivals[row], 1u) == splits - 1) ? 1u : 0u;
+        }
         __syncthreads();
         const bool last = s.sel.bucket != 0;
         MOE_PHASE_MARK(3);
+        MOE_TRACE(2);
         if (!last)
             return;
         __threadfence();
@@ -968,6 +1070,7 @@ __global__ void __launch_bounds__(kThreads, kResident) sample_rows_kernel(const 
     MOE_PHASE_MARK(6);
     finish_row_block(a, s, c, p, row, ws.exact_count, ws.exact_rows);
     MOE_PHASE_MARK(7);
+    MOE_TRACE(2);
 }
 
 // Vocabulary-sharded sampling, second step: after the caller's all-gather each

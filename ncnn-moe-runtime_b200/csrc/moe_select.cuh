@@ -288,30 +288,67 @@ __device__ __noinline__ void block_sort_descending(uint64_t* records, uint32_t p
     }
 }
 
-// Sorts records[0..n) descending for n <= kThreads by counting, for every
-// record, the records that precede it (records are unique, so ranks are too).
-// Two barriers and no atomics: the cheapest order for the few hundred survivors
-// a slice or a row usually has.  Ends with a barrier.
+// Sorts records[0..n) descending for n <= kThreads (kThreads <= 256... any
+// multiple of 32).  Each warp sorts its 32 records in registers with a shuffle
+// network; a record's final position is its position in its own run plus, for
+// every other run, the number of larger records found by binary search.
+// Records are unique and 0 pads the tail, so positions are unique.  Three
+// barriers, no atomics: the cheapest order for the few hundred survivors a
+// slice or a row usually has.  Ends with a barrier.
 template<int kThreads>
 __device__ __noinline__ void block_rank_sort_descending(uint64_t* records, uint32_t n)
 {
     const uint32_t tid = threadIdx.x;
-    const uint64_t mine = (tid < n) ? records[tid] : 0ull;
-    uint32_t rank = 0;
-    const uint32_t pairs = n >> 1;
-    const ulonglong2* two = reinterpret_cast<const ulonglong2*>(records); // records are 16-byte aligned
-#pragma unroll 4
-    for (uint32_t i = 0; i < pairs; ++i)
+    const uint32_t lane = tid & 31u;
+    const uint32_t warp = tid >> 5;
+    const uint32_t runs = (n + 31u) >> 5;
+    uint64_t mine = (tid < n) ? records[tid] : 0ull;
+    if (warp < runs)
     {
-        const ulonglong2 both = two[i];
-        rank += (both.x > mine) ? 1u : 0u;
-        rank += (both.y > mine) ? 1u : 0u;
+#pragma unroll
+        for (uint32_t size = 2; size <= 32; size <<= 1)
+        {
+#pragma unroll
+            for (uint32_t stride = size >> 1; stride > 0; stride >>= 1)
+            {
+                const uint32_t other_lo = __shfl_xor_sync(kFullMask, static_cast<uint32_t>(mine), stride);
+                const uint32_t other_hi = __shfl_xor_sync(kFullMask, static_cast<uint32_t>(mine >> 32), stride);
+                const uint64_t other = (static_cast<uint64_t>(other_hi) << 32) | other_lo;
+                const bool descending = (lane & size) == 0;
+                const bool lower_lane = (lane & stride) == 0;
+                const bool take_max = (descending == lower_lane);
+                mine = ((mine > other) == take_max) ? mine : other;
+            }
+        }
+        records[tid] = mine; // run `warp`, descending, zeros last
     }
-    if (n & 1u)
-        rank += (records[n - 1] > mine) ? 1u : 0u;
     __syncthreads();
-    if (tid < n)
-        records[rank] = mine;
+    uint32_t position = lane;
+    if (warp < runs && mine != 0ull)
+    {
+        for (uint32_t w = 0; w < runs; ++w)
+        {
+            if (w == warp)
+                continue;
+            const uint64_t* run = records + w * 32u;
+            uint32_t lo = 0, hi = 32;
+#pragma unroll
+            for (int step = 0; step < 5; ++step)
+            {
+                const uint32_t mid = (lo + hi) >> 1;
+                if (run[mid] > mine)
+                    lo = mid + 1;
+                else
+                    hi = mid;
+            }
+            if (lo < 32 && run[lo] > mine)
+                ++lo;
+            position += lo;
+        }
+    }
+    __syncthreads();
+    if (warp < runs && mine != 0ull)
+        records[position] = mine;
     __syncthreads();
 }
 
