@@ -644,6 +644,7 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
 
         uint32_t g = group_begin;
         uint32_t my_hits = 0;
+        uint32_t seen_max = threshold_key; // live mode: the largest key this warp knows of
         if (attempt > 0)
         {
 #pragma unroll
@@ -664,7 +665,7 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
                     if (hit && slot < kWarpHitCap)
                         my_queue[slot] = (g + j) * kThreads + tid;
                     my_hits += __popc(voters);
-                    if (mode == kLive && hit)
+                    if (mode == kLive && hit && ordered_key(best) > seen_max)
                         atomicMax(&s.maxkey, ordered_key(best));
                 }
             }
@@ -675,7 +676,10 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
             for (int j = 0; j < kGroupsPerTile; ++j)
                 v[j] = load_stream_32(vector_base + (g + j) * kThreads + tid);
             if (mode == kLive)
-                tau = fmaxf(tau, live_threshold(*reinterpret_cast<volatile uint32_t*>(&s.maxkey), temperature));
+            {
+                seen_max = *reinterpret_cast<volatile uint32_t*>(&s.maxkey);
+                tau = fmaxf(tau, live_threshold(seen_max, temperature));
+            }
         }
         // full groups that do not fill a tile, then the ragged last group
         for (; g < group_end; ++g)
@@ -691,7 +695,7 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
                 if (hit && slot < kWarpHitCap)
                     my_queue[slot] = vi;
                 my_hits += __popc(voters);
-                if (mode == kLive && hit)
+                if (mode == kLive && hit && ordered_key(best) > seen_max)
                     atomicMax(&s.maxkey, ordered_key(best));
             }
         }
@@ -754,14 +758,34 @@ __device__ __forceinline__ void reduce_buffer(Ctx& c, bool sort)
     c.sorted = false;
     if (c.aborted)
         return;
-    if (c.mode != kLive && s.count <= kThreads)
+    const uint32_t n = s.count;
+    if (n <= kThreads)
     {
-        const uint32_t n = s.count;
+        // One record per thread.  Live mode first blanks the records that fell
+        // out of the live window of the final maximum (0 sorts last and is not
+        // counted); then one sort puts the survivors in rank order.
+        uint32_t kept = n;
+        if (c.mode == kLive)
+        {
+            const uint32_t tid = threadIdx.x;
+            const float peak = __fdiv_rn(key_to_float(s.maxkey), c.temperature);
+            bool keep = false;
+            if (tid < n)
+            {
+                const float offset = scaled_offset(key_to_float(record_key(c.rec[tid])), c.temperature, peak);
+                keep = !(offset < kDeadOffset); // keeps NaN offsets: the epilogue reports them
+                if (!keep)
+                    c.rec[tid] = 0ull;
+            }
+            kept = static_cast<uint32_t>(__syncthreads_count(keep));
+        }
         block_rank_sort_descending<kThreads>(c.rec, n);
-        if (n > c.k)
+        if (c.mode != kLive)
+            kept = min(n, c.k);
+        if (kept != n)
         {
             if (threadIdx.x == 0)
-                s.count = c.k;
+                s.count = kept;
             __syncthreads();
         }
         c.sorted = true;
@@ -962,20 +986,6 @@ __global__ void __launch_bounds__(kThreads, kResident) sample_rows_kernel(const 
     const uint32_t group_begin = static_cast<uint32_t>(static_cast<uint64_t>(rank) * groups / splits);
     const uint32_t group_end = static_cast<uint32_t>(static_cast<uint64_t>(rank + 1) * groups / splits);
 
-    // Ask L2 for the first tiles of the slice now (one bulk prefetch, no
-    // registers, nothing to wait on): DRAM stays busy while the threshold of the
-    // first tile is being worked out.
-    if (tid == 0)
-    {
-        const uint32_t full_end = min(group_end, vectors / kThreads);
-        if (group_begin < full_end)
-        {
-            const uint32_t ahead = min(full_end - group_begin, 2u * kGroupsPerTile);
-            const Vec32* first = reinterpret_cast<const Vec32*>(row_pointer + head) + static_cast<size_t>(group_begin) * kThreads;
-            const uint32_t bytes = ahead * kThreads * static_cast<uint32_t>(sizeof(Vec32));
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(first), "r"(bytes) : "memory");
-        }
-    }
     MOE_PHASE_MARK(0);
     const bool streamed = stream_slice_fast<T>(s, c.rec, c.cap, c.mode, c.k, p.temperature, row_pointer, vocab, head, vectors, tail_begin, group_begin,
                                                group_end, rank == 0, rank == splits - 1);
