@@ -206,6 +206,39 @@ int moe_router_dispatch_host(moe_sampler* sampler, const float* router_logits, u
                              const moe_router_options* options_with_host_pointers, uint32_t* expert_offsets,
                              uint32_t* route_token, uint32_t* route_rank, float* route_weight, int32_t* plan_status);
 
+/* Router dispatch for hosts that must not allocate device memory when they
+ * route: engines whose planner or pool owns every byte of the GPU from start-up,
+ * so that a late cudaMalloc fails or falsifies the planner's books, and decode
+ * loops that cannot take the device-wide synchronisation an allocation may
+ * cause.  It has no counterpart in the reference (whose dispatcher runs on the
+ * host); it is moe_router_dispatch with its scratch held in a fixed array inside
+ * the library's device image instead of grown on demand, so it needs no handle
+ * and calls no allocator of any kind.
+ *
+ * Limits: token_count * top_k <= MOE_ROUTER_STATIC_MAX_ROUTES and expert_count
+ * <= MOE_ROUTER_STATIC_MAX_EXPERTS; anything larger is refused with
+ * MOE_STATUS_INVALID_ARGUMENT and a message in error_text.  The array costs
+ * MOE_ROUTER_STATIC_SCRATCH_BYTES on every GPU that loads the library, until
+ * the process ends.
+ *
+ * It works on the CURRENT device.  The first call on a device looks the
+ * array's address up (cudaGetSymbolAddress); make that first call during
+ * start-up, before any stream capture begins.  All calls share the one array:
+ * each call resets the counters it needs, but two calls that overlap on the GPU
+ * (different streams, or several host threads) race on it — keep them
+ * stream-ordered.
+ *
+ * All pointers are device pointers (options->selection_bias /
+ * explicit_expert_ids too); outputs are as for moe_router_dispatch.
+ * error_text may be NULL. */
+#define MOE_ROUTER_STATIC_MAX_ROUTES 65536u
+#define MOE_ROUTER_STATIC_MAX_EXPERTS 4096u
+#define MOE_ROUTER_STATIC_SCRATCH_BYTES (544u * 1024u)
+int moe_router_dispatch_static(void* stream, const float* router_logits, uint32_t token_count,
+                               const moe_router_options* options, uint32_t* expert_offsets, uint32_t* route_token,
+                               uint32_t* route_rank, float* route_weight, int32_t* plan_status, char* error_text,
+                               size_t error_capacity);
+
 /* Replaces gather_tokens (src/engine/cpu_executor.cpp:635-642): copies
  * hidden[route_token[i], :] to gathered[i, :] for every route.  All device. */
 int moe_regroup_gather(moe_sampler* sampler, void* stream, const float* hidden, uint32_t token_count, uint32_t columns,

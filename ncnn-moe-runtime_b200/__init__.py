@@ -44,6 +44,7 @@ EXPORTED_SYMBOLS = [
     "moe_philox_uniform", "moe_host_alloc", "moe_host_free", "moe_sample_batch", "moe_sample_batch_host",
     "moe_sample_local_candidates", "moe_sample_merge_candidates", "moe_router_dispatch", "moe_router_status_message",
     "moe_router_status_error_code", "moe_router_check_options", "moe_router_dispatch_host", "moe_regroup_gather",
+    "moe_router_dispatch_static",
 ]
 
 _library = None
@@ -89,6 +90,7 @@ def library() -> C.CDLL:
     lib.moe_router_status_error_code.argtypes = [C.c_int]
     lib.moe_router_check_options.argtypes = [u32, C.POINTER(RouterOptions)]
     lib.moe_regroup_gather.argtypes = [vp, vp, vp, u32, u32, vp, u32, vp]
+    lib.moe_router_dispatch_static.argtypes = [vp, vp, u32, C.POINTER(RouterOptions), vp, vp, vp, vp, vp, C.c_char_p, sz]
     _library = lib
     return lib
 

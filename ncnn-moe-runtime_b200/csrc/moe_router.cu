@@ -12,6 +12,8 @@
 // Kernel 3 (one CTA per expert): stable compaction of that expert's routes in
 //   (token, rank) order, which is the order the reference appends them in.
 
+#include <cstdio>
+
 #include "moe_common.cuh"
 #include "moe_internal.h"
 
@@ -351,4 +353,140 @@ cudaError_t launch_regroup_gather(const float* hidden, uint32_t columns, const u
     return cudaGetLastError();
 }
 
+
+// ---- router dispatch without any allocation ------------------------------------
+//
+// Some hosts of this library may not call cudaMalloc at the point where they
+// route tokens: a serving engine that has handed every byte of device memory
+// to its own planner or pool up front (so a late allocation either fails or
+// breaks the planner's accounting), or a decode loop that cannot afford the
+// device-wide synchronisation an allocation may imply.  moe_router_dispatch
+// grows its scratch on demand and so does not suit them.  This variant keeps
+// the scratch the three router kernels need — the per-route (expert, weight)
+// pairs, the per-expert counters and the error word — in one fixed array that
+// lives in the library's device image.  Every GPU that loads the library
+// carries these MOE_ROUTER_STATIC_SCRATCH_BYTES until the process exits.
+
+namespace {
+
+struct StaticRouterScratch
+{
+    unsigned long long error_word;
+    uint32_t expert_counts[MOE_ROUTER_STATIC_MAX_EXPERTS];
+    uint32_t selected_expert[MOE_ROUTER_STATIC_MAX_ROUTES];
+    float selected_weight[MOE_ROUTER_STATIC_MAX_ROUTES];
+};
+static_assert(sizeof(StaticRouterScratch) <= MOE_ROUTER_STATIC_SCRATCH_BYTES, "scratch layout outgrew the documented size");
+
+// Device storage.  In host code this name is only a handle for the runtime's
+// symbol lookup, never a pointer a kernel may be given.
+static __device__ __align__(256) unsigned char g_router_static_scratch[MOE_ROUTER_STATIC_SCRATCH_BYTES];
+
+constexpr int kStaticMaxDevices = 64;
+// Device address of the array, looked up once per device ordinal.
+void* g_router_static_address[kStaticMaxDevices] = {};
+
+// The array keeps whatever the previous call left in it: counters and the
+// error word must be back at their start values before the select kernel runs.
+__global__ void router_static_reset_kernel(StaticRouterScratch* scratch, uint32_t experts)
+{
+    for (uint32_t e = blockIdx.x * blockDim.x + threadIdx.x; e < experts; e += gridDim.x * blockDim.x)
+        scratch->expert_counts[e] = 0;
+    if (blockIdx.x == 0 && threadIdx.x == 0)
+        scratch->error_word = ~0ull;
+}
+
+void describe(char* text, size_t capacity, const char* message)
+{
+    if (text != nullptr && capacity > 0)
+        snprintf(text, capacity, "%s", message);
+}
+
+} // namespace
+
+} // namespace moe
+
+extern "C" int moe_router_dispatch_static(void* stream_handle, const float* router_logits, uint32_t token_count,
+                                          const moe_router_options* options, uint32_t* expert_offsets, uint32_t* route_token,
+                                          uint32_t* route_rank, float* route_weight, int32_t* plan_status, char* error_text,
+                                          size_t error_capacity)
+{
+    using namespace moe;
+    describe(error_text, error_capacity, "");
+    const int precheck = moe_router_check_options(token_count, options);
+    if (precheck != 0)
+    {
+        describe(error_text, error_capacity, moe_router_status_message(precheck));
+        return moe_router_status_error_code(precheck);
+    }
+    if (router_logits == nullptr || expert_offsets == nullptr || route_token == nullptr || route_rank == nullptr || route_weight == nullptr ||
+        plan_status == nullptr)
+    {
+        describe(error_text, error_capacity, "router buffers must not be null");
+        return MOE_STATUS_INVALID_ARGUMENT;
+    }
+    const uint64_t routes = static_cast<uint64_t>(token_count) * options->top_k;
+    if (routes > MOE_ROUTER_STATIC_MAX_ROUTES)
+    {
+        describe(error_text, error_capacity,
+                 "token_count * top_k exceeds MOE_ROUTER_STATIC_MAX_ROUTES, the fixed scratch of moe_router_dispatch_static; "
+                 "split the tokens over several calls or use moe_router_dispatch");
+        return MOE_STATUS_INVALID_ARGUMENT;
+    }
+    if (options->expert_count > MOE_ROUTER_STATIC_MAX_EXPERTS)
+    {
+        describe(error_text, error_capacity, "expert_count exceeds MOE_ROUTER_STATIC_MAX_EXPERTS, the fixed scratch of moe_router_dispatch_static");
+        return MOE_STATUS_INVALID_ARGUMENT;
+    }
+    int device = -1;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status != cudaSuccess || device < 0 || device >= kStaticMaxDevices)
+    {
+        describe(error_text, error_capacity, status != cudaSuccess ? cudaGetErrorString(status) : "device ordinal beyond the static table");
+        return MOE_STATUS_CUDA_ERROR;
+    }
+    if (g_router_static_address[device] == nullptr)
+    {
+        // first call on this device (it is the current one): resolve the array's device address
+        void* address = nullptr;
+        status = cudaGetSymbolAddress(&address, g_router_static_scratch);
+        if (status != cudaSuccess || address == nullptr)
+        {
+            describe(error_text, error_capacity, status != cudaSuccess ? cudaGetErrorString(status) : "symbol lookup returned no address");
+            return MOE_STATUS_CUDA_ERROR;
+        }
+        g_router_static_address[device] = address;
+    }
+    StaticRouterScratch* scratch = static_cast<StaticRouterScratch*>(g_router_static_address[device]);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+
+    const uint32_t experts = options->expert_count;
+    router_static_reset_kernel<<<(experts + 255) / 256, 256, 0, stream>>>(scratch, experts);
+    status = cudaGetLastError();
+    if (status != cudaSuccess)
+    {
+        describe(error_text, error_capacity, cudaGetErrorString(status));
+        return MOE_STATUS_CUDA_ERROR;
+    }
+    RouterArgs args = {};
+    args.logits = router_logits;
+    args.token_count = token_count;
+    args.options = *options;
+    args.expert_offsets = expert_offsets;
+    args.route_token = route_token;
+    args.route_rank = route_rank;
+    args.route_weight = route_weight;
+    args.plan_status = plan_status;
+    args.selected_expert = scratch->selected_expert; // address arithmetic on the device pointer only; nothing is read here
+    args.selected_weight = scratch->selected_weight;
+    status = launch_router_dispatch_kernels(args, scratch->expert_counts, &scratch->error_word, stream);
+    if (status != cudaSuccess)
+    {
+        describe(error_text, error_capacity, cudaGetErrorString(status));
+        return MOE_STATUS_CUDA_ERROR;
+    }
+    return MOE_STATUS_OK;
+}
+
+namespace moe {
 } // namespace moe
