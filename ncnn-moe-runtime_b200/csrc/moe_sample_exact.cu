@@ -7,8 +7,8 @@
 // cumulative, renormaliser and inverse CDF are all left-to-right fp32 sums in
 // that order (:92-101,119-134,434-440).  One CTA therefore builds the order of
 // all finite logits of the row with a stable least-significant-digit radix
-// sort in a per-CTA global scratch slot (L2 resident), and one warp replays the
-// sums over it (moe_epilogue.cuh).
+// sort in a per-CTA global scratch slot (L2 resident), and replays the sums over
+// it bit-exactly with a block-parallel scan (moe_seqscan.cuh).
 //
 // CTAs take rows round-robin from the hand-over list; nobody waits on another
 // CTA.  The last CTA to finish clears the list for the next call.
@@ -16,6 +16,35 @@
 #include "moe_common.cuh"
 #include "moe_epilogue.cuh"
 #include "moe_internal.h"
+#include "moe_seqscan.cuh"
+
+#ifdef MOE_PHASE_TIMERS
+// Debug builds only: cycles per phase of the exact kernel, summed over rows.
+__device__ unsigned long long g_exact_cycles[8];
+extern "C" void moe_debug_exact_cycles(unsigned long long* out, int reset)
+{
+    cudaMemcpyFromSymbol(out, g_exact_cycles, sizeof(unsigned long long) * 8);
+    if (reset)
+    {
+        unsigned long long zeros[8] = {};
+        cudaMemcpyToSymbol(g_exact_cycles, zeros, sizeof(zeros));
+    }
+}
+#define MOE_EXACT_MARK(slot)                                                                              \
+    do                                                                                                    \
+    {                                                                                                     \
+        if (threadIdx.x == 0)                                                                             \
+        {                                                                                                 \
+            const long long now = clock64();                                                              \
+            atomicAdd(&g_exact_cycles[slot], static_cast<unsigned long long>(now - exact_phase_start));   \
+            exact_phase_start = now;                                                                      \
+        }                                                                                                 \
+    } while (0)
+#define MOE_EXACT_BEGIN() long long exact_phase_start = clock64()
+#else
+#define MOE_EXACT_MARK(slot) do {} while (0)
+#define MOE_EXACT_BEGIN() do {} while (0)
+#endif
 
 namespace moe {
 
@@ -26,6 +55,8 @@ constexpr int kExactWarps = kExactThreads / 32;
 
 struct ExactShared
 {
+    SeqShared<1024> seq;
+    uint32_t first_fail; // Min-P: first rank whose probability is below the floor
     uint32_t warp_hist[kExactWarps][256];
     uint32_t digit_total[256];
     uint32_t warp_count[kExactWarps];
@@ -199,6 +230,85 @@ __device__ void radix_pass(const uint32_t* keys_in, const uint32_t* index_in, ui
     __syncthreads();
 }
 
+// The arithmetic tail of session.cpp:89-136,429-442 for a complete, sorted
+// candidate list of any length, by the whole block: per-candidate exp and
+// divisions are spread over the threads, the four running sums are replayed
+// bit-exactly by block_sequential_sum.  Same steps, same roundings and same
+// outcomes as finish_row_warp (which serves the short lists of the streaming
+// kernel); every thread returns the same result.
+__device__ RowOutcome finish_row_exact_block(const uint64_t* records, uint32_t count, float* work, float temperature, uint32_t top_k, float top_p,
+                                             float min_p, float uniform, ExactShared& sh)
+{
+    const uint32_t tid = threadIdx.x;
+    RowOutcome out{MOE_ROW_OK, -1, 0.0f, 0u, false};
+    if (count == 0)
+    {
+        out.status = MOE_ROW_NO_FINITE_LOGIT;
+        return out;
+    }
+    const uint32_t head_key = record_key(records[0]);
+    if (head_key >= kKeyPosInf || head_key <= kKeyNegInf)
+    {
+        out.status = MOE_ROW_NO_FINITE_LOGIT;
+        return out;
+    }
+    // every record here is finite (compact_finite dropped the rest), so Top-K only shortens the list
+    const uint32_t finite = (top_k > 0 && top_k <= count) ? top_k : count;
+
+    const float peak = __fdiv_rn(key_to_float(head_key), temperature);
+    for (uint32_t i = tid; i < finite; i += kExactThreads)
+        work[i] = exact_expf(scaled_offset(key_to_float(record_key(records[i])), temperature, peak));
+    __syncthreads();
+    const float total = block_sequential_sum<kExactThreads, 4>(work, finite, kSeqSumOnly, 0.0f, sh.seq).acc;
+    if (!(total - total == 0.0f) || total <= 0.0f)
+    {
+        out.status = MOE_ROW_INVALID_DISTRIBUTION;
+        return out;
+    }
+    for (uint32_t i = tid; i < finite; i += kExactThreads)
+        work[i] = __fdiv_rn(work[i], total);
+    if (tid == 0)
+        sh.first_fail = finite;
+    __syncthreads();
+    // Min-P: probabilities are non-increasing, so the survivors are a prefix
+    uint32_t allowed = finite;
+    if (min_p > 0.0f)
+    {
+        const float floor_probability = __fmul_rn(work[0], min_p);
+        uint32_t mine = finite;
+        for (uint32_t i = tid; i < finite; i += kExactThreads)
+            if (!(work[i] >= floor_probability))
+            {
+                mine = i;
+                break; // my indices ascend: the first failure is my smallest
+            }
+        if (mine < finite)
+            atomicMin(&sh.first_fail, mine);
+        __syncthreads();
+        allowed = sh.first_fail;
+        __syncthreads();
+    }
+    // Top-P: first prefix whose running sum reaches top_p
+    const SeqResult nucleus = block_sequential_sum<kExactThreads, 4>(work, allowed, kSeqReachBound, top_p, sh.seq);
+    const uint32_t kept = nucleus.taken;
+    const float kept_total = block_sequential_sum<kExactThreads, 4>(work, kept, kSeqSumOnly, 0.0f, sh.seq).acc;
+    if (kept == 1)
+    {
+        out.token = static_cast<int32_t>(record_index(records[0]));
+        out.probability = 1.0f;
+        return out;
+    }
+    out.flags |= MOE_ROW_FLAG_USED_UNIFORM;
+    for (uint32_t i = tid; i < kept; i += kExactThreads)
+        work[i] = __fdiv_rn(work[i], kept_total);
+    __syncthreads();
+    const SeqResult draw = block_sequential_sum<kExactThreads, 4>(work, kept, kSeqExceedBound, uniform, sh.seq);
+    const uint32_t chosen = draw.stopped ? draw.taken - 1 : kept - 1; // session.cpp:441-442: the last candidate if the sum never passes the uniform
+    out.token = static_cast<int32_t>(record_index(records[chosen]));
+    out.probability = work[chosen];
+    return out;
+}
+
 template<typename T>
 __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys, uint32_t* slot_index, uint32_t slot_stride, ExactShared& sh)
 {
@@ -214,8 +324,10 @@ __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys
     uint32_t* index[2] = {slot_keys + slot_stride, slot_keys + 3 * static_cast<size_t>(slot_stride)};
     (void)slot_index;
 
+    MOE_EXACT_BEGIN();
     const uint32_t n = compact_finite<T>(row_pointer, a.vocab, keys[0], index[0], sh);
     const bool has_pos_inf = sh.flag_pos_inf != 0;
+    MOE_EXACT_MARK(0);
 
     int source = 0;
     if (n > 1 && !has_pos_inf)
@@ -255,6 +367,7 @@ __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys
         }
     }
 
+    MOE_EXACT_MARK(1);
     // records of the sorted order go to the other pair, the floats of the
     // epilogue to this pair's key array (free once the records are built)
     uint64_t* records = reinterpret_cast<uint64_t*>(keys[1 - source]);
@@ -265,8 +378,8 @@ __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys
             records[i] = make_record(~keys[source][i], index[source][i]);
     }
     __syncthreads();
+    MOE_EXACT_MARK(2);
 
-    if (warp == 0)
     {
         RowOutcome out{MOE_ROW_OK, -1, 0.0f, 0u, false};
         if (has_pos_inf || n == 0)
@@ -276,9 +389,9 @@ __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys
         else
         {
             const float uniform = philox_uniform(p.seed, p.row_id, p.step + a.step_offset);
-            out = finish_row_warp(records, n, work, p.temperature, p.top_k, p.top_p, p.min_p, uniform, false);
+            out = finish_row_exact_block(records, n, work, p.temperature, p.top_k, p.top_p, p.min_p, uniform, sh);
         }
-        if (lane == 0)
+        if (tid == 0)
         {
             if (out.status == MOE_ROW_OK && is_stop_token(a.stop_offsets, a.stop_tokens, row, out.token))
                 out.flags |= MOE_ROW_FLAG_STOP_TOKEN;
@@ -291,6 +404,11 @@ __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys
         }
     }
     __syncthreads();
+    MOE_EXACT_MARK(3);
+#ifdef MOE_PHASE_TIMERS
+    if (threadIdx.x == 0)
+        atomicAdd(&g_exact_cycles[7], 1ull);
+#endif
 }
 
 template<typename T>
