@@ -207,12 +207,154 @@ def run_reference_arm(args):
     return 0
 
 
+
+def run_router_bench(args):
+    """Config 5b: router Top-8 with sigmoid scoring over 4096 tokens x 256 experts (one GPU).
+
+    Latency-bound (4 MiB in, 32768 routes out): reported as time and tokens/s, not as a roofline fraction."""
+    import torch
+    package = graft.load_package()
+    workloads = __import__(graft.PACKAGE_NAME + ".workloads", fromlist=["workloads"])
+    torch.cuda.set_device(0)
+    tokens, experts, top_k = 4096, 256, 8
+    logits_host, bias_host = workloads.config5b_router(tokens, experts)
+    sampler = package.Sampler(max_rows=1, max_vocab=1)
+    logits = [torch.from_numpy(np.roll(logits_host, shift, axis=0)).cuda() for shift in range(4)]
+    bias = torch.from_numpy(bias_host).cuda()
+    plan = sampler.router_dispatch(logits[0], top_k, score_function=package.ROUTER_SIGMOID, selection_bias=bias)
+    hidden = torch.randn(tokens, 4096, device="cuda")
+    torch.cuda.synchronize()
+
+    def step(i):
+        sampler.router_dispatch(logits[i % 4], top_k, score_function=package.ROUTER_SIGMOID, selection_bias=bias, out=plan)
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    chunk = min(args.steps, 64)
+    with torch.cuda.graph(graph):
+        for i in range(chunk):
+            step(i)
+    graph.replay()
+    torch.cuda.synchronize()
+    replays = max(1, args.steps // chunk)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(replays):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / (replays * chunk)
+    # regroup gather of the routed hidden rows (hidden size 4096 fp32): HBM-bound copy
+    gathered = sampler.regroup_gather(hidden, plan.route_token)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(50):
+        sampler.regroup_gather(hidden, plan.route_token)
+    stop.record()
+    torch.cuda.synchronize()
+    gather_ms = start.elapsed_time(stop) / 50
+    gather_bytes = 2 * gathered.numel() * 4
+    # reference dispatcher on the host cores
+    from oracle import oracle as oracle_module
+    oracle = oracle_module.best()
+    t0 = time.perf_counter()
+    want = oracle.expert_dispatch(logits_host, tokens, experts, top_k, score_function=1, selection_bias=bias_host)
+    cpu_s = time.perf_counter() - t0
+    got_tokens = plan.route_token.cpu().numpy().view(np.uint32)
+    step(0)
+    torch.cuda.synchronize()
+    peak, peak_source = measured_peak()
+    line = {"metric": "router tokens/s, stable Top-8 of 256 experts, sigmoid scoring, 4096 tokens", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": 1, "steps": replays * chunk, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "config 5b: 4096 tokens x 256 experts fp32 N(0,1) + bias N(0,0.1), sigmoid, top_k 8, renormalised", "kernels_per_step": 3},
+            "gpu_launches": 3 * replays * chunk,
+            "regroup_gather": {"ms": gather_ms, "achieved_gbs": gather_bytes / (gather_ms * 1e-3) / 1e9, "peak_gbs": peak, "frac": gather_bytes / (gather_ms * 1e-3) / 1e9 / peak,
+                               "shape": "32768 routes x 4096 fp32 columns"},
+            "cpu_baseline": {"value": tokens / cpu_s, "unit": "tokens/s", "cores": 1, "kind": oracle.kind, "sample": "the whole 4096-token call, single thread (the reference dispatcher is single-threaded)"},
+            "routes_equal_to_reference": bool(np.array_equal(plan.route_token.cpu().numpy().view(np.uint32), want["token"]) and got_tokens.size == want["token"].size)}
+    print(json.dumps(line), flush=True)
+    sampler.close()
+    return 0
+
+
+def run_vocab_sharded_bench(args):
+    """Config 5a across N GPUs: each rank owns a vocabulary slice, all-gathers k candidates per row, merges."""
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    package = graft.load_package()
+    workloads = __import__(graft.PACKAGE_NAME + ".workloads", fromlist=["workloads"])
+    parallel = __import__(graft.PACKAGE_NAME + ".parallel", fromlist=["parallel"])
+    logits, params = workloads.config5a_large_vocab(package.ROW_PARAMS_DTYPE)      # every rank builds the same matrix and keeps its slice
+    rows, vocab = logits.shape
+    top_k = 64
+    begin, end = parallel.vocab_shard_range(vocab, world, rank)
+    slices = [torch.from_numpy(np.ascontiguousarray(np.roll(logits, shift, axis=0)[:, begin:end])).cuda() for shift in range(4)]
+    sampler = package.Sampler(max_rows=rows, max_vocab=end - begin, device=local_rank)
+
+    def step(i):
+        local = sampler.local_candidates(slices[i % 4], begin, top_k)
+        gathered = parallel.all_gather_candidates(local) if world > 1 else local.unsqueeze(0)
+        return sampler.merge_candidates(gathered, params if i == 0 else None, top_k, step_offset=i)
+
+    out = step(0)
+    for i in range(1, args.warmup):
+        out = step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    stop.record()
+    torch.cuda.synchronize()
+    elapsed = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    ms = float(elapsed.item()) / args.steps
+    check = step(0)
+    torch.cuda.synchronize()
+    if rank == 0:
+        from oracle import oracle as oracle_module
+        oracle = oracle_module.best()
+        sample_rows = 8
+        uniforms = np.array([package.philox_uniform(p["seed"], p["row_id"], p["step"]) for p in params[:sample_rows]], dtype=np.float32)
+        want = oracle.sample_batch(logits[:sample_rows], params["temperature"][:sample_rows], params["top_k"][:sample_rows], params["top_p"][:sample_rows],
+                                   params["min_p"][:sample_rows], uniforms)
+        agree = int(np.sum(check["token"].cpu().numpy()[:sample_rows] == want["token"]))
+        peak, _ = measured_peak()
+        bytes_per_step = rows * vocab * 4
+        line = {"metric": "vocab-sharded sampled rows/s at vocab 1048576, batch 64", "value": rows / (ms * 1e-3), "unit": "rows/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "config 5a: 64 rows x vocab 1048576 fp32, top_k 64 top_p 0.9", "sharding": f"vocab over {world} GPUs, all-gather of {rows}x{top_k} 8-byte records",
+                           "launch": "direct calls (local candidates kernel, NCCL all-gather, merge kernel)"},
+                "roofline": {"bound": "hbm", "achieved": bytes_per_step / (ms * 1e-3) / 1e9, "peak": peak * world, "unit": "GB/s",
+                             "frac": bytes_per_step / (ms * 1e-3) / 1e9 / (peak * world)},
+                "gpu_launches": (2 + (1 if world > 1 else 0)) * args.steps, "token_ids_equal_to_reference": f"{agree}/{sample_rows}"}
+        print(json.dumps(line), flush=True)
+    sampler.close()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=2000)
     parser.add_argument("--warmup", type=int, default=20)
-    parser.add_argument("--workload", default="headline", choices=sorted(WORKLOADS))
+    parser.add_argument("--workload", default="headline", choices=sorted(WORKLOADS) + ["config5b"])
+    parser.add_argument("--sharding", default="rows", choices=["rows", "vocab"], help="vocab: config 5a split by vocabulary slice with a candidate all-gather")
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--e2e-steps", type=int, default=20)
     parser.add_argument("--no-cpu-baseline", action="store_true")
@@ -220,6 +362,10 @@ def main() -> int:
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
 
+    if args.workload == "config5b":
+        return run_router_bench(args)
+    if args.sharding == "vocab":
+        return run_vocab_sharded_bench(args)
     if args.impl == "reference":
         return run_reference_arm(args)
 

@@ -263,7 +263,8 @@ class Sampler:
             "status": torch.empty(rows, dtype=torch.int32, device=device),
             "topk": torch.empty((rows, topk_stride), dtype=torch.int32, device=device) if topk_stride else None,
         }
-        params = np.ascontiguousarray(params, dtype=ROW_PARAMS_DTYPE)
+        if params is not None:   # None reuses the parameters uploaded by the previous call
+            params = np.ascontiguousarray(params, dtype=ROW_PARAMS_DTYPE)
         stream_handle = torch.cuda.current_stream(device).cuda_stream if stream is None else stream
         self._check(self._lib.moe_sample_merge_candidates(self._handle, C.c_void_p(stream_handle), _dev_ptr(gathered), shards, rows, top_k,
                                                           _np_ptr(params), int(step_offset), _dev_ptr(out["token"]), _dev_ptr(out["probability"]),

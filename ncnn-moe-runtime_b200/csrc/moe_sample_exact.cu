@@ -144,24 +144,39 @@ __device__ void radix_pass(const uint32_t* keys_in, const uint32_t* index_in, ui
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
-    const uint32_t segment = ((n + kExactThreads - 1) / kExactThreads) * 32u;
+    const uint32_t segment = ((n + 4 * kExactThreads - 1) / (4 * kExactThreads)) * 128u; // per warp, whole 128-key trips
     const uint32_t begin = min(n, warp * segment);
     const uint32_t end = min(n, begin + segment);
 
+    MOE_EXACT_BEGIN();
     for (int d = lane; d < 256; d += 32)
         sh.warp_hist[warp][d] = 0;
     __syncwarp();
-    for (uint32_t base = begin; base < end; base += 32)
+    // four coalesced loads in flight per lane: the scratch lives in L2, and a
+    // dependent load per 32 keys would leave the warp waiting most of the time
+    for (uint32_t base = begin; base < end; base += 128)
     {
-        const uint32_t i = base + lane;
-        const bool valid = i < end;
-        const uint32_t digit = valid ? ((keys_in[i] >> shift) & 0xFFu) : 0xFFFFFFFFu;
-        const unsigned peers = __match_any_sync(kFullMask, digit);
-        if (valid && lane == (__ffs(peers) - 1))
-            sh.warp_hist[warp][digit] += __popc(peers);
-        __syncwarp();
+        uint32_t key[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+        {
+            const uint32_t i = base + u * 32 + lane;
+            key[u] = (i < end) ? keys_in[i] : 0u;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+        {
+            const uint32_t i = base + u * 32 + lane;
+            const bool valid = i < end;
+            const uint32_t digit = valid ? ((key[u] >> shift) & 0xFFu) : 0xFFFFFFFFu;
+            const unsigned peers = __match_any_sync(kFullMask, digit);
+            if (valid && lane == (__ffs(peers) - 1))
+                sh.warp_hist[warp][digit] += __popc(peers);
+            __syncwarp();
+        }
     }
     __syncthreads();
+    MOE_EXACT_MARK(4);
     // exclusive offsets: digit-major, then warp order
     if (tid < 256)
     {
@@ -209,25 +224,38 @@ __device__ void radix_pass(const uint32_t* keys_in, const uint32_t* index_in, ui
             sh.warp_hist[w][tid] += digit_base;
     }
     __syncthreads();
-    for (uint32_t base = begin; base < end; base += 32)
+    MOE_EXACT_MARK(5);
+    for (uint32_t base = begin; base < end; base += 128)
     {
-        const uint32_t i = base + lane;
-        const bool valid = i < end;
-        const uint32_t key = valid ? keys_in[i] : 0u;
-        const uint32_t digit = valid ? ((key >> shift) & 0xFFu) : 0xFFFFFFFFu;
-        const unsigned peers = __match_any_sync(kFullMask, digit);
-        if (valid)
+        uint32_t key[4], payload[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
         {
-            const uint32_t slot = sh.warp_hist[warp][digit] + __popc(peers & ((1u << lane) - 1u));
-            keys_out[slot] = key;
-            index_out[slot] = index_in[i];
+            const uint32_t i = base + u * 32 + lane;
+            key[u] = (i < end) ? keys_in[i] : 0u;
+            payload[u] = (i < end) ? index_in[i] : 0u;
         }
-        __syncwarp();
-        if (valid && lane == (__ffs(peers) - 1))
-            sh.warp_hist[warp][digit] += __popc(peers);
-        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+        {
+            const uint32_t i = base + u * 32 + lane;
+            const bool valid = i < end;
+            const uint32_t digit = valid ? ((key[u] >> shift) & 0xFFu) : 0xFFFFFFFFu;
+            const unsigned peers = __match_any_sync(kFullMask, digit);
+            if (valid)
+            {
+                const uint32_t slot = sh.warp_hist[warp][digit] + __popc(peers & ((1u << lane) - 1u));
+                keys_out[slot] = key[u];
+                index_out[slot] = payload[u];
+            }
+            __syncwarp();
+            if (valid && lane == (__ffs(peers) - 1))
+                sh.warp_hist[warp][digit] += __popc(peers);
+            __syncwarp();
+        }
     }
     __syncthreads();
+    MOE_EXACT_MARK(6);
 }
 
 // The arithmetic tail of session.cpp:89-136,429-442 for a complete, sorted
@@ -332,14 +360,20 @@ __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys
     int source = 0;
     if (n > 1 && !has_pos_inf)
     {
-        // digits on which all keys agree need no pass (bf16 logits: the two low bytes)
+        // A digit needs no pass when it is the same function of the higher digits
+        // for every key.  Keys are ~ordered_key(v): their low bytes are the
+        // magnitude bytes of v, complemented or not by the sign alone, so a byte
+        // on which all magnitudes agree (bf16 logits: the two low bytes) can be
+        // skipped.  (x ^ (x >> 31 ? 0 : ~0)) & 0x7FFFFFFF recovers the magnitude.
         uint32_t any_bits = 0;
         uint32_t all_bits = 0xFFFFFFFFu;
         for (uint32_t i = tid; i < n; i += kExactThreads)
         {
             const uint32_t key = keys[0][i];
-            any_bits |= key;
-            all_bits &= key;
+            const uint32_t magnitude = ((key & 0x80000000u) ? key : ~key) & 0x7FFFFFFFu;
+            const uint32_t probe = magnitude | (key & 0x80000000u);
+            any_bits |= probe;
+            all_bits &= probe;
         }
         any_bits = __reduce_or_sync(kFullMask, any_bits);
         all_bits = __reduce_and_sync(kFullMask, all_bits);
