@@ -72,11 +72,13 @@ __device__ __forceinline__ float load_logit(const T* row, uint32_t index)
     return LogitTraits<T>::widen(row, index);
 }
 
-// Stable compaction of the finite logits of a row into (inverted key, index)
-// arrays, index ascending.  Returns the count; sets sh.flag_pos_inf when a
+// Stable compaction of the finite logits of a row into 64-bit sort items
+// (inverted ordered key in the high word, token id in the low word), index
+// ascending.  The complement of an item is the candidate record the epilogue
+// reads, and ascending items are descending records.  Returns the count; sets sh.flag_pos_inf when a
 // +inf logit was seen (the row is then an error, session.cpp:84-85).
 template<typename T>
-__device__ uint32_t compact_finite(const T* row, uint32_t vocab, uint32_t* keys, uint32_t* index, ExactShared& sh)
+__device__ uint32_t compact_finite(const T* row, uint32_t vocab, uint64_t* items, ExactShared& sh)
 {
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -127,8 +129,7 @@ __device__ uint32_t compact_finite(const T* row, uint32_t vocab, uint32_t* keys,
         if (keep)
         {
             const uint32_t slot = cursor + __popc(voters & ((1u << lane) - 1u));
-            keys[slot] = ~ordered_key(v); // ascending sort of this = descending logits
-            index[slot] = i;
+            items[slot] = (static_cast<uint64_t>(~ordered_key(v)) << 32) | i; // ascending sort of this = descending logits
         }
         cursor += __popc(voters);
     }
@@ -138,8 +139,7 @@ __device__ uint32_t compact_finite(const T* row, uint32_t vocab, uint32_t* keys,
 
 // One stable counting-sort pass on an 8-bit digit.  Each warp owns a contiguous
 // segment of the input, so input order is preserved inside every digit.
-__device__ void radix_pass(const uint32_t* keys_in, const uint32_t* index_in, uint32_t* keys_out, uint32_t* index_out, uint32_t n, int shift,
-                           ExactShared& sh)
+__device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32_t n, int shift, ExactShared& sh)
 {
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -161,7 +161,7 @@ __device__ void radix_pass(const uint32_t* keys_in, const uint32_t* index_in, ui
         for (int u = 0; u < 4; ++u)
         {
             const uint32_t i = base + u * 32 + lane;
-            key[u] = (i < end) ? keys_in[i] : 0u;
+            key[u] = (i < end) ? static_cast<uint32_t>(items_in[i] >> 32) : 0u;
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u)
@@ -227,26 +227,24 @@ __device__ void radix_pass(const uint32_t* keys_in, const uint32_t* index_in, ui
     MOE_EXACT_MARK(5);
     for (uint32_t base = begin; base < end; base += 128)
     {
-        uint32_t key[4], payload[4];
+        uint64_t item[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u)
         {
             const uint32_t i = base + u * 32 + lane;
-            key[u] = (i < end) ? keys_in[i] : 0u;
-            payload[u] = (i < end) ? index_in[i] : 0u;
+            item[u] = (i < end) ? items_in[i] : 0ull;
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u)
         {
             const uint32_t i = base + u * 32 + lane;
             const bool valid = i < end;
-            const uint32_t digit = valid ? ((key[u] >> shift) & 0xFFu) : 0xFFFFFFFFu;
+            const uint32_t digit = valid ? (static_cast<uint32_t>(item[u] >> (32 + shift)) & 0xFFu) : 0xFFFFFFFFu;
             const unsigned peers = __match_any_sync(kFullMask, digit);
             if (valid)
             {
                 const uint32_t slot = sh.warp_hist[warp][digit] + __popc(peers & ((1u << lane) - 1u));
-                keys_out[slot] = key[u];
-                index_out[slot] = payload[u];
+                items_out[slot] = item[u]; // one 8-byte store per item
             }
             __syncwarp();
             if (valid && lane == (__ffs(peers) - 1))
@@ -346,14 +344,12 @@ __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys
     const moe_row_params p = a.params[row];
     const T* row_pointer = static_cast<const T*>(a.logits) + static_cast<size_t>(row) * a.row_stride;
 
-    // pair q = (slot_keys + q*slot_stride, slot_index + q*slot_stride); the two
-    // arrays of a pair are adjacent so that a pair can also hold 64-bit records
-    uint32_t* keys[2] = {slot_keys, slot_keys + 2 * static_cast<size_t>(slot_stride)};
-    uint32_t* index[2] = {slot_keys + slot_stride, slot_keys + 3 * static_cast<size_t>(slot_stride)};
+    // the slot holds two buffers of slot_stride 64-bit items; the sort ping-pongs between them
+    uint64_t* items[2] = {reinterpret_cast<uint64_t*>(slot_keys), reinterpret_cast<uint64_t*>(slot_keys) + slot_stride};
     (void)slot_index;
 
     MOE_EXACT_BEGIN();
-    const uint32_t n = compact_finite<T>(row_pointer, a.vocab, keys[0], index[0], sh);
+    const uint32_t n = compact_finite<T>(row_pointer, a.vocab, items[0], sh);
     const bool has_pos_inf = sh.flag_pos_inf != 0;
     MOE_EXACT_MARK(0);
 
@@ -361,7 +357,7 @@ __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys
     if (n > 1 && !has_pos_inf)
     {
         // A digit needs no pass when it is the same function of the higher digits
-        // for every key.  Keys are ~ordered_key(v): their low bytes are the
+        // for every key.  Keys (high words) are ~ordered_key(v): their low bytes are the
         // magnitude bytes of v, complemented or not by the sign alone, so a byte
         // on which all magnitudes agree (bf16 logits: the two low bytes) can be
         // skipped.  (x ^ (x >> 31 ? 0 : ~0)) & 0x7FFFFFFF recovers the magnitude.
@@ -369,7 +365,7 @@ __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys
         uint32_t all_bits = 0xFFFFFFFFu;
         for (uint32_t i = tid; i < n; i += kExactThreads)
         {
-            const uint32_t key = keys[0][i];
+            const uint32_t key = static_cast<uint32_t>(items[0][i] >> 32);
             const uint32_t magnitude = ((key & 0x80000000u) ? key : ~key) & 0x7FFFFFFFu;
             const uint32_t probe = magnitude | (key & 0x80000000u);
             any_bits |= probe;
@@ -396,20 +392,20 @@ __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys
         {
             if (((varying >> shift) & 0xFFu) == 0)
                 continue;
-            radix_pass(keys[source], index[source], keys[1 - source], index[1 - source], n, shift, sh);
+            radix_pass(items[source], items[1 - source], n, shift, sh);
             source = 1 - source;
         }
     }
 
     MOE_EXACT_MARK(1);
-    // records of the sorted order go to the other pair, the floats of the
-    // epilogue to this pair's key array (free once the records are built)
-    uint64_t* records = reinterpret_cast<uint64_t*>(keys[1 - source]);
-    float* work = reinterpret_cast<float*>(keys[source]);
+    // complementing a sorted item gives the candidate record (ordered key, 0xFFFFFFFF - id);
+    // the other buffer is free and serves the epilogue's floats
+    uint64_t* records = items[source];
+    float* work = reinterpret_cast<float*>(items[1 - source]);
     if (!has_pos_inf)
     {
         for (uint32_t i = tid; i < n; i += kExactThreads)
-            records[i] = make_record(~keys[source][i], index[source][i]);
+            records[i] = ~records[i];
     }
     __syncthreads();
     MOE_EXACT_MARK(2);
