@@ -91,7 +91,13 @@ constexpr int kThreads = 256;
 constexpr int kCapSmall = 2048;           // records a CTA can hold: batches whose Top-K sizes are small (6 CTAs per SM)
 constexpr int kCapLarge = 4096;           // ... and batches with top_k up to MOE_SAMPLER_TOPK_FAST_MAX (4 CTAs per SM)
 constexpr int kItems = kCapLarge / kThreads; // most records per thread in block-wide passes
-constexpr int kGroupsPerTile = 4;         // vector loads in flight per thread
+#ifndef MOE_TILE
+#define MOE_TILE 2
+#endif
+#ifndef MOE_RESIDENT
+#define MOE_RESIDENT 6
+#endif
+constexpr int kGroupsPerTile = MOE_TILE;  // vector loads in flight per thread
 constexpr uint32_t kWarpHitCap = 128;      // vectors a warp of the barrier-free loop can queue per slice
 // live mode: the buffer is re-tested against the running maximum at half fill;
 // more survivors than live_abort(cap) send the row to the exact kernel
@@ -423,7 +429,6 @@ __device__ __noinline__ void stream_slice_safe(Ctx& c, const T* row_pointer, uin
                                                uint32_t group_begin, uint32_t group_end, uint32_t rank, uint32_t splits)
 {
     using U = Unpack<T>;
-    RowShared& s = c.s;
     const int tid = threadIdx.x;
     const uint4* vector_base = reinterpret_cast<const uint4*>(row_pointer + head);
     // unaligned leading logits (lowest indices: first, by the first CTA)
@@ -525,6 +530,27 @@ __device__ __forceinline__ void offer_values(RowShared& s, uint64_t* rec, uint32
     }
 }
 
+// Unpacks a warp's queued vectors: re-reads each 32-byte vector and appends the
+// logits that reach the threshold.  Called by whole warps, at the end of the
+// warp's part of the stream and whenever its queue is nearly full.  Out of line
+// so that the streaming loop stays small.
+template<typename T>
+__device__ __forceinline__ void drain_warp_queue(RowShared& s, uint64_t* rec, uint32_t cap, Mode mode, float tau, const Vec32* vector_base,
+                                              uint32_t head, const uint32_t* queue, uint32_t queued)
+{
+    using W = Wide<T>;
+    const uint32_t lane = threadIdx.x & 31u;
+    for (uint32_t i = lane; i < queued; i += 32)
+    {
+        const uint32_t vi = queue[i];
+        const Vec32 again = load_stream_32(vector_base + vi);
+        float x[W::kWidth];
+        W::values(again, x);
+        offer_values<W::kWidth>(s, rec, cap, mode, tau, x, head + vi * W::kWidth);
+    }
+    __syncwarp();
+}
+
 // The barrier-free streaming loop.  The first tile of the slice estimates a
 // threshold from the per-thread maxima (their r-th largest, r chosen so that a
 // few times k logits of the whole slice are expected above it; live mode uses
@@ -597,6 +623,7 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
     uint32_t* const my_queue = s.hit_queue[warp];
     const unsigned lanes_below = (1u << lane) - 1u;
 
+    uint32_t live_maximum = 0; // live mode, second attempt: the slice maximum found by the first
     for (int attempt = 0;; ++attempt)
     {
         // Threshold = the r-th largest thread maximum: at least r logits of the tile reach it.
@@ -627,7 +654,8 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
                 s.sel.bucket = sorted_key;
         }
         __syncthreads();
-        const uint32_t threshold_key = s.sel.bucket;
+        // a live row whose first attempt overflowed knows its true maximum now: use it
+        const uint32_t threshold_key = (live_maximum != 0u) ? live_maximum : s.sel.bucket;
         if (threshold_key <= kKeyNegInf)
             return false; // the tile holds (almost) nothing finite
         float tau;
@@ -667,6 +695,13 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
                     my_hits += __popc(voters);
                     if (mode == kLive && hit && ordered_key(best) > seen_max)
                         atomicMax(&s.maxkey, ordered_key(best));
+                    if (my_hits > kWarpHitCap - 32)
+                    {
+                        // the next vote might not fit: unpack what is queued now (rare; live rows with a late maximum)
+                        __syncwarp();
+                        drain_warp_queue<T>(s, rec, cap, mode, tau, vector_base, head, my_queue, my_hits);
+                        my_hits = 0;
+                    }
                 }
             }
             g += kGroupsPerTile;
@@ -697,6 +732,12 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
                 my_hits += __popc(voters);
                 if (mode == kLive && hit && ordered_key(best) > seen_max)
                     atomicMax(&s.maxkey, ordered_key(best));
+                if (my_hits > kWarpHitCap - 32)
+                {
+                    __syncwarp();
+                    drain_warp_queue<T>(s, rec, cap, mode, tau, vector_base, head, my_queue, my_hits);
+                    my_hits = 0;
+                }
             }
         }
         // logits before / after the 32-byte aligned body of the row
@@ -714,16 +755,7 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
         __syncwarp();
         if (mode == kLive)
             tau = fmaxf(tau, live_threshold(*reinterpret_cast<volatile uint32_t*>(&s.maxkey), temperature));
-        if (my_hits > kWarpHitCap)
-            s.overflow = 1u;
-        for (uint32_t i = lane; i < min(my_hits, kWarpHitCap); i += 32)
-        {
-            const uint32_t vi = my_queue[i];
-            const Vec32 again = load_stream_32(vector_base + vi);
-            float x[W::kWidth];
-            W::values(again, x);
-            offer_values<W::kWidth>(s, rec, cap, mode, tau, x, head + vi * W::kWidth);
-        }
+        drain_warp_queue<T>(s, rec, cap, mode, tau, vector_base, head, my_queue, my_hits);
         __syncthreads();
         const uint32_t found = s.count;
         const bool overflow = s.overflow != 0;
@@ -732,7 +764,12 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
             return true;
         // Too few logits reached the sampled threshold (or far too many): forget
         // them.  A short count is retried once or twice with a lower threshold —
-        // the slice is in L2 now — before the careful loop takes over.
+        // the slice is in L2 now — before the careful loop takes over.  A live
+        // row that overflowed (its maximum came late, so the threshold of the
+        // first tile let too much through) has seen its true maximum by now and
+        // is streamed once more against it.
+        const uint32_t seen_maximum = s.maxkey;
+        __syncthreads();
         if (tid == 0)
         {
             s.count = 0;
@@ -740,6 +777,13 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
             s.overflow = 0;
         }
         __syncthreads();
+        if (mode == kLive)
+        {
+            if (live_maximum != 0u || seen_maximum == 0u)
+                return false; // already retried with the true maximum: the live set really is large
+            live_maximum = seen_maximum;
+            continue;
+        }
         const uint32_t limit = (3u * kThreads) / 4u;
         if (overflow || r >= limit || attempt >= 2)
             return false;
@@ -900,7 +944,7 @@ __global__ void __launch_bounds__(kThreads, kResident) sample_rows_kernel(const 
 {
     extern __shared__ __align__(16) unsigned char shared_raw[];
     RowShared& s = *reinterpret_cast<RowShared*>(shared_raw);
-    constexpr uint32_t kCapacity = (kResident >= 6) ? kCapSmall : kCapLarge;
+    constexpr uint32_t kCapacity = (kResident >= 5) ? kCapSmall : kCapLarge;
     uint64_t* const records = reinterpret_cast<uint64_t*>(shared_raw + sizeof(RowShared));
     float* const scratch = reinterpret_cast<float*>(records + kCapacity);
     const uint32_t row = blockIdx.x / splits;
@@ -1177,7 +1221,7 @@ template<typename T, int kResident>
 cudaError_t launch_typed(const SampleArgs& args, const Workspace& ws, uint32_t splits, cudaStream_t stream)
 {
     static bool configured = false; // per instantiation; the attribute is per device function
-    const size_t shared_bytes = shared_bytes_for(kResident >= 6 ? kCapSmall : kCapLarge);
+    const size_t shared_bytes = shared_bytes_for(kResident >= 5 ? kCapSmall : kCapLarge);
     if (!configured)
     {
         cudaError_t status = cudaFuncSetAttribute(sample_rows_kernel<T, kResident>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared_bytes));
@@ -1202,8 +1246,8 @@ cudaError_t launch_sample_rows(const SampleArgs& args, const Workspace& ws, uint
         return launch_typed<__nv_bfloat16, 4>(args, ws, splits, stream);
     }
     if (args.dtype == MOE_DTYPE_F32)
-        return launch_typed<float, 6>(args, ws, splits, stream);
-    return launch_typed<__nv_bfloat16, 6>(args, ws, splits, stream);
+        return launch_typed<float, MOE_RESIDENT>(args, ws, splits, stream);
+    return launch_typed<__nv_bfloat16, MOE_RESIDENT>(args, ws, splits, stream);
 }
 
 cudaError_t launch_merge_candidates(const uint64_t* gathered, uint32_t shards, uint32_t rows, uint32_t top_k, const moe_row_params* params,
