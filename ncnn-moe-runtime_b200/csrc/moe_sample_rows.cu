@@ -95,7 +95,7 @@ constexpr int kItems = kCapLarge / kThreads; // most records per thread in block
 #define MOE_TILE 2
 #endif
 #ifndef MOE_RESIDENT
-#define MOE_RESIDENT 6
+#define MOE_RESIDENT 5
 #endif
 constexpr int kGroupsPerTile = MOE_TILE;  // vector loads in flight per thread
 constexpr uint32_t kWarpHitCap = 128;      // vectors a warp of the barrier-free loop can queue per slice
@@ -1282,12 +1282,12 @@ cudaError_t launch_merge_candidates(const uint64_t* gathered, uint32_t shards, u
 uint32_t choose_splits(uint32_t rows, uint32_t vocab, int dtype, int sm_count, uint32_t slice_slots, bool large_top_k)
 {
     // Cut rows into slices only while all CTAs of the launch stay resident at
-    // once (6 per SM, 4 with the large record buffer): a single wave has no ragged second wave, and the fixed
+    // once (5 per SM, 4 with the large record buffer): a single wave has no ragged second wave, and the fixed
     // per-slice work (threshold estimate, select, publication) stays small
     // next to a slice of at least 64 KiB.
     const uint64_t row_bytes = static_cast<uint64_t>(vocab) * (dtype == MOE_DTYPE_F32 ? 4u : 2u);
     const uint64_t by_size = row_bytes / (64u * 1024u);
-    const uint64_t resident = static_cast<uint64_t>(sm_count) * (large_top_k ? 4u : 6u);
+    const uint64_t resident = static_cast<uint64_t>(sm_count) * (large_top_k ? 4u : static_cast<unsigned>(MOE_RESIDENT));
     uint32_t splits = 1;
     while (splits < 8u && static_cast<uint64_t>(rows) * splits * 2u <= resident && splits * 2u <= by_size &&
            static_cast<uint64_t>(rows) * splits * 2u <= slice_slots)
