@@ -359,6 +359,7 @@ def main() -> int:
     parser.add_argument("--e2e-steps", type=int, default=20)
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-graph", action="store_true", help="issue every step as a direct call instead of replaying a CUDA graph")
+    parser.add_argument("--no-overlap", action="store_true", help="launch every step strictly after the previous one (no programmatic dependent launch)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -417,6 +418,9 @@ def main() -> int:
         step(i)
     torch.cuda.synchronize()
 
+    # Steps are independent batches, so their launches may overlap (programmatic dependent
+    # launch): the serial tail of step i (select, sort, draw) runs while step i+1 streams.
+    sampler.set_overlap(not args.no_overlap)
     # The kernels of a step take tens of microseconds, less than one Python ->
     # ctypes call, so the timed loop replays a CUDA graph of `chunk` consecutive
     # steps (captured from the same C-ABI calls) and issues the remainder directly.
@@ -450,6 +454,20 @@ def main() -> int:
     if distributed:
         dist.barrier()
     elapsed_ms = start_event.elapsed_time(stop_event)
+    # the same steps strictly one after the other, for the record (latency of a single step)
+    sampler.set_overlap(False)
+    serial_steps = min(args.steps, 256)
+    serial_start = torch.cuda.Event(enable_timing=True)
+    serial_stop = torch.cuda.Event(enable_timing=True)
+    for i in range(3):
+        step(i)
+    torch.cuda.synchronize()
+    serial_start.record()
+    for i in range(serial_steps):
+        step(args.warmup + i)
+    serial_stop.record()
+    torch.cuda.synchronize()
+    serial_ms_per_step = serial_start.elapsed_time(serial_stop) / serial_steps
     clock_where = "timed region"
     if len(clocks.samples) < 5:
         # the timed region was shorter than a few NVML polls: sample the same loop again, untimed
@@ -511,7 +529,10 @@ def main() -> int:
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_label,
         "data": "synthetic",
         "config": {"workload": description, "rows_per_gpu": rows, "vocab": vocab, "sharding": "rows" if world > 1 else "none",
-                   "launch": f"CUDA graph of {chunk} steps replayed {replays}x + {remainder} direct calls" if graph is not None else "direct calls",
+                   "launch": (f"CUDA graph of {chunk} steps replayed {replays}x + {remainder} direct calls" if graph is not None else "direct calls")
+                             + ("" if args.no_overlap else "; consecutive launches overlap (programmatic dependent launch, the batches are independent)"),
+                   "serialized_direct_calls": {"ms_per_step": serial_ms_per_step, "rows_per_s": rows / (serial_ms_per_step * 1e-3),
+                                               "note": "same steps without overlap, one direct C-ABI call per step, host launch overhead included"},
                    "l2": f"{rotation} distinct resident batches of {bytes_per_step / 1e6:.0f} MB rotated, each step reads a different one"},
         "clocks": clocks.summary(clock_where),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d_bytes), "d2h_bytes_per_step": int(d2h_bytes), "steps": e2e_steps,

@@ -89,6 +89,17 @@ typedef struct moe_sampler moe_sampler;
  * reference sampler is stateless apart from Session::random_generator_). */
 int moe_sampler_create(int device, uint32_t max_rows, uint32_t max_vocab, moe_sampler** out);
 void moe_sampler_destroy(moe_sampler* sampler);
+/* Back-to-back sampling calls on one stream normally run one after the other.
+ * With overlap enabled, moe_sample_batch launches its kernel with programmatic
+ * stream serialization: it may start reading its logits while the previous
+ * kernel of the stream is still in its last microseconds (selecting, sorting,
+ * drawing), and waits for that kernel to complete before it writes anything.
+ * Results are unchanged.  Enable it only when the logits of a call do not
+ * depend on the kernel launched immediately before it on the same stream
+ * (independent batches, or logits produced earlier): that kernel is not waited
+ * for before the logits are read.  Off by default.  No reference counterpart
+ * (the reference samples on the host). */
+int moe_sampler_set_overlap(moe_sampler* sampler, int enable);
 /* Text of the last failing call on this handle (never NULL). */
 const char* moe_sampler_last_error(const moe_sampler* sampler);
 
@@ -122,7 +133,8 @@ void moe_host_free(void* pointer);
  * row_flags, row_status  device, rows entries (may be NULL)
  * topk_index        device, [rows x topk_stride] or NULL: for rows with
  *                   0 < top_k <= MOE_SAMPLER_TOPK_FAST_MAX the first min(top_k, topk_stride)
- *                   token ids of the reference rank order (session.cpp:80-87), -1 padded
+ *                   token ids of the reference rank order (session.cpp:80-87), -1 padded;
+ *                   every other row (greedy, top_k = 0, top_k above the limit, rejected) is all -1
  * Asynchronous on `stream` (a cudaStream_t). */
 int moe_sample_batch(moe_sampler* sampler, void* stream, const void* logits, int dtype, uint32_t rows, uint32_t vocab,
                      size_t row_stride, const moe_row_params* params, uint64_t step_offset, const int32_t* stop_offsets,

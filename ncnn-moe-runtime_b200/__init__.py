@@ -44,7 +44,7 @@ EXPORTED_SYMBOLS = [
     "moe_philox_uniform", "moe_host_alloc", "moe_host_free", "moe_sample_batch", "moe_sample_batch_host",
     "moe_sample_local_candidates", "moe_sample_merge_candidates", "moe_router_dispatch", "moe_router_status_message",
     "moe_router_status_error_code", "moe_router_check_options", "moe_router_dispatch_host", "moe_regroup_gather",
-    "moe_router_dispatch_static",
+    "moe_router_dispatch_static", "moe_sampler_set_overlap",
 ]
 
 _library = None
@@ -69,6 +69,7 @@ def library() -> C.CDLL:
     lib.moe_sampler_create.argtypes = [C.c_int, u32, u32, C.POINTER(vp)]
     lib.moe_sampler_destroy.argtypes = [vp]
     lib.moe_sampler_destroy.restype = None
+    lib.moe_sampler_set_overlap.argtypes = [vp, C.c_int]
     lib.moe_sampler_last_error.argtypes = [vp]
     lib.moe_sampler_last_error.restype = C.c_char_p
     lib.moe_row_status_message.argtypes = [C.c_int]
@@ -159,6 +160,10 @@ class Sampler:
         self.device = device
         self.max_rows = max_rows
         self.max_vocab = max_vocab
+
+    def set_overlap(self, enable: bool):
+        """Let consecutive sample_batch launches on one stream overlap (see moe_sampler_set_overlap)."""
+        self._check(self._lib.moe_sampler_set_overlap(self._handle, int(bool(enable))))
 
     def close(self):
         if getattr(self, "_handle", None):

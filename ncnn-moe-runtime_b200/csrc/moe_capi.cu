@@ -30,6 +30,7 @@ struct moe_sampler
     uint32_t resident_rows = 0;
     bool resident_needs_exact = false;
     bool resident_large_top_k = false;
+    bool overlap_launches = false;
     bool resident_has_stops = false;
 
     // staging for the host-buffer entry points
@@ -293,6 +294,14 @@ void moe_sampler_destroy(moe_sampler* sampler)
     delete sampler;
 }
 
+int moe_sampler_set_overlap(moe_sampler* sampler, int enable)
+{
+    if (sampler == nullptr)
+        return MOE_STATUS_INVALID_ARGUMENT;
+    sampler->overlap_launches = enable != 0;
+    return MOE_STATUS_OK;
+}
+
 const char* moe_sampler_last_error(const moe_sampler* sampler)
 {
     return sampler != nullptr ? sampler->last_error.c_str() : "null sampler handle";
@@ -379,6 +388,7 @@ int moe_sample_batch(moe_sampler* sampler, void* stream_handle, const void* logi
     args.topk_index = topk_index;
     args.topk_stride = topk_index != nullptr ? topk_stride : 0;
     args.large_top_k = sampler->resident_large_top_k;
+    args.overlap_previous = sampler->overlap_launches;
     const uint32_t splits = pick_splits(sampler, rows, vocab, dtype, args.large_top_k);
     MOE_CUDA_CHECK(sampler, launch_sample_rows(args, sampler->ws, splits, stream));
     if (sampler->resident_needs_exact)

@@ -60,6 +60,10 @@ struct SampleArgs
     // some row has a Top-K too large for the small record buffer: use the
     // large-buffer instantiation (fewer CTAs per SM)
     bool large_top_k;
+    // launched with programmatic stream serialization: the kernel may start
+    // while the previous kernel of the stream is still finishing, so it waits
+    // for that kernel (griddepcontrol.wait) before its first global write
+    bool overlap_previous;
 };
 
 cudaError_t launch_sample_rows(const SampleArgs& args, const Workspace& ws, uint32_t splits, cudaStream_t stream);

@@ -410,6 +410,15 @@ __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys
     __syncthreads();
     MOE_EXACT_MARK(2);
 
+    if (a.topk_index != nullptr)
+    {
+        // same contract as the streaming kernel: the rank-ordered ids of a Top-K row, -1 elsewhere
+        const bool lists = !has_pos_inf && p.temperature != 0.0f && p.top_k > 0 && p.top_k <= MOE_SAMPLER_TOPK_FAST_MAX;
+        const uint32_t listed = lists ? min(n, p.top_k) : 0u;
+        for (uint32_t i = tid; i < a.topk_stride; i += kExactThreads)
+            a.topk_index[static_cast<size_t>(row) * a.topk_stride + i] = (i < listed) ? static_cast<int32_t>(record_index(records[i])) : -1;
+    }
+
     {
         RowOutcome out{MOE_ROW_OK, -1, 0.0f, 0u, false};
         if (has_pos_inf || n == 0)

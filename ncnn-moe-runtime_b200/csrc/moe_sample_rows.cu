@@ -87,6 +87,18 @@ namespace moe {
 
 namespace {
 
+// Programmatic dependent launch (sm_90+).  `wait` blocks until every kernel this
+// launch depends on has completed and its memory is visible; `launch_dependents`
+// lets the next kernel of the stream begin once all CTAs have issued it or exited.
+__device__ __forceinline__ void grid_dependency_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_release()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 constexpr int kThreads = 256;
 constexpr int kCapSmall = 2048;           // records a CTA can hold: batches whose Top-K sizes are small (6 CTAs per SM)
 constexpr int kCapLarge = 4096;           // ... and batches with top_k up to MOE_SAMPLER_TOPK_FAST_MAX (4 CTAs per SM)
@@ -971,6 +983,8 @@ __global__ void __launch_bounds__(kThreads, kResident) sample_rows_kernel(const 
     if (invalid != MOE_ROW_OK)
     {
         // every CTA of the row takes this branch, so the arrival counter stays untouched
+        if (a.overlap_previous)
+            grid_dependency_wait();
         if (rank == 0)
         {
             if (tid == 0)
@@ -1042,10 +1056,20 @@ __global__ void __launch_bounds__(kThreads, kResident) sample_rows_kernel(const 
         atomicAdd(&g_phase_cycles[9], streamed ? 0ull : 1ull);
     }
 #endif
+    if (a.overlap_previous && streamed)
+        grid_dependency_release(); // this CTA has read its logits: the next launch may start filling free SM slots
     if (!streamed)
         stream_slice_safe<T>(c, row_pointer, vocab, head, 2u * vectors, tail_begin, 2u * group_begin, min(2u * group_end, (2u * vectors + kThreads - 1) / kThreads),
                              rank, splits); // the same logits in 16-byte vectors
     MOE_PHASE_MARK(2);
+    if (a.overlap_previous)
+    {
+        grid_dependency_release();
+        // Everything up to here only read the logits and the row parameters.  The
+        // slots, counters and outputs below may still be in use by the previous
+        // launch: wait until it has completed.
+        grid_dependency_wait();
+    }
 
     if (splits > 1)
     {
@@ -1229,8 +1253,22 @@ cudaError_t launch_typed(const SampleArgs& args, const Workspace& ws, uint32_t s
             return status;
         configured = true;
     }
-    sample_rows_kernel<T, kResident><<<args.rows * splits, kThreads, shared_bytes, stream>>>(args, ws, splits);
-    return cudaGetLastError();
+    if (!args.overlap_previous)
+    {
+        sample_rows_kernel<T, kResident><<<args.rows * splits, kThreads, shared_bytes, stream>>>(args, ws, splits);
+        return cudaGetLastError();
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(args.rows * splits, 1, 1);
+    config.blockDim = dim3(kThreads, 1, 1);
+    config.dynamicSmemBytes = shared_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, sample_rows_kernel<T, kResident>, args, ws, splits);
 }
 
 } // namespace

@@ -166,3 +166,48 @@ def test_adversarial_orderings(pkg, parity):
     for options in (dict(top_k=50, top_p=0.9), dict(top_k=1024), dict(temperature=0.0), dict(top_p=0.9)):
         params = pkg.make_row_params(4, seed=6, **options)
         parity.check(logits, params, topk_stride=64)
+
+
+@pytest.mark.parametrize("mixed", [False, True], ids=["topk_only", "with_live_and_greedy_rows"])
+def test_overlapped_launches_give_the_same_results(pkg, workloads, parity, torch_cuda, mixed):
+    """Programmatic dependent launch: consecutive calls may overlap on the GPU; every call
+    must still produce exactly what it produces alone (independent batches, separate outputs).
+    With Top-K rows only, one streaming launch follows the other directly; with live rows the
+    full-vocabulary kernel runs in between."""
+    torch = torch_cuda
+    logits, params = workloads.config1_row(pkg.ROW_PARAMS_DTYPE, rows=96, vocab=50021, seed=21)
+    if mixed:
+        params["top_k"][::7] = 0              # some rows go through the live / exact paths
+        params["temperature"][::11] = 0.0     # some greedy rows
+    batches = [torch.from_numpy(np.roll(logits, shift, axis=0).copy()).cuda() for shift in range(4)]
+    sampler = pkg.Sampler(max_rows=96, max_vocab=50021)
+    try:
+        alone = []
+        sampler.sample_batch(batches[0], params)
+        for step, batch in enumerate(batches):
+            out = sampler.sample_batch(batch, None, step_offset=step, topk_stride=50)
+            torch.cuda.synchronize()
+            alone.append({k: v.clone() for k, v in out.items()})
+        if mixed:
+            for out in alone:   # rows without Top-K (whichever kernel finished them) and greedy rows list nothing
+                assert bool((out["topk"][::7] == -1).all()) and bool((out["topk"][::11] == -1).all())
+        sampler.set_overlap(True)
+        together = []
+        for repeat in range(3):
+            for step, batch in enumerate(batches):
+                together.append((step, sampler.sample_batch(batch, None, step_offset=step, topk_stride=50)))   # no synchronisation in between
+        torch.cuda.synchronize()
+        for step, out in together:
+            for key in ("token", "probability", "flags", "status", "topk"):
+                if not torch.equal(out[key], alone[step][key]):
+                    bad = torch.nonzero((out[key] != alone[step][key]).reshape(96, -1).any(dim=1)).flatten().tolist()
+                    raise AssertionError(f"step {step} {key}: rows {bad[:8]} differ: "
+                                         f"{out[key][bad[0]].tolist()} vs alone {alone[step][key][bad[0]].tolist()}; params {params[bad[0]]}")
+        # and against the oracle for one of them
+        explicit = params.copy()
+        explicit["step"] = 2
+        shifted = np.roll(logits, 2, axis=0)
+        want = parity.checker.sample_batch(shifted, explicit["temperature"], explicit["top_k"], explicit["top_p"], explicit["min_p"], parity.uniforms(explicit))
+        np.testing.assert_array_equal(alone[2]["token"].cpu().numpy(), want["token"])
+    finally:
+        sampler.close()
