@@ -48,7 +48,7 @@ FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only when ME
 # kernel on the headline workload, from the ncu capture summarised in
 # profiles/ (None until a capture exists for the workload).
 NCU_TRAFFIC_BYTES = {
-    "headline": 222_970_000,  # 214.32 MB read + 8.65 MB written, profiles/sample_rows_kernel_f32_headline.md
+    "headline": 220_030_000,  # 213.59 MB read + 6.44 MB written, profiles/sample_rows_kernel_f32_headline.md
 }
 
 WORKLOADS = {

@@ -141,6 +141,35 @@ int moe_sample_batch(moe_sampler* sampler, void* stream, const void* logits, int
                      const int32_t* stop_tokens, int32_t* token_id, float* probability, uint32_t* row_flags,
                      int32_t* row_status, int32_t* topk_index, uint32_t topk_stride);
 
+/* moe_sample_batch with its outputs in a struct, plus one more: every row's
+ * kept candidates with their renormalised probabilities, i.e. the vector that
+ * sampling_distribution returns (src/engine/session.cpp:76-136) and that the
+ * speculative-decoding acceptance test reads through candidate_probability
+ * (session.cpp:138-148,800-812).  All pointers are device pointers.
+ * kept_count   [rows] or NULL: candidates kept after Top-K, Min-P and Top-P
+ *              (0 for a rejected row; 1 for a greedy row, which lists its token
+ *              with probability 1).  NULL switches the two lists off.
+ * kept_token, kept_probability  [rows x kept_stride] or NULL: the first
+ *              min(kept_count, kept_stride) candidates in rank order; entries
+ *              past that are left untouched. */
+typedef struct moe_sample_outputs
+{
+    int32_t* token_id;
+    float* probability;
+    uint32_t* row_flags;
+    int32_t* row_status;
+    int32_t* topk_index;
+    uint32_t topk_stride;
+    int32_t* kept_token;
+    float* kept_probability;
+    uint32_t* kept_count;
+    uint32_t kept_stride;
+} moe_sample_outputs;
+
+int moe_sample_batch_ex(moe_sampler* sampler, void* stream, const void* logits, int dtype, uint32_t rows, uint32_t vocab,
+                        size_t row_stride, const moe_row_params* params, uint64_t step_offset, const int32_t* stop_offsets,
+                        const int32_t* stop_tokens, const moe_sample_outputs* outputs);
+
 /* Same operation with every buffer in HOST memory (what a Session-shaped
  * caller holds: LogitsOutput::values is a std::vector<float>, session.h:30-33).
  * Copies in, samples, copies out and synchronises before returning. */

@@ -19,6 +19,13 @@ import numpy as np
 HERE = Path(__file__).resolve().parent
 LIBRARY_PATH = HERE / "libmoe_b200_sampler.so"
 
+
+class SampleOutputs(C.Structure):
+    """moe_sample_outputs of include/moe_b200_sampler.h."""
+    _fields_ = [("token_id", C.c_void_p), ("probability", C.c_void_p), ("row_flags", C.c_void_p), ("row_status", C.c_void_p),
+                ("topk_index", C.c_void_p), ("topk_stride", C.c_uint32), ("kept_token", C.c_void_p), ("kept_probability", C.c_void_p),
+                ("kept_count", C.c_void_p), ("kept_stride", C.c_uint32)]
+
 DTYPE_F32 = 0
 DTYPE_BF16 = 1
 ROW_FLAG_STOP_TOKEN = 1
@@ -41,7 +48,7 @@ class RouterOptions(C.Structure):
 
 EXPORTED_SYMBOLS = [
     "moe_sampler_create", "moe_sampler_destroy", "moe_sampler_last_error", "moe_row_status_message", "moe_row_status_error_code",
-    "moe_philox_uniform", "moe_host_alloc", "moe_host_free", "moe_sample_batch", "moe_sample_batch_host",
+    "moe_philox_uniform", "moe_host_alloc", "moe_host_free", "moe_sample_batch", "moe_sample_batch_ex", "moe_sample_batch_host",
     "moe_sample_local_candidates", "moe_sample_merge_candidates", "moe_router_dispatch", "moe_router_status_message",
     "moe_router_status_error_code", "moe_router_check_options", "moe_router_dispatch_host", "moe_regroup_gather",
     "moe_router_dispatch_static", "moe_sampler_set_overlap",
@@ -81,6 +88,7 @@ def library() -> C.CDLL:
     lib.moe_host_free.argtypes = [vp]
     lib.moe_host_free.restype = None
     lib.moe_sample_batch.argtypes = [vp, vp, vp, C.c_int, u32, u32, sz, vp, u64, vp, vp, vp, vp, vp, vp, vp, u32]
+    lib.moe_sample_batch_ex.argtypes = [vp, vp, vp, C.c_int, u32, u32, sz, vp, u64, vp, vp, C.POINTER(SampleOutputs)]
     lib.moe_sample_batch_host.argtypes = [vp, vp, C.c_int, u32, u32, sz, vp, vp, vp, vp, vp, vp, vp, vp, u32]
     lib.moe_sample_local_candidates.argtypes = [vp, vp, vp, C.c_int, u32, u32, sz, u32, u32, vp]
     lib.moe_sample_merge_candidates.argtypes = [vp, vp, vp, u32, u32, u32, vp, u64, vp, vp, vp, vp, vp, u32]
@@ -181,8 +189,9 @@ class Sampler:
             raise MoeError(status, self._lib.moe_sampler_last_error(self._handle).decode())
 
     # ---- device-resident logits (torch tensors) ---------------------------------
-    def sample_batch(self, logits, params=None, step_offset=0, stop_lists=None, topk_stride=0, stream=None, vocab=None, out=None):
-        """logits: CUDA tensor [rows, row_stride] float32 or bfloat16.  Returns a dict of CUDA tensors."""
+    def sample_batch(self, logits, params=None, step_offset=0, stop_lists=None, topk_stride=0, stream=None, vocab=None, out=None, kept_stride=0):
+        """logits: CUDA tensor [rows, row_stride] float32 or bfloat16.  Returns a dict of CUDA tensors.
+        kept_stride > 0 also returns every row's kept candidates (kept_count, kept_token, kept_probability)."""
         import torch
         rows, row_stride = logits.shape
         vocab = row_stride if vocab is None else vocab
@@ -205,6 +214,17 @@ class Sampler:
             params = np.ascontiguousarray(params, dtype=ROW_PARAMS_DTYPE)
             assert params.shape == (rows,)
         stream_handle = torch.cuda.current_stream(device).cuda_stream if stream is None else stream
+        if kept_stride:
+            if "kept_count" not in out:
+                out["kept_count"] = torch.empty(rows, dtype=torch.int32, device=device)
+                out["kept_token"] = torch.full((rows, kept_stride), -1, dtype=torch.int32, device=device)
+                out["kept_probability"] = torch.zeros((rows, kept_stride), dtype=torch.float32, device=device)
+            outputs = SampleOutputs(_dev_ptr(out["token"]), _dev_ptr(out["probability"]), _dev_ptr(out["flags"]), _dev_ptr(out["status"]),
+                                    _dev_ptr(out.get("topk")), int(topk_stride), _dev_ptr(out["kept_token"]), _dev_ptr(out["kept_probability"]),
+                                    _dev_ptr(out["kept_count"]), int(kept_stride))
+            self._check(self._lib.moe_sample_batch_ex(self._handle, C.c_void_p(stream_handle), _dev_ptr(logits), dtype, rows, vocab, logits.stride(0),
+                                                      _np_ptr(params), int(step_offset), _np_ptr(offsets), _np_ptr(tokens), C.byref(outputs)))
+            return out
         self._check(self._lib.moe_sample_batch(self._handle, C.c_void_p(stream_handle), _dev_ptr(logits), dtype, rows, vocab, logits.stride(0),
                                                _np_ptr(params), int(step_offset), _np_ptr(offsets), _np_ptr(tokens), _dev_ptr(out["token"]),
                                                _dev_ptr(out["probability"]), _dev_ptr(out["flags"]), _dev_ptr(out["status"]),

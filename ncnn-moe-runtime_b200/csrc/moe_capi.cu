@@ -354,12 +354,36 @@ int moe_sample_batch(moe_sampler* sampler, void* stream_handle, const void* logi
                      const moe_row_params* params, uint64_t step_offset, const int32_t* stop_offsets, const int32_t* stop_tokens,
                      int32_t* token_id, float* probability, uint32_t* row_flags, int32_t* row_status, int32_t* topk_index, uint32_t topk_stride)
 {
+    moe_sample_outputs outputs = {};
+    outputs.token_id = token_id;
+    outputs.probability = probability;
+    outputs.row_flags = row_flags;
+    outputs.row_status = row_status;
+    outputs.topk_index = topk_index;
+    outputs.topk_stride = topk_stride;
+    return moe_sample_batch_ex(sampler, stream_handle, logits, dtype, rows, vocab, row_stride, params, step_offset, stop_offsets, stop_tokens, &outputs);
+}
+
+int moe_sample_batch_ex(moe_sampler* sampler, void* stream_handle, const void* logits, int dtype, uint32_t rows, uint32_t vocab, size_t row_stride,
+                        const moe_row_params* params, uint64_t step_offset, const int32_t* stop_offsets, const int32_t* stop_tokens,
+                        const moe_sample_outputs* outputs)
+{
     if (int status = check_shape(sampler, dtype, rows, vocab, row_stride))
         return status;
     if (rows == 0)
         return MOE_STATUS_OK;
+    if (outputs == nullptr)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "outputs must not be null");
+    int32_t* const token_id = outputs->token_id;
+    float* const probability = outputs->probability;
+    uint32_t* const row_flags = outputs->row_flags;
+    int32_t* const row_status = outputs->row_status;
+    int32_t* const topk_index = outputs->topk_index;
+    const uint32_t topk_stride = outputs->topk_stride;
     if (logits == nullptr || token_id == nullptr || probability == nullptr)
         return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "logits, token_id and probability must not be null");
+    if (outputs->kept_count == nullptr && (outputs->kept_token != nullptr || outputs->kept_probability != nullptr))
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "kept_token / kept_probability need kept_count");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
     DeviceGuard guard(sampler->device);
     if (params != nullptr)
@@ -387,6 +411,10 @@ int moe_sample_batch(moe_sampler* sampler, void* stream_handle, const void* logi
     args.row_status = row_status;
     args.topk_index = topk_index;
     args.topk_stride = topk_index != nullptr ? topk_stride : 0;
+    args.kept_token = outputs->kept_token;
+    args.kept_probability = outputs->kept_probability;
+    args.kept_count = outputs->kept_count;
+    args.kept_stride = outputs->kept_count != nullptr ? outputs->kept_stride : 0;
     args.large_top_k = sampler->resident_large_top_k;
     args.overlap_previous = sampler->overlap_launches;
     const uint32_t splits = pick_splits(sampler, rows, vocab, dtype, args.large_top_k);

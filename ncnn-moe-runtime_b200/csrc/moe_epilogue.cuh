@@ -26,16 +26,41 @@ struct RowOutcome
     bool defer;
 };
 
+// Where one row's kept candidates go (all null / 0 when the caller did not ask).
+struct KeptList
+{
+    int32_t* token;
+    float* probability;
+    uint32_t* count;
+    uint32_t stride;
+};
+
+__device__ __forceinline__ KeptList kept_list_of_row(int32_t* token, float* probability, uint32_t* count, uint32_t stride, uint32_t row)
+{
+    KeptList list{nullptr, nullptr, nullptr, 0u};
+    if (count != nullptr)
+    {
+        list.token = token != nullptr ? token + static_cast<size_t>(row) * stride : nullptr;
+        list.probability = probability != nullptr ? probability + static_cast<size_t>(row) * stride : nullptr;
+        list.count = count + row;
+        list.stride = stride;
+    }
+    return list;
+}
+
 // records[0..count): sorted descending.  work[0..count): scratch floats.
 // tail_may_exist: the list is only the numerically live prefix of the row's
 // candidates (every omitted candidate has exp(x - peak) < 2^-26, so it cannot
 // change any of the four running sums, but it could still be the fall-back
 // "last candidate" of session.cpp:441-442).
 __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, uint32_t count, float* work, float temperature,
-                                                       uint32_t top_k, float top_p, float min_p, float uniform, bool tail_may_exist)
+                                                       uint32_t top_k, float top_p, float min_p, float uniform, bool tail_may_exist,
+                                                       const KeptList& kept_list)
 {
     const int lane = threadIdx.x & 31;
     RowOutcome out{MOE_ROW_OK, -1, 0.0f, 0u, false};
+    if (kept_list.count != nullptr && lane == 0)
+        *kept_list.count = 0; // stays 0 on every error return
     if (count == 0)
     {
         out.status = MOE_ROW_NO_FINITE_LOGIT;
@@ -105,16 +130,29 @@ __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, u
         }
     }
 
-    // renormaliser (session.cpp:130-134)
-    float kept_total = 0.0f;
-#pragma unroll 8
-    for (uint32_t i = 0; i < kept; ++i)
-        kept_total = __fadd_rn(kept_total, work[i]);
+    // renormaliser (session.cpp:130-134): the same adds over the same prefix from the same zero as the loop above
+    const float kept_total = running;
 
+    if (kept_list.count != nullptr && !list_is_complete && !cut)
+    {
+        out.defer = true; // the kept list runs on into the omitted candidates: the exact path lists them
+        return out;
+    }
     if (kept == 1)
     {
         out.token = static_cast<int32_t>(record_index(records[0])); // session.cpp:429-430: no uniform drawn
         out.probability = 1.0f;
+        if (kept_list.count != nullptr && lane == 0)
+        {
+            *kept_list.count = 1;
+            if (kept_list.stride > 0)
+            {
+                if (kept_list.token != nullptr)
+                    kept_list.token[0] = out.token;
+                if (kept_list.probability != nullptr)
+                    kept_list.probability[0] = 1.0f; // x / x
+            }
+        }
         return out;
     }
     out.flags |= MOE_ROW_FLAG_USED_UNIFORM;
@@ -124,6 +162,18 @@ __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, u
     for (uint32_t i = lane; i < kept; i += 32)
         work[i] = __fdiv_rn(work[i], kept_total);
     __syncwarp();
+    if (kept_list.count != nullptr)
+    {
+        if (lane == 0)
+            *kept_list.count = kept;
+        for (uint32_t i = lane; i < min(kept, kept_list.stride); i += 32)
+        {
+            if (kept_list.token != nullptr)
+                kept_list.token[i] = static_cast<int32_t>(record_index(records[i]));
+            if (kept_list.probability != nullptr)
+                kept_list.probability[i] = work[i];
+        }
+    }
     running = 0.0f;
 #pragma unroll 4
     for (uint32_t i = 0; i < kept; ++i)

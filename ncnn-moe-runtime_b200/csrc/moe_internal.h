@@ -53,6 +53,12 @@ struct SampleArgs
     int32_t* row_status;   // may be null
     int32_t* topk_index;   // may be null
     uint32_t topk_stride;
+    // optional: every row's kept candidates with their renormalised probabilities
+    // (the vector sampling_distribution returns, session.cpp:76-136)
+    int32_t* kept_token;     // [rows x kept_stride] or null
+    float* kept_probability; // [rows x kept_stride] or null
+    uint32_t* kept_count;    // [rows] or null: candidates kept (may exceed kept_stride; the list is cut there)
+    uint32_t kept_stride;
     // vocabulary-sharded local pass: write the slice's Top-K records instead of sampling
     uint64_t* candidates_out; // may be null
     uint32_t candidates_k;

@@ -64,7 +64,17 @@ struct ExactShared
     uint32_t warp_and[kExactWarps];
     uint32_t flag_pos_inf;
     uint32_t total;
+    uint32_t finite_total; // finite logits of the row
+    uint32_t max_key;      // ordered key of the largest finite logit
+    uint32_t floor_bucket; // coarse bucket below which every logit is numerically dead
+    float warp_sum[kExactWarps];
 };
+
+// Coarse value buckets of the dead-tail filter: the top 12 bits of the ordered
+// key (sign, exponent, three mantissa bits).
+constexpr int kCoarseShift = 20;
+constexpr uint32_t kCoarseBuckets = 1u << (32 - kCoarseShift);
+static_assert(kCoarseBuckets <= kExactWarps * 256u, "the coarse histogram lives in warp_hist");
 
 template<typename T>
 __device__ __forceinline__ float load_logit(const T* row, uint32_t index)
@@ -72,34 +82,155 @@ __device__ __forceinline__ float load_logit(const T* row, uint32_t index)
     return LogitTraits<T>::widen(row, index);
 }
 
-// Stable compaction of the finite logits of a row into 64-bit sort items
-// (inverted ordered key in the high word, token id in the low word), index
-// ascending.  The complement of an item is the candidate record the epilogue
-// reads, and ascending items are descending records.  Returns the count; sets sh.flag_pos_inf when a
-// +inf logit was seen (the row is then an error, session.cpp:84-85).
+// Dead-tail filter.  In rank order a candidate is added to every running sum of
+// the reference (session.cpp:92-101,119-134,434-440) after all larger ones, so
+// the accumulator it meets is at least their sum; an addend below 2^-25 of the
+// accumulator is less than half a unit in its last place and leaves it
+// unchanged.  One sweep builds a histogram of the row over coarse value
+// buckets; with S(b) = a lower bound of sum(exp(l/T - peak)) over the buckets
+// >= b and E(b) = exp(lower edge of b / T - peak), every logit below the lower
+// edge of b is dead in all four sums as soon as E(b) <= 2^-27 * 0.9 * S(b) (the factor four
+// covers the rounding of the sequential sums and of the normalising
+// divisions).  Only the logits at or above the highest such edge are sorted.
+// Sets sh.finite_total, sh.max_key, sh.flag_pos_inf and returns the ordered
+// key of that edge (0: keep every finite logit).
 template<typename T>
-__device__ uint32_t compact_finite(const T* row, uint32_t vocab, uint64_t* items, ExactShared& sh)
+__device__ uint32_t dead_tail_floor(const T* row, uint32_t vocab, float temperature, ExactShared& sh)
 {
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
-    const uint32_t segment = ((vocab + kExactThreads - 1) / kExactThreads) * 32u; // per warp, multiple of 32
+    uint32_t* const coarse = &sh.warp_hist[0][0];
+    for (uint32_t b = tid; b < kCoarseBuckets; b += kExactThreads)
+        coarse[b] = 0;
+    if (tid == 0)
+    {
+        sh.flag_pos_inf = 0;
+        sh.finite_total = 0;
+        sh.max_key = 0;
+        sh.floor_bucket = 0;
+    }
+    __syncthreads();
+    uint32_t finite = 0;
+    uint32_t max_key = 0;
+    bool saw_pos_inf = false;
+    for (uint32_t base = 0; base < vocab; base += 4 * kExactThreads)
+    {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+        {
+            const uint32_t i = base + u * kExactThreads + tid;
+            v[u] = (i < vocab) ? load_logit(row, i) : __uint_as_float(0x7FC00000u);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+        {
+            saw_pos_inf |= (v[u] == INFINITY);
+            if (fabsf(v[u]) < INFINITY)
+            {
+                const uint32_t key = ordered_key(v[u]);
+                atomicAdd(&coarse[key >> kCoarseShift], 1u);
+                max_key = max(max_key, key);
+                ++finite;
+            }
+        }
+    }
+    finite = __reduce_add_sync(kFullMask, finite);
+    max_key = __reduce_max_sync(kFullMask, max_key);
+    const bool warp_saw_pos_inf = __any_sync(kFullMask, saw_pos_inf);
+    if (lane == 0)
+    {
+        atomicAdd(&sh.finite_total, finite);
+        atomicMax(&sh.max_key, max_key);
+        if (warp_saw_pos_inf)
+            sh.flag_pos_inf = 1;
+    }
+    __syncthreads();
+    if (sh.finite_total == 0 || sh.flag_pos_inf != 0)
+        return 0u;
+    const float peak = __fdiv_rn(key_to_float(sh.max_key), temperature);
+    // thread t owns the four buckets 4t..4t+3 counted from the top
+    constexpr int kPerThread = kCoarseBuckets / kExactThreads;
+    float edge_exp[kPerThread];
+    float mine[kPerThread];
+    float running = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j)
+    {
+        const uint32_t bucket = kCoarseBuckets - 1u - (static_cast<uint32_t>(tid) * kPerThread + j);
+        const float edge = key_to_float(bucket << kCoarseShift); // smallest value of the bucket
+        const uint32_t count = coarse[bucket];
+        // buckets whose edge is not a finite number hold no finite logit; they never become the floor
+        edge_exp[j] = (fabsf(edge) < INFINITY) ? expf(fminf(edge / temperature - peak, 0.0f)) : INFINITY;
+        if (count != 0)
+            running += static_cast<float>(count) * edge_exp[j];
+        mine[j] = running;
+    }
+    // inclusive scan of the per-thread sums, top bucket first
+    float scan = running;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1)
+    {
+        const float other = __shfl_up_sync(kFullMask, scan, offset);
+        if (lane >= offset)
+            scan += other;
+    }
+    if (lane == 31)
+        sh.warp_sum[warp] = scan;
+    __syncthreads();
+    float before = scan - running;
+    for (int w = 0; w < warp; ++w)
+        before += sh.warp_sum[w];
+    uint32_t best = 0;
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j)
+    {
+        const uint32_t bucket = kCoarseBuckets - 1u - (static_cast<uint32_t>(tid) * kPerThread + j);
+        const float above = before + mine[j]; // lower bound of the sum over the buckets >= this one
+        if (edge_exp[j] <= above * (0.9f * 7.450580596923828e-09f)) // 2^-27
+            best = max(best, bucket);
+    }
+    best = __reduce_max_sync(kFullMask, best);
+    if (lane == 0 && best != 0)
+        atomicMax(&sh.floor_bucket, best);
+    __syncthreads();
+    const uint32_t floor_key = sh.floor_bucket << kCoarseShift;
+    __syncthreads(); // warp_hist is reused by the sort
+    return floor_key;
+}
+
+// Stable compaction of the finite logits at or above `floor_key` into 64-bit
+// sort items (inverted ordered key in the high word, token id in the low word),
+// index ascending.  The complement of an item is the candidate record the
+// epilogue reads, and ascending items are descending records.  Returns the count.
+template<typename T>
+__device__ uint32_t compact_live(const T* row, uint32_t vocab, uint32_t floor_key, uint64_t* items, ExactShared& sh)
+{
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const uint32_t segment = ((vocab + 4 * kExactThreads - 1) / (4 * kExactThreads)) * 128u; // per warp, whole 128-logit trips
     const uint32_t begin = min(vocab, warp * segment);
     const uint32_t end = min(vocab, begin + segment);
-    if (tid == 0)
-        sh.flag_pos_inf = 0;
-    __syncthreads();
+    const uint32_t least = max(floor_key, kKeyNegInf + 1u);
     uint32_t mine = 0;
-    bool saw_pos_inf = false;
-    for (uint32_t base = begin; base < end; base += 32)
+    for (uint32_t base = begin; base < end; base += 128)
     {
-        const uint32_t i = base + lane;
-        const float v = (i < end) ? load_logit(row, i) : __uint_as_float(0x7FC00000u);
-        saw_pos_inf |= (v == INFINITY);
-        mine += __popc(__ballot_sync(kFullMask, fabsf(v) < INFINITY));
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+        {
+            const uint32_t i = base + u * 32 + lane;
+            v[u] = (i < end) ? load_logit(row, i) : __uint_as_float(0x7FC00000u);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+        {
+            const uint32_t key = ordered_key(v[u]);
+            mine += __popc(__ballot_sync(kFullMask, fabsf(v[u]) < INFINITY && key >= least));
+        }
     }
-    if (__any_sync(kFullMask, saw_pos_inf) && lane == 0)
-        sh.flag_pos_inf = 1;
     if (lane == 0)
         sh.warp_count[warp] = mine;
     __syncthreads();
@@ -120,18 +251,29 @@ __device__ uint32_t compact_finite(const T* row, uint32_t vocab, uint64_t* items
     }
     __syncthreads();
     uint32_t cursor = sh.warp_count[warp];
-    for (uint32_t base = begin; base < end; base += 32)
+    for (uint32_t base = begin; base < end; base += 128)
     {
-        const uint32_t i = base + lane;
-        const float v = (i < end) ? load_logit(row, i) : __uint_as_float(0x7FC00000u);
-        const bool keep = fabsf(v) < INFINITY;
-        const unsigned voters = __ballot_sync(kFullMask, keep);
-        if (keep)
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
         {
-            const uint32_t slot = cursor + __popc(voters & ((1u << lane) - 1u));
-            items[slot] = (static_cast<uint64_t>(~ordered_key(v)) << 32) | i; // ascending sort of this = descending logits
+            const uint32_t i = base + u * 32 + lane;
+            v[u] = (i < end) ? load_logit(row, i) : __uint_as_float(0x7FC00000u);
         }
-        cursor += __popc(voters);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+        {
+            const uint32_t i = base + u * 32 + lane;
+            const uint32_t key = ordered_key(v[u]);
+            const bool keep = fabsf(v[u]) < INFINITY && key >= least;
+            const unsigned voters = __ballot_sync(kFullMask, keep);
+            if (keep)
+            {
+                const uint32_t slot = cursor + __popc(voters & ((1u << lane) - 1u));
+                items[slot] = (static_cast<uint64_t>(~key) << 32) | i; // ascending sort of this = descending logits
+            }
+            cursor += __popc(voters);
+        }
     }
     __syncthreads();
     return sh.total;
@@ -148,7 +290,6 @@ __device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32
     const uint32_t begin = min(n, warp * segment);
     const uint32_t end = min(n, begin + segment);
 
-    MOE_EXACT_BEGIN();
     for (int d = lane; d < 256; d += 32)
         sh.warp_hist[warp][d] = 0;
     __syncwarp();
@@ -176,7 +317,6 @@ __device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32
         }
     }
     __syncthreads();
-    MOE_EXACT_MARK(4);
     // exclusive offsets: digit-major, then warp order
     if (tid < 256)
     {
@@ -224,7 +364,6 @@ __device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32
             sh.warp_hist[w][tid] += digit_base;
     }
     __syncthreads();
-    MOE_EXACT_MARK(5);
     for (uint32_t base = begin; base < end; base += 128)
     {
         uint64_t item[4];
@@ -253,7 +392,6 @@ __device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32
         }
     }
     __syncthreads();
-    MOE_EXACT_MARK(6);
 }
 
 // The arithmetic tail of session.cpp:89-136,429-442 for a complete, sorted
@@ -262,12 +400,21 @@ __device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32
 // bit-exactly by block_sequential_sum.  Same steps, same roundings and same
 // outcomes as finish_row_warp (which serves the short lists of the streaming
 // kernel); every thread returns the same result.
-__device__ RowOutcome finish_row_exact_block(const uint64_t* records, uint32_t count, float* work, float temperature, uint32_t top_k, float top_p,
-                                             float min_p, float uniform, ExactShared& sh)
+// `records` holds the first `present` candidates of the rank order; the
+// row has `finite_total` finite logits, and those missing from `records` are
+// numerically dead (dead_tail_floor).  When the outcome would depend on a
+// missing candidate (Min-P prefix or last-candidate fallback reaching past
+// `present`), sets needs_full and returns: the caller repeats the row unfiltered.
+__device__ RowOutcome finish_row_exact_block(const uint64_t* records, uint32_t present, uint32_t finite_total, float* work, float temperature,
+                                             uint32_t top_k, float top_p, float min_p, float uniform, ExactShared& sh, bool& needs_full,
+                                             const KeptList& kept_list)
 {
     const uint32_t tid = threadIdx.x;
     RowOutcome out{MOE_ROW_OK, -1, 0.0f, 0u, false};
-    if (count == 0)
+    needs_full = false;
+    if (kept_list.count != nullptr && tid == 0)
+        *kept_list.count = 0; // stays 0 on every error return
+    if (present == 0)
     {
         out.status = MOE_ROW_NO_FINITE_LOGIT;
         return out;
@@ -278,58 +425,105 @@ __device__ RowOutcome finish_row_exact_block(const uint64_t* records, uint32_t c
         out.status = MOE_ROW_NO_FINITE_LOGIT;
         return out;
     }
-    // every record here is finite (compact_finite dropped the rest), so Top-K only shortens the list
-    const uint32_t finite = (top_k > 0 && top_k <= count) ? top_k : count;
+    // every candidate is finite (the compaction dropped the rest), so Top-K only shortens the list (session.cpp:86-87)
+    const uint32_t listed = (top_k > 0 && top_k < finite_total) ? top_k : finite_total;
+    const uint32_t have = min(present, listed); // candidates of the list whose records exist
 
     const float peak = __fdiv_rn(key_to_float(head_key), temperature);
-    for (uint32_t i = tid; i < finite; i += kExactThreads)
+    for (uint32_t i = tid; i < have; i += kExactThreads)
         work[i] = exact_expf(scaled_offset(key_to_float(record_key(records[i])), temperature, peak));
     __syncthreads();
-    const float total = block_sequential_sum<kExactThreads, 4>(work, finite, kSeqSumOnly, 0.0f, sh.seq).acc;
+    const float total = block_sequential_sum<kExactThreads, 4>(work, have, kSeqSumOnly, 0.0f, sh.seq).acc;
     if (!(total - total == 0.0f) || total <= 0.0f)
     {
         out.status = MOE_ROW_INVALID_DISTRIBUTION;
         return out;
     }
-    for (uint32_t i = tid; i < finite; i += kExactThreads)
+    for (uint32_t i = tid; i < have; i += kExactThreads)
         work[i] = __fdiv_rn(work[i], total);
     if (tid == 0)
-        sh.first_fail = finite;
+        sh.first_fail = have;
     __syncthreads();
     // Min-P: probabilities are non-increasing, so the survivors are a prefix
-    uint32_t allowed = finite;
+    uint32_t allowed = listed;
     if (min_p > 0.0f)
     {
         const float floor_probability = __fmul_rn(work[0], min_p);
-        uint32_t mine = finite;
-        for (uint32_t i = tid; i < finite; i += kExactThreads)
+        uint32_t mine = have;
+        for (uint32_t i = tid; i < have; i += kExactThreads)
             if (!(work[i] >= floor_probability))
             {
                 mine = i;
                 break; // my indices ascend: the first failure is my smallest
             }
-        if (mine < finite)
+        if (mine < have)
             atomicMin(&sh.first_fail, mine);
         __syncthreads();
-        allowed = sh.first_fail;
+        const uint32_t first_fail = sh.first_fail;
         __syncthreads();
+        if (first_fail < have)
+            allowed = first_fail;
+        else if (have < listed)
+        {
+            needs_full = true; // the prefix may go on among the filtered candidates
+            return out;
+        }
     }
-    // Top-P: first prefix whose running sum reaches top_p
-    const SeqResult nucleus = block_sequential_sum<kExactThreads, 4>(work, allowed, kSeqReachBound, top_p, sh.seq);
-    const uint32_t kept = nucleus.taken;
-    const float kept_total = block_sequential_sum<kExactThreads, 4>(work, kept, kSeqSumOnly, 0.0f, sh.seq).acc;
+    // Top-P: first prefix whose running sum reaches top_p; never reached: the whole list stays
+    const SeqResult nucleus = block_sequential_sum<kExactThreads, 4>(work, min(allowed, have), kSeqReachBound, top_p, sh.seq);
+    const uint32_t kept = nucleus.stopped ? nucleus.taken : allowed;
+    // the renormaliser (session.cpp:130-132) repeats the adds of the Top-P loop over the same prefix from the same zero
+    const float kept_total = nucleus.acc;
+    if (kept_list.count != nullptr && min(kept, kept_list.stride) > have)
+    {
+        needs_full = true; // the caller wants candidates that were filtered
+        return out;
+    }
     if (kept == 1)
     {
         out.token = static_cast<int32_t>(record_index(records[0]));
         out.probability = 1.0f;
+        if (kept_list.count != nullptr && tid == 0)
+        {
+            *kept_list.count = 1;
+            if (kept_list.stride > 0)
+            {
+                if (kept_list.token != nullptr)
+                    kept_list.token[0] = out.token;
+                if (kept_list.probability != nullptr)
+                    kept_list.probability[0] = 1.0f;
+            }
+        }
         return out;
     }
     out.flags |= MOE_ROW_FLAG_USED_UNIFORM;
-    for (uint32_t i = tid; i < kept; i += kExactThreads)
+    const uint32_t kept_have = min(kept, have);
+    for (uint32_t i = tid; i < kept_have; i += kExactThreads)
         work[i] = __fdiv_rn(work[i], kept_total);
     __syncthreads();
-    const SeqResult draw = block_sequential_sum<kExactThreads, 4>(work, kept, kSeqExceedBound, uniform, sh.seq);
-    const uint32_t chosen = draw.stopped ? draw.taken - 1 : kept - 1; // session.cpp:441-442: the last candidate if the sum never passes the uniform
+    if (kept_list.count != nullptr)
+    {
+        if (tid == 0)
+            *kept_list.count = kept;
+        for (uint32_t i = tid; i < min(kept_have, kept_list.stride); i += kExactThreads)
+        {
+            if (kept_list.token != nullptr)
+                kept_list.token[i] = static_cast<int32_t>(record_index(records[i]));
+            if (kept_list.probability != nullptr)
+                kept_list.probability[i] = work[i];
+        }
+    }
+    const SeqResult draw = block_sequential_sum<kExactThreads, 4>(work, kept_have, kSeqExceedBound, uniform, sh.seq);
+    uint32_t chosen;
+    if (draw.stopped)
+        chosen = draw.taken - 1;
+    else if (kept <= have)
+        chosen = kept - 1; // session.cpp:441-442: the last candidate if the sum never passes the uniform
+    else
+    {
+        needs_full = true; // the last candidate of the list is a filtered one
+        return out;
+    }
     out.token = static_cast<int32_t>(record_index(records[chosen]));
     out.probability = work[chosen];
     return out;
@@ -349,104 +543,122 @@ __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys
     (void)slot_index;
 
     MOE_EXACT_BEGIN();
-    const uint32_t n = compact_finite<T>(row_pointer, a.vocab, items[0], sh);
+    // rows that list their Top-K ids need every rank up to top_k: no filter for them
+    const bool lists = a.topk_index != nullptr && p.top_k > 0 && p.top_k <= MOE_SAMPLER_TOPK_FAST_MAX;
+    uint32_t floor_key = dead_tail_floor<T>(row_pointer, a.vocab, p.temperature, sh);
     const bool has_pos_inf = sh.flag_pos_inf != 0;
-    MOE_EXACT_MARK(0);
+    const uint32_t finite_total = sh.finite_total;
+    if (lists)
+        floor_key = 0;
+    MOE_EXACT_MARK(4);
 
-    int source = 0;
-    if (n > 1 && !has_pos_inf)
+    RowOutcome out{MOE_ROW_OK, -1, 0.0f, 0u, false};
+    uint64_t* records = items[0];
+    uint32_t n = 0;
+    if (has_pos_inf || finite_total == 0)
     {
-        // A digit needs no pass when it is the same function of the higher digits
-        // for every key.  Keys (high words) are ~ordered_key(v): their low bytes are the
-        // magnitude bytes of v, complemented or not by the sign alone, so a byte
-        // on which all magnitudes agree (bf16 logits: the two low bytes) can be
-        // skipped.  (x ^ (x >> 31 ? 0 : ~0)) & 0x7FFFFFFF recovers the magnitude.
-        uint32_t any_bits = 0;
-        uint32_t all_bits = 0xFFFFFFFFu;
-        for (uint32_t i = tid; i < n; i += kExactThreads)
+        out.status = MOE_ROW_NO_FINITE_LOGIT;
+        if (a.kept_count != nullptr && tid == 0)
+            a.kept_count[row] = 0;
+    }
+    else
+    {
+        for (int attempt = 0; attempt < 2; ++attempt)
         {
-            const uint32_t key = static_cast<uint32_t>(items[0][i] >> 32);
-            const uint32_t magnitude = ((key & 0x80000000u) ? key : ~key) & 0x7FFFFFFFu;
-            const uint32_t probe = magnitude | (key & 0x80000000u);
-            any_bits |= probe;
-            all_bits &= probe;
-        }
-        any_bits = __reduce_or_sync(kFullMask, any_bits);
-        all_bits = __reduce_and_sync(kFullMask, all_bits);
-        if (lane == 0)
-        {
-            sh.warp_or[warp] = any_bits;
-            sh.warp_and[warp] = all_bits;
-        }
-        __syncthreads();
-        any_bits = 0;
-        all_bits = 0xFFFFFFFFu;
-        for (int w = 0; w < kExactWarps; ++w)
-        {
-            any_bits |= sh.warp_or[w];
-            all_bits &= sh.warp_and[w];
-        }
-        const uint32_t varying = any_bits ^ all_bits;
-        __syncthreads();
-        for (int shift = 0; shift < 32; shift += 8)
-        {
-            if (((varying >> shift) & 0xFFu) == 0)
-                continue;
-            radix_pass(items[source], items[1 - source], n, shift, sh);
-            source = 1 - source;
+            n = compact_live<T>(row_pointer, a.vocab, floor_key, items[0], sh);
+            MOE_EXACT_MARK(0);
+            int source = 0;
+            if (n > 1)
+            {
+                // A digit needs no pass when it is the same function of the higher digits
+                // for every key.  Keys (high words) are ~ordered_key(v): their low bytes are the
+                // magnitude bytes of v, complemented or not by the sign alone, so a byte
+                // on which all magnitudes agree (bf16 logits: the two low bytes) can be
+                // skipped.  (x ^ (x >> 31 ? 0 : ~0)) & 0x7FFFFFFF recovers the magnitude.
+                uint32_t any_bits = 0;
+                uint32_t all_bits = 0xFFFFFFFFu;
+                for (uint32_t i = tid; i < n; i += kExactThreads)
+                {
+                    const uint32_t key = static_cast<uint32_t>(items[0][i] >> 32);
+                    const uint32_t magnitude = ((key & 0x80000000u) ? key : ~key) & 0x7FFFFFFFu;
+                    const uint32_t probe = magnitude | (key & 0x80000000u);
+                    any_bits |= probe;
+                    all_bits &= probe;
+                }
+                any_bits = __reduce_or_sync(kFullMask, any_bits);
+                all_bits = __reduce_and_sync(kFullMask, all_bits);
+                if (lane == 0)
+                {
+                    sh.warp_or[warp] = any_bits;
+                    sh.warp_and[warp] = all_bits;
+                }
+                __syncthreads();
+                any_bits = 0;
+                all_bits = 0xFFFFFFFFu;
+                for (int w = 0; w < kExactWarps; ++w)
+                {
+                    any_bits |= sh.warp_or[w];
+                    all_bits &= sh.warp_and[w];
+                }
+                const uint32_t varying = any_bits ^ all_bits;
+                __syncthreads();
+                for (int shift = 0; shift < 32; shift += 8)
+                {
+                    if (((varying >> shift) & 0xFFu) == 0)
+                        continue;
+                    radix_pass(items[source], items[1 - source], n, shift, sh);
+                    source = 1 - source;
+                }
+            }
+            MOE_EXACT_MARK(1);
+            // complementing a sorted item gives the candidate record (ordered key, 0xFFFFFFFF - id);
+            // the other buffer is free and serves the epilogue's floats
+            records = items[source];
+            float* work = reinterpret_cast<float*>(items[1 - source]);
+            for (uint32_t i = tid; i < n; i += kExactThreads)
+                records[i] = ~records[i];
+            __syncthreads();
+            MOE_EXACT_MARK(2);
+
+            const float uniform = philox_uniform(p.seed, p.row_id, p.step + a.step_offset);
+            bool needs_full = false;
+            out = finish_row_exact_block(records, n, finite_total, work, p.temperature, p.top_k, p.top_p, p.min_p, uniform, sh, needs_full,
+                                         kept_list_of_row(a.kept_token, a.kept_probability, a.kept_count, a.kept_stride, row));
+            MOE_EXACT_MARK(3);
+            if (!needs_full || floor_key == 0)
+                break;
+            floor_key = 0; // the outcome hangs on a filtered candidate: once more with every finite logit
+            __syncthreads();
         }
     }
-
-    MOE_EXACT_MARK(1);
-    // complementing a sorted item gives the candidate record (ordered key, 0xFFFFFFFF - id);
-    // the other buffer is free and serves the epilogue's floats
-    uint64_t* records = items[source];
-    float* work = reinterpret_cast<float*>(items[1 - source]);
-    if (!has_pos_inf)
-    {
-        for (uint32_t i = tid; i < n; i += kExactThreads)
-            records[i] = ~records[i];
-    }
-    __syncthreads();
-    MOE_EXACT_MARK(2);
 
     if (a.topk_index != nullptr)
     {
         // same contract as the streaming kernel: the rank-ordered ids of a Top-K row, -1 elsewhere
-        const bool lists = !has_pos_inf && p.temperature != 0.0f && p.top_k > 0 && p.top_k <= MOE_SAMPLER_TOPK_FAST_MAX;
-        const uint32_t listed = lists ? min(n, p.top_k) : 0u;
+        const bool shown = lists && out.status != MOE_ROW_NO_FINITE_LOGIT && p.temperature != 0.0f;
+        const uint32_t listed = shown ? min(n, p.top_k) : 0u;
         for (uint32_t i = tid; i < a.topk_stride; i += kExactThreads)
             a.topk_index[static_cast<size_t>(row) * a.topk_stride + i] = (i < listed) ? static_cast<int32_t>(record_index(records[i])) : -1;
     }
 
+    if (tid == 0)
     {
-        RowOutcome out{MOE_ROW_OK, -1, 0.0f, 0u, false};
-        if (has_pos_inf || n == 0)
-        {
-            out.status = MOE_ROW_NO_FINITE_LOGIT;
-        }
-        else
-        {
-            const float uniform = philox_uniform(p.seed, p.row_id, p.step + a.step_offset);
-            out = finish_row_exact_block(records, n, work, p.temperature, p.top_k, p.top_p, p.min_p, uniform, sh);
-        }
-        if (tid == 0)
-        {
-            if (out.status == MOE_ROW_OK && is_stop_token(a.stop_offsets, a.stop_tokens, row, out.token))
-                out.flags |= MOE_ROW_FLAG_STOP_TOKEN;
-            a.token_id[row] = out.token;
-            a.probability[row] = out.probability;
-            if (a.row_flags != nullptr)
-                a.row_flags[row] = out.flags;
-            if (a.row_status != nullptr)
-                a.row_status[row] = out.status;
-        }
+        if (out.status == MOE_ROW_OK && is_stop_token(a.stop_offsets, a.stop_tokens, row, out.token))
+            out.flags |= MOE_ROW_FLAG_STOP_TOKEN;
+        a.token_id[row] = out.token;
+        a.probability[row] = out.probability;
+        if (a.row_flags != nullptr)
+            a.row_flags[row] = out.flags;
+        if (a.row_status != nullptr)
+            a.row_status[row] = out.status;
     }
     __syncthreads();
-    MOE_EXACT_MARK(3);
 #ifdef MOE_PHASE_TIMERS
     if (threadIdx.x == 0)
+    {
         atomicAdd(&g_exact_cycles[7], 1ull);
+        atomicAdd(&g_exact_cycles[5], static_cast<unsigned long long>(n));
+    }
 #endif
 }
 

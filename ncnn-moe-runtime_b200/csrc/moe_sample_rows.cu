@@ -908,6 +908,7 @@ __device__ __forceinline__ void finish_row_block(const SampleArgs& a, RowShared&
     if (tid < 32)
     {
         RowOutcome out{MOE_ROW_OK, -1, 0.0f, 0u, false};
+        const KeptList kept_list = kept_list_of_row(a.kept_token, a.kept_probability, a.kept_count, a.kept_stride, row);
         if (c.mode == kGreedy)
         {
             if (n == 0)
@@ -919,11 +920,23 @@ __device__ __forceinline__ void finish_row_block(const SampleArgs& a, RowShared&
                 out.token = static_cast<int32_t>(record_index(c.rec[0]));
                 out.probability = 1.0f;
             }
+            if (kept_list.count != nullptr && tid == 0)
+            {
+                // greedy builds no distribution (session.cpp:404-424): the chosen token stands alone
+                *kept_list.count = n == 0 ? 0u : 1u;
+                if (n != 0 && kept_list.stride > 0)
+                {
+                    if (kept_list.token != nullptr)
+                        kept_list.token[0] = out.token;
+                    if (kept_list.probability != nullptr)
+                        kept_list.probability[0] = 1.0f;
+                }
+            }
         }
         else
         {
             const float uniform = philox_uniform(p.seed, p.row_id, p.step + a.step_offset);
-            out = finish_row_warp(c.rec, n, c.work, p.temperature, p.top_k, p.top_p, p.min_p, uniform, c.mode == kLive);
+            out = finish_row_warp(c.rec, n, c.work, p.temperature, p.top_k, p.top_p, p.min_p, uniform, c.mode == kLive, kept_list);
         }
         if (tid == 0)
         {
@@ -964,6 +977,14 @@ __global__ void __launch_bounds__(kThreads, kResident) sample_rows_kernel(const 
     const int tid = threadIdx.x;
     const bool candidates_only = a.candidates_out != nullptr;
 
+    // Overlapped launches: the next launch on the stream may start as soon as
+    // every CTA of this one has started (all of them are then resident, so a
+    // dependent CTA that waits for this grid can never keep one of its CTAs
+    // off an SM).  Its CTAs fill the SM slots this grid leaves free and stream
+    // their own logits while this grid finishes.
+    if (a.overlap_previous)
+        grid_dependency_release();
+
     moe_row_params p;
     if (candidates_only)
     {
@@ -995,6 +1016,8 @@ __global__ void __launch_bounds__(kThreads, kResident) sample_rows_kernel(const 
                     a.row_flags[row] = 0;
                 if (a.row_status != nullptr)
                     a.row_status[row] = invalid;
+                if (a.kept_count != nullptr)
+                    a.kept_count[row] = 0;
             }
             if (a.topk_index != nullptr)
                 for (uint32_t i = tid; i < a.topk_stride; i += kThreads)
@@ -1056,15 +1079,12 @@ __global__ void __launch_bounds__(kThreads, kResident) sample_rows_kernel(const 
         atomicAdd(&g_phase_cycles[9], streamed ? 0ull : 1ull);
     }
 #endif
-    if (a.overlap_previous && streamed)
-        grid_dependency_release(); // this CTA has read its logits: the next launch may start filling free SM slots
     if (!streamed)
         stream_slice_safe<T>(c, row_pointer, vocab, head, 2u * vectors, tail_begin, 2u * group_begin, min(2u * group_end, (2u * vectors + kThreads - 1) / kThreads),
                              rank, splits); // the same logits in 16-byte vectors
     MOE_PHASE_MARK(2);
     if (a.overlap_previous)
     {
-        grid_dependency_release();
         // Everything up to here only read the logits and the row parameters.  The
         // slots, counters and outputs below may still be in use by the previous
         // launch: wait until it has completed.

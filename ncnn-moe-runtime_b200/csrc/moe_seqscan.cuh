@@ -166,6 +166,11 @@ __device__ __noinline__ SeqResult block_sequential_sum(const float* x, uint32_t 
         const int unit_exponent = acc_biased - 150; // acc = A * 2^unit_exponent, A in [2^23, 2^24)
         const uint32_t start_integer = (acc_bits & 0x7FFFFFu) | 0x800000u;
         const float unit = __uint_as_float(static_cast<uint32_t>(acc_biased - 23) << 23); // 2^(b-23), normal because acc_biased > 23
+        // The sequence does not increase and the accumulator does not decrease:
+        // once the next addend is below half a unit, no later add changes the
+        // accumulator (and no stop condition can fire any more).
+        if (x[position] < 0.5f * unit)
+            break;
 
         // my kItems consecutive elements
         float mine[kItems];
@@ -244,8 +249,9 @@ __device__ __noinline__ SeqResult block_sequential_sum(const float* x, uint32_t 
                 {
                     const float value = __uint2float_rn(next) * unit; // exact: next < 2^24, unit a power of two
                     if ((stop == kSeqReachBound && value >= bound) || (stop == kSeqExceedBound && bound < value))
-                        event = offset;
-                    running = next;
+                        event = offset; // `running` stays the integer before this element: its owner adds it below
+                    else
+                        running = next;
                 }
             }
         }

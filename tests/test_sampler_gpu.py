@@ -211,3 +211,89 @@ def test_overlapped_launches_give_the_same_results(pkg, workloads, parity, torch
         np.testing.assert_array_equal(alone[2]["token"].cpu().numpy(), want["token"])
     finally:
         sampler.close()
+
+
+def _check_kept_lists(pkg, parity, torch, logits, params, kept_stride):
+    """kept_count / kept_token / kept_probability against sampling_distribution of the oracle:
+    ids exact, probabilities within 1e-5 of the reference arithmetic and bit-exact against
+    the port run with the device's exp rounding; the sampled token agrees with the plain call."""
+    device_logits = parity.device_logits(logits)
+    rows = logits.shape[0]
+    sampler = pkg.Sampler(max_rows=rows, max_vocab=logits.shape[1])
+    try:
+        out = sampler.sample_batch(device_logits, params, kept_stride=kept_stride)
+        plain = sampler.sample_batch(device_logits, None)
+        torch.cuda.synchronize()
+        out = {k: v.cpu().numpy() for k, v in out.items() if v is not None}
+        np.testing.assert_array_equal(out["token"], plain["token"].cpu().numpy())
+        np.testing.assert_array_equal(out["probability"].view(np.uint32), plain["probability"].cpu().numpy().view(np.uint32))
+    finally:
+        sampler.close()
+    widened = logits if logits.dtype == np.float32 else (logits.astype(np.uint32) << 16).view(np.float32)
+    parity.port.set_exp_mode(1)
+    try:
+        for r in range(rows):
+            p = params[r]
+            if out["status"][r] != 0:
+                assert out["kept_count"][r] == 0
+                continue
+            if p["temperature"] == 0.0:
+                assert out["kept_count"][r] == 1 and out["kept_token"][r, 0] == out["token"][r] and out["kept_probability"][r, 0] == 1.0
+                continue
+            args = (widened[r], float(p["temperature"]), int(p["top_k"]), float(p["top_p"]), float(p["min_p"]))
+            ids, probabilities = parity.checker.distribution(*args)
+            count = int(out["kept_count"][r])
+            assert count == ids.size, (r, count, ids.size)
+            shown = min(count, kept_stride)
+            np.testing.assert_array_equal(out["kept_token"][r, :shown], ids[:shown], err_msg=f"row {r}")
+            np.testing.assert_allclose(out["kept_probability"][r, :shown], probabilities[:shown], rtol=1e-5, atol=0, err_msg=f"row {r}")
+            _, exact = parity.port.distribution(*args)
+            np.testing.assert_array_equal(out["kept_probability"][r, :shown].view(np.uint32), exact[:shown].view(np.uint32), err_msg=f"row {r}")
+            assert np.all(out["kept_token"][r, shown:] == -1)   # entries past the list stay untouched
+    finally:
+        parity.port.set_exp_mode(0)
+
+
+def test_kept_candidate_lists_match_sampling_distribution(pkg, workloads, parity, torch_cuda):
+    """moe_sample_batch_ex: the vector sampling_distribution returns (session.cpp:76-136), per row."""
+    logits, params = workloads.config3_mixed(pkg.ROW_PARAMS_DTYPE, rows=40, vocab=30011, seed=9)
+    params["temperature"][::9] = 0.0      # greedy rows list their token alone
+    params["top_p"][3] = 2.0              # a rejected row lists nothing
+    _check_kept_lists(pkg, parity, torch_cuda, logits, params, kept_stride=128)
+
+
+def test_kept_candidate_lists_on_golden_rows(pkg, parity, torch_cuda):
+    """The committed reference fixture holds full candidate lists for its first rows."""
+    from pathlib import Path
+    g = np.load(Path(__file__).parent / "golden" / "sampler_reference.npz")
+    rows = g["logits"].shape[0]
+    params = np.zeros(rows, dtype=pkg.ROW_PARAMS_DTYPE)
+    for name in ("temperature", "top_k", "top_p", "min_p"):
+        params[name] = g[name]
+    params["seed"], params["row_id"] = 5, np.arange(rows)
+    sampler = pkg.Sampler(max_rows=rows, max_vocab=g["logits"].shape[1])
+    try:
+        out = sampler.sample_batch(torch_cuda.from_numpy(g["logits"]).cuda(), params, kept_stride=g["logits"].shape[1])
+        torch_cuda.cuda.synchronize()
+        out = {k: v.cpu().numpy() for k, v in out.items() if v is not None}
+    finally:
+        sampler.close()
+    cursor = 0
+    checked = 0
+    for r, count in enumerate(g["dist_count"]):
+        if count < 0:
+            assert out["kept_count"][r] == 0 or params["temperature"][r] == 0.0
+            continue
+        assert out["kept_count"][r] == count
+        np.testing.assert_array_equal(out["kept_token"][r, :count], g["dist_ids"][cursor:cursor + count])
+        np.testing.assert_allclose(out["kept_probability"][r, :count], g["dist_probability"][cursor:cursor + count], rtol=1e-5, atol=0)
+        cursor += count
+        checked += 1
+    assert checked > 8
+
+
+def test_kept_candidate_lists_without_top_k(pkg, workloads, parity, torch_cuda):
+    """Rows without Top-K: short lists finish in the streaming kernel, long ones in the full-vocabulary kernel."""
+    logits, params = workloads.config2_greedy_temperature(pkg.ROW_PARAMS_DTYPE, rows=12, vocab=20011, seed=4)
+    params["top_p"][1::2] = np.linspace(0.3, 1.0, params["top_p"][1::2].size)
+    _check_kept_lists(pkg, parity, torch_cuda, logits, params, kept_stride=20011)
