@@ -170,9 +170,9 @@ int upload_rows(moe_sampler* sampler, cudaStream_t stream, uint32_t rows, const 
 }
 
 // Slices per row; MOE_B200_SPLITS (1, 2, 4 or 8) overrides the built-in policy for tuning runs.
-uint32_t pick_splits(const moe_sampler* sampler, uint32_t rows, uint32_t vocab, int dtype, bool large_top_k)
+uint32_t pick_splits(const moe_sampler* sampler, uint32_t rows, uint32_t vocab, int dtype, bool large_top_k, bool overlapped = false)
 {
-    uint32_t splits = choose_splits(rows, vocab, dtype, sampler->sm_count, sampler->ws.slice_slots, large_top_k);
+    uint32_t splits = choose_splits(rows, vocab, dtype, sampler->sm_count, sampler->ws.slice_slots, large_top_k, overlapped);
     if (const char* forced = std::getenv("MOE_B200_SPLITS"))
     {
         const long value = std::strtol(forced, nullptr, 10);
@@ -417,7 +417,7 @@ int moe_sample_batch_ex(moe_sampler* sampler, void* stream_handle, const void* l
     args.kept_stride = outputs->kept_count != nullptr ? outputs->kept_stride : 0;
     args.large_top_k = sampler->resident_large_top_k;
     args.overlap_previous = sampler->overlap_launches;
-    const uint32_t splits = pick_splits(sampler, rows, vocab, dtype, args.large_top_k);
+    const uint32_t splits = pick_splits(sampler, rows, vocab, dtype, args.large_top_k, args.overlap_previous);
     MOE_CUDA_CHECK(sampler, launch_sample_rows(args, sampler->ws, splits, stream));
     if (sampler->resident_needs_exact)
         MOE_CUDA_CHECK(sampler, launch_sample_exact(args, sampler->ws, stream));

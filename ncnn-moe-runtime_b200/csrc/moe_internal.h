@@ -96,6 +96,6 @@ cudaError_t launch_router_dispatch_kernels(const RouterArgs& args, uint32_t* exp
 cudaError_t launch_regroup_gather(const float* hidden, uint32_t columns, const uint32_t* route_token, uint32_t route_count, float* gathered,
                                   cudaStream_t stream);
 
-uint32_t choose_splits(uint32_t rows, uint32_t vocab, int dtype, int sm_count, uint32_t slice_slots, bool large_top_k);
+uint32_t choose_splits(uint32_t rows, uint32_t vocab, int dtype, int sm_count, uint32_t slice_slots, bool large_top_k, bool overlapped);
 
 } // namespace moe
