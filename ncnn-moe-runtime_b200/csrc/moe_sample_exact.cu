@@ -20,13 +20,13 @@
 
 #ifdef MOE_PHASE_TIMERS
 // Debug builds only: cycles per phase of the exact kernel, summed over rows.
-__device__ unsigned long long g_exact_cycles[8];
+__device__ unsigned long long g_exact_cycles[16];
 extern "C" void moe_debug_exact_cycles(unsigned long long* out, int reset)
 {
-    cudaMemcpyFromSymbol(out, g_exact_cycles, sizeof(unsigned long long) * 8);
+    cudaMemcpyFromSymbol(out, g_exact_cycles, sizeof(unsigned long long) * 16);
     if (reset)
     {
-        unsigned long long zeros[8] = {};
+        unsigned long long zeros[16] = {};
         cudaMemcpyToSymbol(g_exact_cycles, zeros, sizeof(zeros));
     }
 }
@@ -52,6 +52,7 @@ namespace {
 
 constexpr int kExactThreads = 1024;
 constexpr int kExactWarps = kExactThreads / 32;
+constexpr int kSeqItems = 8; // elements per thread and scan step of the sequential sums
 
 struct ExactShared
 {
@@ -281,7 +282,7 @@ __device__ uint32_t compact_live(const T* row, uint32_t vocab, uint32_t floor_ke
 
 // One stable counting-sort pass on an 8-bit digit.  Each warp owns a contiguous
 // segment of the input, so input order is preserved inside every digit.
-__device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32_t n, int shift, ExactShared& sh)
+__device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32_t n, int shift, bool complement_output, ExactShared& sh)
 {
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -383,7 +384,7 @@ __device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32
             if (valid)
             {
                 const uint32_t slot = sh.warp_hist[warp][digit] + __popc(peers & ((1u << lane) - 1u));
-                items_out[slot] = item[u]; // one 8-byte store per item
+                items_out[slot] = complement_output ? ~item[u] : item[u]; // one 8-byte store per item
             }
             __syncwarp();
             if (valid && lane == (__ffs(peers) - 1))
@@ -429,11 +430,14 @@ __device__ RowOutcome finish_row_exact_block(const uint64_t* records, uint32_t p
     const uint32_t listed = (top_k > 0 && top_k < finite_total) ? top_k : finite_total;
     const uint32_t have = min(present, listed); // candidates of the list whose records exist
 
+    MOE_EXACT_BEGIN();
     const float peak = __fdiv_rn(key_to_float(head_key), temperature);
     for (uint32_t i = tid; i < have; i += kExactThreads)
         work[i] = exact_expf(scaled_offset(key_to_float(record_key(records[i])), temperature, peak));
     __syncthreads();
-    const float total = block_sequential_sum<kExactThreads, 4>(work, have, kSeqSumOnly, 0.0f, sh.seq).acc;
+    MOE_EXACT_MARK(8);
+    const float total = block_sequential_sum<kExactThreads, kSeqItems>(work, have, kSeqSumOnly, 0.0f, sh.seq).acc;
+    MOE_EXACT_MARK(9);
     if (!(total - total == 0.0f) || total <= 0.0f)
     {
         out.status = MOE_ROW_INVALID_DISTRIBUTION;
@@ -469,8 +473,10 @@ __device__ RowOutcome finish_row_exact_block(const uint64_t* records, uint32_t p
             return out;
         }
     }
+    MOE_EXACT_MARK(10);
     // Top-P: first prefix whose running sum reaches top_p; never reached: the whole list stays
-    const SeqResult nucleus = block_sequential_sum<kExactThreads, 4>(work, min(allowed, have), kSeqReachBound, top_p, sh.seq);
+    const SeqResult nucleus = block_sequential_sum<kExactThreads, kSeqItems>(work, min(allowed, have), kSeqReachBound, top_p, sh.seq);
+    MOE_EXACT_MARK(11);
     const uint32_t kept = nucleus.stopped ? nucleus.taken : allowed;
     // the renormaliser (session.cpp:130-132) repeats the adds of the Top-P loop over the same prefix from the same zero
     const float kept_total = nucleus.acc;
@@ -513,7 +519,9 @@ __device__ RowOutcome finish_row_exact_block(const uint64_t* records, uint32_t p
                 kept_list.probability[i] = work[i];
         }
     }
-    const SeqResult draw = block_sequential_sum<kExactThreads, 4>(work, kept_have, kSeqExceedBound, uniform, sh.seq);
+    MOE_EXACT_MARK(12);
+    const SeqResult draw = block_sequential_sum<kExactThreads, kSeqItems>(work, kept_have, kSeqExceedBound, uniform, sh.seq);
+    MOE_EXACT_MARK(13);
     uint32_t chosen;
     if (draw.stopped)
         chosen = draw.taken - 1;
@@ -568,6 +576,7 @@ __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys
             n = compact_live<T>(row_pointer, a.vocab, floor_key, items[0], sh);
             MOE_EXACT_MARK(0);
             int source = 0;
+            bool complemented = false;
             if (n > 1)
             {
                 // A digit needs no pass when it is the same function of the higher digits
@@ -602,22 +611,31 @@ __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys
                 }
                 const uint32_t varying = any_bits ^ all_bits;
                 __syncthreads();
+                // complementing a sorted item gives the candidate record (ordered key,
+                // 0xFFFFFFFF - id); the last pass stores the complement directly
+                int last_shift = -1;
+                for (int shift = 0; shift < 32; shift += 8)
+                    if (((varying >> shift) & 0xFFu) != 0)
+                        last_shift = shift;
                 for (int shift = 0; shift < 32; shift += 8)
                 {
                     if (((varying >> shift) & 0xFFu) == 0)
                         continue;
-                    radix_pass(items[source], items[1 - source], n, shift, sh);
+                    radix_pass(items[source], items[1 - source], n, shift, shift == last_shift, sh);
                     source = 1 - source;
+                    complemented = shift == last_shift;
                 }
             }
             MOE_EXACT_MARK(1);
-            // complementing a sorted item gives the candidate record (ordered key, 0xFFFFFFFF - id);
             // the other buffer is free and serves the epilogue's floats
             records = items[source];
             float* work = reinterpret_cast<float*>(items[1 - source]);
-            for (uint32_t i = tid; i < n; i += kExactThreads)
-                records[i] = ~records[i];
-            __syncthreads();
+            if (!complemented)
+            {
+                for (uint32_t i = tid; i < n; i += kExactThreads)
+                    records[i] = ~records[i];
+                __syncthreads();
+            }
             MOE_EXACT_MARK(2);
 
             const float uniform = philox_uniform(p.seed, p.row_id, p.step + a.step_offset);

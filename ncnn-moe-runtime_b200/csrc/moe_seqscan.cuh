@@ -61,47 +61,18 @@ __device__ __forceinline__ void seq_compose(uint32_t a0, uint32_t a1, uint32_t b
     r1 = seq_clamp(a1 + (((1u + a1) & 1u) ? b1 : b0));
 }
 
-// Integer step of one addend against the unit u = 2^unit_exponent (unbiased):
+// Integer step of one non-negative addend x <= acc against the unit u of the
+// accumulator, given 1/u (a power of two, so x / u is exact):
 // d0 / d1 = step when the accumulator's integer is even / odd.
-__device__ __forceinline__ void seq_element(float x, int unit_exponent, uint32_t& d0, uint32_t& d1)
+__device__ __forceinline__ void seq_element(float x, float inverse_unit, uint32_t& d0, uint32_t& d1)
 {
-    const uint32_t bits = __float_as_uint(x);
-    const int biased = static_cast<int>((bits >> 23) & 0xFFu);
-    uint32_t mantissa = bits & 0x7FFFFFu;
-    int exponent; // x = mantissa * 2^exponent
-    if (biased == 0)
-        exponent = -149; // zero or subnormal
-    else
-    {
-        mantissa |= 0x800000u;
-        exponent = biased - 150;
-    }
-    const int shift = exponent - unit_exponent;
-    uint32_t q = 0;
-    int fraction = 0; // 0 below one half, 1 exactly one half, 2 above
-    if (mantissa != 0)
-    {
-        if (shift >= 0)
-        {
-            q = (shift < 8) ? (mantissa << shift) : kSeqSaturate; // callers guarantee x <= acc, so this stays < 2^24 or saturates
-            if (q > kSeqSaturate)
-                q = kSeqSaturate;
-        }
-        else
-        {
-            const int s = -shift;
-            if (s <= 24)
-            {
-                q = mantissa >> s;
-                const uint32_t rest = mantissa & ((1u << s) - 1u);
-                const uint32_t half = 1u << (s - 1);
-                fraction = rest > half ? 2 : (rest == half ? 1 : 0);
-            }
-            // s >= 25: x < u / 2, no effect
-        }
-    }
-    d0 = q + (fraction == 2 ? 1u : (fraction == 1 ? (q & 1u) : 0u));
-    d1 = q + (fraction == 2 ? 1u : (fraction == 1 ? ((q + 1u) & 1u) : 0u));
+    const float scaled = __fmul_rn(x, inverse_unit);          // exact; below 2^24 because x <= acc
+    const uint32_t q = min(__float2uint_rz(scaled), kSeqSaturate);
+    const float fraction = __fsub_rn(scaled, __uint2float_rn(q)); // exact (q < 2^24 on every path that uses it)
+    const uint32_t up = fraction > 0.5f ? 1u : 0u;
+    const uint32_t tie = fraction == 0.5f ? 1u : 0u;
+    d0 = q + up + (tie & q);        // tie: round to the even integer
+    d1 = q + up + (tie & (q + 1u));
 }
 
 // All threads of the block call this with the same arguments; x[0..n) is
@@ -163,9 +134,9 @@ __device__ __noinline__ SeqResult block_sequential_sum(const float* x, uint32_t 
             }
             continue;
         }
-        const int unit_exponent = acc_biased - 150; // acc = A * 2^unit_exponent, A in [2^23, 2^24)
         const uint32_t start_integer = (acc_bits & 0x7FFFFFu) | 0x800000u;
         const float unit = __uint_as_float(static_cast<uint32_t>(acc_biased - 23) << 23); // 2^(b-23), normal because acc_biased > 23
+        const float inverse_unit = __uint_as_float(static_cast<uint32_t>(277 - acc_biased) << 23); // 2^(23-b), normal for the same reason
         // The sequence does not increase and the accumulator does not decrease:
         // once the next addend is below half a unit, no later add changes the
         // accumulator (and no stop condition can fire any more).
@@ -174,7 +145,6 @@ __device__ __noinline__ SeqResult block_sequential_sum(const float* x, uint32_t 
 
         // my kItems consecutive elements
         float mine[kItems];
-        uint32_t e0[kItems], e1[kItems];
         uint32_t t0 = 0, t1 = 0; // composed over my elements
         const uint32_t first = tid * kItems;
 #pragma unroll
@@ -182,15 +152,20 @@ __device__ __noinline__ SeqResult block_sequential_sum(const float* x, uint32_t 
         {
             const uint32_t offset = first + j;
             mine[j] = (offset < chunk) ? x[position + offset] : 0.0f;
-            seq_element(mine[j], unit_exponent, e0[j], e1[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < kItems; ++j)
+        {
+            uint32_t e0, e1;
+            seq_element(mine[j], inverse_unit, e0, e1);
             if (j == 0)
             {
-                t0 = e0[0];
-                t1 = e1[0];
+                t0 = e0;
+                t1 = e1;
             }
             else
             {
-                seq_compose(t0, t1, e0[j], e1[j], t0, t1);
+                seq_compose(t0, t1, e0, e1, t0, t1);
             }
         }
         // inclusive scan of the thread aggregates across the warp
@@ -214,16 +189,30 @@ __device__ __noinline__ SeqResult block_sequential_sum(const float* x, uint32_t 
             sh.stopped = 0;
         }
         __syncthreads();
-        // step sum of everything before my warp, for the actual start parity
+        // step sum of everything before my warp, for the actual start parity:
+        // every warp scans the warps' pairs with shuffles (lane w holds warp w)
         const uint32_t start_parity = start_integer & 1u;
         uint32_t before = 0; // integer steps taken before my first element
         {
-            uint32_t parity = start_parity;
-            for (uint32_t w = 0; w < warp; ++w)
+            constexpr uint32_t kWarps = kThreads / 32;
+            uint32_t w0 = lane < kWarps ? sh.warp_pair[lane][0] : 0u;
+            uint32_t w1 = lane < kWarps ? sh.warp_pair[lane][1] : 0u;
+#pragma unroll
+            for (int offset = 1; offset < 32; offset <<= 1)
             {
-                const uint32_t d = sh.warp_pair[w][parity];
-                before = seq_clamp(before + d);
-                parity = (parity + d) & 1u;
+                const uint32_t p0 = __shfl_up_sync(kFullMask, w0, offset);
+                const uint32_t p1 = __shfl_up_sync(kFullMask, w1, offset);
+                if (lane >= static_cast<uint32_t>(offset))
+                    seq_compose(p0, p1, w0, w1, w0, w1);
+            }
+            // inclusive pair of the warps up to warp - 1
+            const uint32_t prior0 = __shfl_sync(kFullMask, w0, warp == 0 ? 0 : warp - 1);
+            const uint32_t prior1 = __shfl_sync(kFullMask, w1, warp == 0 ? 0 : warp - 1);
+            uint32_t parity = start_parity;
+            if (warp > 0)
+            {
+                before = start_parity ? prior1 : prior0;
+                parity = (start_parity + before) & 1u;
             }
             // lanes before me inside the warp
             const uint32_t x0 = __shfl_up_sync(kFullMask, s0, 1);
@@ -240,7 +229,9 @@ __device__ __noinline__ SeqResult block_sequential_sum(const float* x, uint32_t 
             const uint32_t offset = first + j;
             if (offset < chunk && event == 0xFFFFFFFFu)
             {
-                const uint32_t next = seq_clamp(running + ((running & 1u) ? e1[j] : e0[j]));
+                uint32_t e0, e1; // recomputed rather than kept: registers are the scarce resource here
+                seq_element(mine[j], inverse_unit, e0, e1);
+                const uint32_t next = seq_clamp(running + ((running & 1u) ? e1 : e0));
                 if (running >= (1u << 24) || next >= (1u << 24))
                 {
                     event = offset; // carry out of the binade at this element (or already before it)
