@@ -47,7 +47,10 @@ enum moe_row_status
     MOE_ROW_BAD_MIN_P = 4,           /* "min_p must be in the range [0, 1]" */
     MOE_ROW_NO_FINITE_LOGIT = 5,     /* "sampling requires at least one finite logit" */
     MOE_ROW_INVALID_DISTRIBUTION = 6,/* "sampling distribution is invalid" */
-    MOE_ROW_WORKSPACE_EXHAUSTED = 7  /* library limit, no reference counterpart */
+    MOE_ROW_WORKSPACE_EXHAUSTED = 7, /* library limit, no reference counterpart */
+    /* speculative verification only (ErrorCode::InternalError in the reference) */
+    MOE_ROW_DRAFT_ZERO_PROBABILITY = 8, /* "sampled draft token has zero probability", session.cpp:813-821 */
+    MOE_ROW_RESIDUAL_EMPTY = 9          /* "speculative residual distribution is empty", session.cpp:169-174 */
 };
 
 enum moe_dtype
@@ -169,6 +172,45 @@ typedef struct moe_sample_outputs
 int moe_sample_batch_ex(moe_sampler* sampler, void* stream, const void* logits, int dtype, uint32_t rows, uint32_t vocab,
                         size_t row_stride, const moe_row_params* params, uint64_t step_offset, const int32_t* stop_offsets,
                         const int32_t* stop_tokens, const moe_sample_outputs* outputs);
+
+/* The verification step of speculative decoding for one Session
+ * (the loop of Session::generate, src/engine/session.cpp:776-880): the
+ * `draft_count` proposed tokens are walked in order, each accepted with
+ * probability min(1, p_target / p_draft) where both probabilities come from
+ * sampling_distribution of that position's target and draft logits under the
+ * Session's options (candidate_probability, :138-148); temperature 0 accepts
+ * while the target's greedy token equals the proposal (:778-794).  The token
+ * after the accepted prefix is a draw from the residual distribution
+ * max(0, target - draft) of the rejected position, summed in token-id order
+ * (sample_residual_distribution, :150-202), or the ordinary sample of the next
+ * target row when nothing was rejected or temperature is 0 (:871-874).
+ * Uniforms are Philox(seed, row_id, step), step advancing by one per consumed
+ * uniform exactly as the Session's generator would advance.
+ *
+ * target_logits   device, [(draft_count + 1) x row_stride] of `dtype`
+ * draft_logits    device, [draft_count x row_stride]
+ * proposed_tokens device, draft_count token ids
+ * params          HOST, ONE entry: the Session's options and its (seed, row_id, step)
+ * accepted_probability  device, draft_count floats: the probability reported
+ *                 for each accepted token (target probability; 1 when greedy)
+ * result          device
+ * draft_count <= MOE_SPECULATIVE_MAX_DRAFT and 2 * draft_count + 1 <= the
+ * handle's max_rows.  The call replaces the handle's resident row parameters
+ * and allocates its scratch on first use.  Asynchronous on `stream`. */
+#define MOE_SPECULATIVE_MAX_DRAFT 16u
+typedef struct moe_speculative_result
+{
+    uint32_t accepted;       /* proposed tokens accepted, 0..draft_count */
+    int32_t next_token;      /* the token emitted after them, -1 on error */
+    float next_probability;
+    uint32_t uniforms_used;  /* add to the Session's step */
+    int32_t status;          /* MOE_ROW_OK or the status of the position that failed */
+    uint32_t flags;          /* reserved, 0 */
+} moe_speculative_result;
+
+int moe_speculative_verify(moe_sampler* sampler, void* stream, const void* target_logits, const void* draft_logits, int dtype,
+                           uint32_t draft_count, uint32_t vocab, size_t row_stride, const int32_t* proposed_tokens,
+                           const moe_row_params* params, float* accepted_probability, moe_speculative_result* result);
 
 /* Same operation with every buffer in HOST memory (what a Session-shaped
  * caller holds: LogitsOutput::values is a std::vector<float>, session.h:30-33).

@@ -20,6 +20,11 @@ HERE = Path(__file__).resolve().parent
 LIBRARY_PATH = HERE / "libmoe_b200_sampler.so"
 
 
+SPECULATIVE_RESULT_DTYPE = np.dtype([("accepted", np.uint32), ("next_token", np.int32), ("next_probability", np.float32),
+                                     ("uniforms_used", np.uint32), ("status", np.int32), ("flags", np.uint32)])
+SPECULATIVE_MAX_DRAFT = 16
+
+
 class SampleOutputs(C.Structure):
     """moe_sample_outputs of include/moe_b200_sampler.h."""
     _fields_ = [("token_id", C.c_void_p), ("probability", C.c_void_p), ("row_flags", C.c_void_p), ("row_status", C.c_void_p),
@@ -48,7 +53,7 @@ class RouterOptions(C.Structure):
 
 EXPORTED_SYMBOLS = [
     "moe_sampler_create", "moe_sampler_destroy", "moe_sampler_last_error", "moe_row_status_message", "moe_row_status_error_code",
-    "moe_philox_uniform", "moe_host_alloc", "moe_host_free", "moe_sample_batch", "moe_sample_batch_ex", "moe_sample_batch_host",
+    "moe_philox_uniform", "moe_host_alloc", "moe_host_free", "moe_sample_batch", "moe_sample_batch_ex", "moe_speculative_verify", "moe_sample_batch_host",
     "moe_sample_local_candidates", "moe_sample_merge_candidates", "moe_router_dispatch", "moe_router_status_message",
     "moe_router_status_error_code", "moe_router_check_options", "moe_router_dispatch_host", "moe_regroup_gather",
     "moe_router_dispatch_static", "moe_sampler_set_overlap",
@@ -89,6 +94,7 @@ def library() -> C.CDLL:
     lib.moe_host_free.restype = None
     lib.moe_sample_batch.argtypes = [vp, vp, vp, C.c_int, u32, u32, sz, vp, u64, vp, vp, vp, vp, vp, vp, vp, u32]
     lib.moe_sample_batch_ex.argtypes = [vp, vp, vp, C.c_int, u32, u32, sz, vp, u64, vp, vp, C.POINTER(SampleOutputs)]
+    lib.moe_speculative_verify.argtypes = [vp, vp, vp, vp, C.c_int, u32, u32, sz, vp, vp, vp, vp]
     lib.moe_sample_batch_host.argtypes = [vp, vp, C.c_int, u32, u32, sz, vp, vp, vp, vp, vp, vp, vp, vp, u32]
     lib.moe_sample_local_candidates.argtypes = [vp, vp, vp, C.c_int, u32, u32, sz, u32, u32, vp]
     lib.moe_sample_merge_candidates.argtypes = [vp, vp, vp, u32, u32, u32, vp, u64, vp, vp, vp, vp, vp, u32]
@@ -229,6 +235,32 @@ class Sampler:
                                                _np_ptr(params), int(step_offset), _np_ptr(offsets), _np_ptr(tokens), _dev_ptr(out["token"]),
                                                _dev_ptr(out["probability"]), _dev_ptr(out["flags"]), _dev_ptr(out["status"]),
                                                _dev_ptr(out.get("topk")), int(topk_stride)))
+        return out
+
+    def speculative_verify(self, target_logits, draft_logits, proposed, params, stream=None):
+        """Verification step of speculative decoding for one Session (moe_speculative_verify).
+        target_logits: CUDA [draft_count + 1, row_stride]; draft_logits: CUDA [draft_count, row_stride];
+        proposed: CUDA int32 [draft_count]; params: one ROW_PARAMS_DTYPE entry.
+        Returns dict(accepted, next_token, next_probability, uniforms_used, status, accepted_probability) on the host."""
+        import torch
+        draft_count = int(proposed.numel())
+        rows, row_stride = target_logits.shape
+        assert rows == draft_count + 1
+        dtype = DTYPE_F32 if target_logits.dtype == torch.float32 else DTYPE_BF16
+        device = target_logits.device
+        params = np.ascontiguousarray(params, dtype=ROW_PARAMS_DTYPE).reshape(1)
+        accepted_probability = torch.zeros(max(draft_count, 1), dtype=torch.float32, device=device)
+        result = torch.zeros(SPECULATIVE_RESULT_DTYPE.itemsize, dtype=torch.uint8, device=device)
+        stream_handle = torch.cuda.current_stream(device).cuda_stream if stream is None else stream
+        self._check(self._lib.moe_speculative_verify(self._handle, C.c_void_p(stream_handle), _dev_ptr(target_logits),
+                                                     _dev_ptr(draft_logits) if draft_count else None, dtype, draft_count, row_stride,
+                                                     target_logits.stride(0), _dev_ptr(proposed) if draft_count else None, _np_ptr(params),
+                                                     _dev_ptr(accepted_probability), _dev_ptr(result)))
+        torch.cuda.synchronize(device)
+        record = result.cpu().numpy().view(SPECULATIVE_RESULT_DTYPE)[0]
+        out = {name: record[name].item() for name in SPECULATIVE_RESULT_DTYPE.names}
+        out["next_probability"] = np.float32(record["next_probability"])
+        out["accepted_probability"] = accepted_probability.cpu().numpy()[:out["accepted"]]
         return out
 
     # ---- host buffers (numpy) ----------------------------------------------------

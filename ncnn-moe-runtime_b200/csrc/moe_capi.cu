@@ -43,6 +43,19 @@ struct moe_sampler
     int32_t* topk_dev = nullptr;
     size_t topk_dev_entries = 0;
 
+    // speculative verification scratch (allocated on first use)
+    int32_t* spec_kept_token = nullptr;
+    float* spec_kept_probability = nullptr;
+    uint32_t* spec_kept_count = nullptr;
+    int32_t* spec_token = nullptr;
+    float* spec_probability = nullptr;
+    uint32_t* spec_flags = nullptr;
+    int32_t* spec_status = nullptr;
+    float* spec_dense = nullptr;
+    int32_t* spec_residual_token = nullptr;
+    float* spec_residual_value = nullptr;
+    uint32_t spec_rows = 0;
+
     // router scratch
     uint32_t* selected_expert = nullptr;
     float* selected_weight = nullptr;
@@ -285,7 +298,9 @@ void moe_sampler_destroy(moe_sampler* sampler)
                         sampler->status_dev, sampler->topk_dev, sampler->selected_expert, sampler->selected_weight, sampler->expert_counts,
                         sampler->router_error, sampler->router_logits_dev, sampler->router_bias_dev, sampler->router_explicit_dev,
                         sampler->router_offsets_dev, sampler->router_token_dev, sampler->router_rank_dev, sampler->router_weight_dev,
-                        sampler->router_status_dev};
+                        sampler->router_status_dev, sampler->spec_kept_token, sampler->spec_kept_probability, sampler->spec_kept_count,
+                        sampler->spec_token, sampler->spec_probability, sampler->spec_flags, sampler->spec_status, sampler->spec_dense,
+                        sampler->spec_residual_token, sampler->spec_residual_value};
     for (void* pointer : pointers)
         if (pointer != nullptr)
             cudaFree(pointer);
@@ -319,6 +334,8 @@ const char* moe_row_status_message(int row_status)
     case MOE_ROW_NO_FINITE_LOGIT: return "sampling requires at least one finite logit";
     case MOE_ROW_INVALID_DISTRIBUTION: return "sampling distribution is invalid";
     case MOE_ROW_WORKSPACE_EXHAUSTED: return "row does not fit the sampler workspace";
+    case MOE_ROW_DRAFT_ZERO_PROBABILITY: return "sampled draft token has zero probability";
+    case MOE_ROW_RESIDUAL_EMPTY: return "speculative residual distribution is empty";
     default: return "unknown row status";
     }
 }
@@ -327,7 +344,7 @@ int moe_row_status_error_code(int row_status)
 {
     if (row_status == MOE_ROW_OK)
         return MOE_STATUS_OK;
-    if (row_status == MOE_ROW_WORKSPACE_EXHAUSTED)
+    if (row_status == MOE_ROW_WORKSPACE_EXHAUSTED || row_status == MOE_ROW_DRAFT_ZERO_PROBABILITY || row_status == MOE_ROW_RESIDUAL_EMPTY)
         return MOE_STATUS_INTERNAL_ERROR;
     return MOE_STATUS_INVALID_ARGUMENT;
 }
@@ -421,6 +438,97 @@ int moe_sample_batch_ex(moe_sampler* sampler, void* stream_handle, const void* l
     MOE_CUDA_CHECK(sampler, launch_sample_rows(args, sampler->ws, splits, stream));
     if (sampler->resident_needs_exact)
         MOE_CUDA_CHECK(sampler, launch_sample_exact(args, sampler->ws, stream));
+    return MOE_STATUS_OK;
+}
+
+int moe_speculative_verify(moe_sampler* sampler, void* stream_handle, const void* target_logits, const void* draft_logits, int dtype,
+                           uint32_t draft_count, uint32_t vocab, size_t row_stride, const int32_t* proposed_tokens,
+                           const moe_row_params* params, float* accepted_probability, moe_speculative_result* result)
+{
+    const uint32_t rows = 2u * draft_count + 1u;
+    if (int status = check_shape(sampler, dtype, rows, vocab, row_stride))
+        return status;
+    if (draft_count > MOE_SPECULATIVE_MAX_DRAFT)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "draft_count exceeds MOE_SPECULATIVE_MAX_DRAFT");
+    if (target_logits == nullptr || params == nullptr || result == nullptr ||
+        (draft_count > 0 && (draft_logits == nullptr || proposed_tokens == nullptr || accepted_probability == nullptr)))
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "target_logits, draft_logits, proposed_tokens, params, accepted_probability and result must not be null");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+    DeviceGuard guard(sampler->device);
+    const uint32_t capacity_rows = 2u * MOE_SPECULATIVE_MAX_DRAFT + 1u;
+    if (sampler->spec_rows == 0)
+    {
+        const size_t list_entries = static_cast<size_t>(capacity_rows) * sampler->max_vocab;
+        const auto reserve = [](auto*& pointer, size_t entries) {
+            size_t capacity = 0;
+            return grow(pointer, capacity, entries);
+        };
+        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_kept_token, list_entries));
+        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_kept_probability, list_entries));
+        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_kept_count, capacity_rows));
+        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_token, capacity_rows));
+        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_probability, capacity_rows));
+        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_flags, capacity_rows));
+        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_status, capacity_rows));
+        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_dense, sampler->max_vocab));
+        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_residual_token, sampler->max_vocab));
+        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_residual_value, sampler->max_vocab));
+        sampler->spec_rows = capacity_rows;
+    }
+    // every position samples under the Session's options; the target rows come first
+    std::vector<moe_row_params> row_params(draft_count + 1u, params[0]);
+    if (int status = upload_rows(sampler, stream, draft_count + 1u, row_params.data(), nullptr, nullptr))
+        return status;
+
+    const uint32_t kept_stride = sampler->max_vocab;
+    SampleArgs args = {};
+    args.dtype = dtype;
+    args.vocab = vocab;
+    args.row_stride = row_stride;
+    args.params = sampler->params_dev;
+    // the one sample that can be used is that of the target row after all proposals,
+    // which the Session would draw with its uniform number draft_count of this step
+    args.step_offset = draft_count;
+    args.large_top_k = sampler->resident_large_top_k;
+    for (int side = 0; side < 2; ++side)
+    {
+        const uint32_t first = side == 0 ? 0u : draft_count + 1u;
+        args.logits = side == 0 ? target_logits : draft_logits;
+        args.rows = side == 0 ? draft_count + 1u : draft_count;
+        if (args.rows == 0)
+            continue;
+        args.token_id = sampler->spec_token + first;
+        args.probability = sampler->spec_probability + first;
+        args.row_flags = sampler->spec_flags + first;
+        args.row_status = sampler->spec_status + first;
+        args.kept_token = sampler->spec_kept_token + static_cast<size_t>(first) * kept_stride;
+        args.kept_probability = sampler->spec_kept_probability + static_cast<size_t>(first) * kept_stride;
+        args.kept_count = sampler->spec_kept_count + first;
+        args.kept_stride = kept_stride;
+        const uint32_t splits = pick_splits(sampler, args.rows, vocab, dtype, args.large_top_k);
+        MOE_CUDA_CHECK(sampler, launch_sample_rows(args, sampler->ws, splits, stream));
+        if (sampler->resident_needs_exact)
+            MOE_CUDA_CHECK(sampler, launch_sample_exact(args, sampler->ws, stream));
+    }
+    SpeculativeArgs verify = {};
+    verify.draft_count = draft_count;
+    verify.vocab = vocab;
+    verify.params = sampler->params_dev;
+    verify.proposed = proposed_tokens;
+    verify.token = sampler->spec_token;
+    verify.probability = sampler->spec_probability;
+    verify.row_flags = sampler->spec_flags;
+    verify.row_status = sampler->spec_status;
+    verify.kept_token = sampler->spec_kept_token;
+    verify.kept_probability = sampler->spec_kept_probability;
+    verify.kept_count = sampler->spec_kept_count;
+    verify.kept_stride = kept_stride;
+    verify.dense = sampler->spec_dense;
+    verify.residual_token = sampler->spec_residual_token;
+    verify.residual_value = sampler->spec_residual_value;
+    verify.accepted_probability = accepted_probability;
+    verify.result = result;
+    MOE_CUDA_CHECK(sampler, launch_speculative_verify(verify, stream));
     return MOE_STATUS_OK;
 }
 

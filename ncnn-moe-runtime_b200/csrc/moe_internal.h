@@ -78,6 +78,31 @@ cudaError_t launch_merge_candidates(const uint64_t* gathered, uint32_t shards, u
                                     uint64_t step_offset, int32_t* token_id, float* probability, uint32_t* row_flags, int32_t* row_status,
                                     int32_t* topk_index, uint32_t topk_stride, cudaStream_t stream);
 
+// Speculative verification: rows 0..draft_count of the row outputs and kept
+// lists are the target positions, rows draft_count+1..2*draft_count the draft positions.
+struct SpeculativeArgs
+{
+    uint32_t draft_count;
+    uint32_t vocab;
+    const moe_row_params* params; // device, entry 0 = the Session's options and counters
+    const int32_t* proposed;      // device
+    const int32_t* token;         // per-row sampler outputs
+    const float* probability;
+    const uint32_t* row_flags;
+    const int32_t* row_status;
+    const int32_t* kept_token;
+    const float* kept_probability;
+    const uint32_t* kept_count;
+    uint32_t kept_stride;
+    float* dense;             // [vocab] scratch: the residual by token id
+    int32_t* residual_token;  // [vocab] scratch: its positive entries in token-id order
+    float* residual_value;
+    float* accepted_probability;
+    moe_speculative_result* result;
+};
+
+cudaError_t launch_speculative_verify(const SpeculativeArgs& args, cudaStream_t stream);
+
 struct RouterArgs
 {
     const float* logits;

@@ -66,6 +66,9 @@ class Oracle:
                                                u32p, u32p, u32p, u32p, f32p, C.c_size_t,
                                                C.POINTER(C.c_size_t), C.POINTER(C.c_size_t), C.c_char_p, C.c_size_t]
         lib.oracle_expert_dispatch.restype = C.c_int
+        lib.oracle_speculative_verify.argtypes = [f32p, f32p, C.c_size_t, C.c_size_t, i32p, C.c_float, C.c_uint32, C.c_float, C.c_float, f32p,
+                                                  u32p, f32p, i32p, f32p, u32p, C.c_char_p, C.c_size_t]
+        lib.oracle_speculative_verify.restype = C.c_int
         if self.kind == "port":
             lib.oracle_set_exp_mode.argtypes = [C.c_int]
             lib.oracle_philox4x32_10.argtypes = [u32p, u32p, u32p]
@@ -79,6 +82,9 @@ class Oracle:
             lib.oracle_session_sample.restype = C.c_int
             lib.oracle_session_destroy.argtypes = [C.c_void_p]
             lib.oracle_mt19937_uniforms.argtypes = [C.c_uint64, C.c_size_t, f32p]
+            lib.oracle_residual_with_generator.argtypes = [f32p, f32p, C.c_size_t, C.c_float, C.c_uint32, C.c_float, C.c_float, C.c_uint64,
+                                                           i32p, f32p, C.c_char_p, C.c_size_t]
+            lib.oracle_residual_with_generator.restype = C.c_int
 
     # -- sampler -----------------------------------------------------------
     def set_exp_mode(self, mode: int) -> None:
@@ -188,6 +194,42 @@ class Oracle:
         finally:
             self.lib.oracle_session_destroy(handle)
         return results
+
+    def speculative_verify(self, target_logits, draft_logits, proposed, uniforms, temperature=1.0, top_k=0, top_p=1.0, min_p=0.0):
+        """The verification step of speculative decoding (session.cpp:776-880) for one Session.
+        target_logits [(n + 1) x vocab], draft_logits [n x vocab], proposed [n], uniforms [>= n + 1] consumed in order.
+        -> dict(status, message, accepted, accepted_probability[n], next_token, next_probability, uniforms_used)"""
+        target_logits = np.ascontiguousarray(target_logits, dtype=np.float32)
+        draft_logits = np.ascontiguousarray(draft_logits, dtype=np.float32).reshape(-1, target_logits.shape[1])
+        proposed = np.ascontiguousarray(proposed, dtype=np.int32)
+        uniforms = np.ascontiguousarray(uniforms, dtype=np.float32)
+        count = proposed.size
+        assert target_logits.shape[0] == count + 1 and draft_logits.shape[0] == count and uniforms.size >= count + 1
+        accepted = C.c_uint32(0)
+        used = C.c_uint32(0)
+        token = C.c_int32(-1)
+        probability = C.c_float(0.0)
+        accepted_probability = np.zeros(max(count, 1), dtype=np.float32)
+        message = C.create_string_buffer(256)
+        status = self.lib.oracle_speculative_verify(_ptr(target_logits, C.c_float), _ptr(draft_logits, C.c_float), target_logits.shape[1], count,
+                                                    _ptr(proposed, C.c_int32), temperature, top_k, top_p, min_p, _ptr(uniforms, C.c_float),
+                                                    C.byref(accepted), _ptr(accepted_probability, C.c_float), C.byref(token),
+                                                    C.byref(probability), C.byref(used), message, 256)
+        return {"status": status, "message": message.value.decode(), "accepted": accepted.value,
+                "accepted_probability": accepted_probability[:accepted.value].copy(), "next_token": token.value,
+                "next_probability": np.float32(probability.value), "uniforms_used": used.value}
+
+    def residual_with_generator(self, target_logits, draft_logits, seed, temperature=1.0, top_k=0, top_p=1.0, min_p=0.0):
+        """Reference only: sample_residual_distribution (session.cpp:150-202) itself with std::mt19937_64(seed)."""
+        target_logits = np.ascontiguousarray(target_logits, dtype=np.float32)
+        draft_logits = np.ascontiguousarray(draft_logits, dtype=np.float32)
+        token = C.c_int32(-1)
+        probability = C.c_float(0.0)
+        message = C.create_string_buffer(256)
+        status = self.lib.oracle_residual_with_generator(_ptr(target_logits, C.c_float), _ptr(draft_logits, C.c_float), target_logits.size,
+                                                         temperature, top_k, top_p, min_p, int(seed), C.byref(token), C.byref(probability),
+                                                         message, 256)
+        return status, token.value, np.float32(probability.value), message.value.decode()
 
     def mt19937_uniforms(self, seed, count):
         values = np.zeros(count, dtype=np.float32)

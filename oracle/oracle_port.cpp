@@ -34,6 +34,7 @@ enum Status : int
     kOk = 0,
     kInvalidArgument = 1, // ErrorCode::InvalidArgument + 1 (include/ncnn/moe/result.h:12-19)
     kInvalidModel = 3,    // ErrorCode::InvalidModel + 1
+    kInternalError = 5,   // ErrorCode::InternalError + 1
 };
 
 inline float exp_f(float x)
@@ -215,6 +216,59 @@ int sample_one(const float* logits, size_t vocab, const Options& o, float unifor
     *token = kept.back().id;
     *probability = kept.back().p;
     return kOk;
+}
+
+// candidate_probability (session.cpp:138-148).
+float probability_of(const std::vector<Candidate>& list, int32_t token)
+{
+    for (const Candidate& c : list)
+        if (c.id == token)
+            return c.p;
+    return 0.0f;
+}
+
+// sample_residual_distribution (session.cpp:150-202) with the uniform supplied
+// by the caller: residual = max(0, target - draft) per token id, summed in
+// token-id order; the draw is uniform * normaliser.
+int residual_sample(const std::vector<Candidate>& target, const std::vector<Candidate>& draft, size_t vocab, float uniform, int32_t* token,
+                    float* probability, char* message, size_t capacity)
+{
+    std::vector<float> residual(vocab, 0.0f);
+    for (const Candidate& c : target)
+        residual[static_cast<size_t>(c.id)] = c.p;
+    for (const Candidate& c : draft)
+    {
+        float& slot = residual[static_cast<size_t>(c.id)];
+        const float reduced = slot - c.p;
+        slot = reduced > 0.0f ? reduced : 0.0f;
+    }
+    float normaliser = 0.0f;
+    for (float value : residual)
+        normaliser += value;
+    if (!std::isfinite(normaliser) || normaliser <= 0.0f)
+        return fail(kInternalError, "speculative residual distribution is empty", message, capacity);
+    const float sample_value = uniform * normaliser;
+    float running = 0.0f;
+    for (size_t id = 0; id < vocab; ++id)
+    {
+        running += residual[id];
+        if (sample_value < running)
+        {
+            *token = static_cast<int32_t>(id);
+            *probability = residual[id] / normaliser;
+            return kOk;
+        }
+    }
+    for (size_t id = vocab; id != 0; --id)
+    {
+        if (residual[id - 1] > 0.0f)
+        {
+            *token = static_cast<int32_t>(id - 1);
+            *probability = residual[id - 1] / normaliser;
+            return kOk;
+        }
+    }
+    return fail(kInternalError, "speculative residual sampling failed", message, capacity);
 }
 
 inline float widen_bf16(uint16_t bits)
@@ -403,6 +457,78 @@ int oracle_sample_batch(const void* logits, int dtype, size_t rows, size_t vocab
             used_uniform[row] = used;
     });
     return kOk;
+}
+
+// The verification step of speculative decoding (session.cpp:776-880) for one
+// Session: `proposed[0..draft_count)` against target_logits[(draft_count + 1) x vocab]
+// and draft_logits[draft_count x vocab]; uniforms are consumed in order.
+int oracle_speculative_verify(const float* target_logits, const float* draft_logits, size_t vocab, size_t draft_count, const int32_t* proposed,
+                              float temperature, uint32_t top_k, float top_p, float min_p, const float* uniforms, uint32_t* accepted_out,
+                              float* accepted_probability, int32_t* next_token, float* next_probability, uint32_t* uniforms_used, char* message,
+                              size_t capacity)
+{
+    const Options o{temperature, top_k, top_p, min_p};
+    if (message != nullptr && capacity > 0)
+        message[0] = '\0';
+    size_t used = 0;
+    size_t accepted = 0;
+    std::vector<Candidate> rejected_target, rejected_draft;
+    *uniforms_used = 0;
+    *accepted_out = 0;
+    while (accepted < draft_count)
+    {
+        const float* target_row = target_logits + accepted * vocab;
+        if (temperature == 0.0f)
+        {
+            int32_t token = -1;
+            float probability = 0.0f;
+            if (int status = sample_one(target_row, vocab, o, 0.0f, &token, &probability, nullptr, message, capacity))
+                return status;
+            if (token != proposed[accepted])
+                break;
+            accepted_probability[accepted] = 1.0f;
+        }
+        else
+        {
+            if (vocab == 0)
+                return fail(kInvalidArgument, "cannot sample empty logits", message, capacity);
+            if (int status = check_options(o, message, capacity))
+                return status;
+            std::vector<Candidate> target, draft;
+            if (int status = distribution(target_row, vocab, o, target, message, capacity))
+                return status;
+            if (int status = distribution(draft_logits + accepted * vocab, vocab, o, draft, message, capacity))
+                return status;
+            const float target_probability = probability_of(target, proposed[accepted]);
+            const float draft_probability = probability_of(draft, proposed[accepted]);
+            if (draft_probability <= 0.0f)
+                return fail(kInternalError, "sampled draft token has zero probability", message, capacity);
+            const float ratio = target_probability / draft_probability;
+            const float acceptance = ratio < 1.0f ? ratio : 1.0f; // std::min(1.0f, ratio)
+            if (uniforms[used++] >= acceptance)
+            {
+                rejected_target = std::move(target);
+                rejected_draft = std::move(draft);
+                break;
+            }
+            accepted_probability[accepted] = target_probability;
+        }
+        ++accepted;
+    }
+    int status = kOk;
+    if (accepted < draft_count && temperature > 0.0f)
+    {
+        status = residual_sample(rejected_target, rejected_draft, vocab, uniforms[used++], next_token, next_probability, message, capacity);
+    }
+    else
+    {
+        int used_uniform = 0;
+        status = sample_one(target_logits + accepted * vocab, vocab, o, uniforms[used], next_token, next_probability, &used_uniform, message, capacity);
+        used += static_cast<size_t>(used_uniform);
+    }
+    *accepted_out = static_cast<uint32_t>(accepted);
+    *uniforms_used = static_cast<uint32_t>(used);
+    return status;
 }
 
 void oracle_philox4x32_10(const uint32_t* counter, const uint32_t* key, uint32_t* out)

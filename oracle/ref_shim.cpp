@@ -262,6 +262,136 @@ int oracle_sampling_distribution(const float* logits, size_t vocab, float temper
     return 0;
 }
 
+// The verification step of speculative decoding (src/engine/session.cpp:776-880)
+// for one Session.  The reference's own sampling_distribution and
+// candidate_probability do the work; restated here are only the accept loop
+// around them and the draw of sample_residual_distribution (:150-202), so that
+// injected uniforms can replace the Session's mt19937_64.  The residual
+// restatement is cross-checked against the reference function itself by
+// oracle_residual_with_generator below.
+static int residual_injected(std::span<const SamplingCandidate> target, std::span<const SamplingCandidate> draft, size_t vocabulary_size,
+                             float uniform, int32_t* token, float* probability, char* message, size_t capacity)
+{
+    std::vector<float> residual(vocabulary_size, 0.0f);
+    for (const SamplingCandidate& candidate : target)
+        residual[candidate.token_id] = candidate.probability;
+    for (const SamplingCandidate& candidate : draft)
+        residual[candidate.token_id] = std::max(0.0f, residual[candidate.token_id] - candidate.probability);
+    const float normalizer = std::accumulate(residual.begin(), residual.end(), 0.0f);
+    if (!std::isfinite(normalizer) || normalizer <= 0.0f)
+        return status_of(Error{ErrorCode::InternalError, "speculative residual distribution is empty"}, message, capacity);
+    const float sample_value = uniform * normalizer; // uniform_real_distribution<float>(0, normalizer): canonical * (b - a) + a
+    float cumulative = 0.0f;
+    for (size_t token_id = 0; token_id < residual.size(); ++token_id)
+    {
+        cumulative += residual[token_id];
+        if (sample_value < cumulative)
+        {
+            *token = static_cast<int32_t>(token_id);
+            *probability = residual[token_id] / normalizer;
+            return 0;
+        }
+    }
+    for (size_t token_id = residual.size(); token_id != 0; --token_id)
+    {
+        if (residual[token_id - 1] > 0.0f)
+        {
+            *token = static_cast<int32_t>(token_id - 1);
+            *probability = residual[token_id - 1] / normalizer;
+            return 0;
+        }
+    }
+    return status_of(Error{ErrorCode::InternalError, "speculative residual sampling failed"}, message, capacity);
+}
+
+int oracle_speculative_verify(const float* target_logits, const float* draft_logits, size_t vocab, size_t draft_count, const int32_t* proposed,
+                              float temperature, uint32_t top_k, float top_p, float min_p, const float* uniforms, uint32_t* accepted_out,
+                              float* accepted_probability, int32_t* next_token, float* next_probability, uint32_t* uniforms_used, char* message,
+                              size_t capacity)
+{
+    clear_message(message, capacity);
+    const SamplingOptions options{temperature, top_k, top_p, min_p};
+    size_t used = 0;
+    size_t accepted = 0;
+    std::vector<SamplingCandidate> rejected_target, rejected_draft;
+    *uniforms_used = 0;
+    *accepted_out = 0;
+    while (accepted < draft_count)
+    {
+        const std::span<const float> target_row(target_logits + accepted * vocab, vocab);
+        if (temperature == 0.0f)
+        {
+            int32_t token = -1;
+            float probability = 0.0f;
+            if (int status = sample_injected(target_row, options, 0.0f, &token, &probability, nullptr, message, capacity))
+                return status;
+            if (token != proposed[accepted])
+                break;
+            accepted_probability[accepted] = 1.0f;
+        }
+        else
+        {
+            auto valid = validate_sampling_options(options);
+            if (!valid)
+                return status_of(valid.error(), message, capacity);
+            auto target_distribution = sampling_distribution(target_row, options);
+            auto draft_distribution = sampling_distribution(std::span<const float>(draft_logits + accepted * vocab, vocab), options);
+            if (!target_distribution || !draft_distribution)
+                return status_of(!target_distribution ? target_distribution.error() : draft_distribution.error(), message, capacity);
+            const float target_probability = candidate_probability(target_distribution.value(), proposed[accepted]);
+            const float draft_probability = candidate_probability(draft_distribution.value(), proposed[accepted]);
+            if (draft_probability <= 0.0f)
+                return status_of(Error{ErrorCode::InternalError, "sampled draft token has zero probability"}, message, capacity);
+            const float acceptance_probability = std::min(1.0f, target_probability / draft_probability);
+            if (uniforms[used++] >= acceptance_probability)
+            {
+                rejected_target = std::move(target_distribution).value();
+                rejected_draft = std::move(draft_distribution).value();
+                break;
+            }
+            accepted_probability[accepted] = target_probability;
+        }
+        ++accepted;
+    }
+    int status = 0;
+    if (accepted < draft_count && temperature > 0.0f)
+    {
+        status = residual_injected(rejected_target, rejected_draft, vocab, uniforms[used++], next_token, next_probability, message, capacity);
+    }
+    else
+    {
+        int used_uniform = 0;
+        status = sample_injected(std::span<const float>(target_logits + accepted * vocab, vocab), options, uniforms[used], next_token,
+                                 next_probability, &used_uniform, message, capacity);
+        used += static_cast<size_t>(used_uniform);
+    }
+    *accepted_out = static_cast<uint32_t>(accepted);
+    *uniforms_used = static_cast<uint32_t>(used);
+    return status;
+}
+
+// The reference's sample_residual_distribution itself, driven by a fresh
+// std::mt19937_64(seed) exactly as a Session would, on the distributions of
+// two logit rows.  Pins residual_injected: oracle_mt19937_uniforms(seed, 1)
+// gives the uniform this call consumes.
+int oracle_residual_with_generator(const float* target_logits, const float* draft_logits, size_t vocab, float temperature, uint32_t top_k,
+                                   float top_p, float min_p, uint64_t seed, int32_t* token, float* probability, char* message, size_t capacity)
+{
+    clear_message(message, capacity);
+    const SamplingOptions options{temperature, top_k, top_p, min_p};
+    auto target_distribution = sampling_distribution(std::span<const float>(target_logits, vocab), options);
+    auto draft_distribution = sampling_distribution(std::span<const float>(draft_logits, vocab), options);
+    if (!target_distribution || !draft_distribution)
+        return status_of(!target_distribution ? target_distribution.error() : draft_distribution.error(), message, capacity);
+    std::mt19937_64 generator(seed);
+    auto sampled = sample_residual_distribution(target_distribution.value(), draft_distribution.value(), vocab, generator);
+    if (!sampled)
+        return status_of(sampled.error(), message, capacity);
+    *token = sampled.value().token_id;
+    *probability = sampled.value().probability;
+    return 0;
+}
+
 int oracle_sample_with_uniform(const float* logits, size_t vocab, float temperature, uint32_t top_k, float top_p, float min_p, float uniform,
                             int32_t* token, float* probability, int* used_uniform, char* message, size_t message_capacity)
 {

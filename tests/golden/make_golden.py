@@ -128,6 +128,47 @@ def router_cases(ref):
     return out
 
 
+def speculative_cases(ref):
+    """Verification steps of speculative decoding: the reference's sampling_distribution /
+    candidate_probability under the accept loop, and its own sample_residual_distribution
+    driven by std::mt19937_64 (the residual draws of the injected-uniform loop are checked
+    against it by tests/test_oracle_cpu.py)."""
+    rng = np.random.default_rng(20260303)
+    vocab, draft_count = 768, 4
+    out = {}
+    index = 0
+    for options in ((1.0, 40, 0.95, 0.0), (0.7, 0, 0.9, 0.02), (1.3, 8, 1.0, 0.0), (1.0, 0, 1.0, 0.0), (0.0, 0, 1.0, 0.0)):
+        for closeness in (0.05, 0.5, 1.5):
+            temperature, top_k, top_p, min_p = options
+            target = (2.5 * rng.standard_normal((draft_count + 1, vocab))).astype(np.float32)
+            draft = (target[:draft_count] + closeness * rng.standard_normal((draft_count, vocab)).astype(np.float32)).astype(np.float32)
+            proposed = []
+            for j in range(draft_count):
+                if temperature == 0.0:
+                    proposed.append(int(np.argmax(draft[j])) if rng.random() < 0.7 else int(rng.integers(vocab)))
+                else:
+                    proposed.append(ref.sample(draft[j], float(rng.random()), temperature, top_k, top_p, min_p)[1])
+            proposed = np.array(proposed, np.int32)
+            uniforms = rng.random(draft_count + 2).astype(np.float32)
+            got = ref.speculative_verify(target, draft, proposed, uniforms, temperature, top_k, top_p, min_p)
+            assert got["status"] == 0
+            tag = f"case{index}_"
+            out[tag + "target"], out[tag + "draft"], out[tag + "proposed"], out[tag + "uniforms"] = target, draft, proposed, uniforms
+            out[tag + "options"] = np.array(options, np.float64)
+            out[tag + "accepted"] = np.array([got["accepted"], got["next_token"], got["uniforms_used"]], np.int64)
+            out[tag + "accepted_probability"] = got["accepted_probability"]
+            out[tag + "next_probability"] = np.array([got["next_probability"]], np.float32)
+            # the reference's residual sampler itself on the first position, with its own generator
+            seed = int(rng.integers(1 << 40))
+            status, token, probability, _ = ref.residual_with_generator(target[0], draft[0], seed, max(temperature, 0.5), top_k, top_p, min_p)
+            out[tag + "residual"] = np.array([status, token, seed], np.int64)
+            out[tag + "residual_probability"] = np.array([probability], np.float32)
+            out[tag + "residual_uniform"] = ref.mt19937_uniforms(seed, 1)
+            index += 1
+    out["case_count"] = np.array([index], np.int64)
+    return out
+
+
 def main():
     ref = oracle_module.reference()
     if ref is None:
@@ -135,7 +176,8 @@ def main():
     np.savez_compressed(HERE / "sampler_reference.npz", **sampler_cases(ref))
     np.savez_compressed(HERE / "session_route_reference.npz", **session_route_cases(ref))
     np.savez_compressed(HERE / "router_reference.npz", **router_cases(ref))
-    for name in ("sampler_reference.npz", "session_route_reference.npz", "router_reference.npz"):
+    np.savez_compressed(HERE / "speculative_reference.npz", **speculative_cases(ref))
+    for name in ("sampler_reference.npz", "session_route_reference.npz", "router_reference.npz", "speculative_reference.npz"):
         print(name, (HERE / name).stat().st_size, "bytes")
 
 

@@ -156,3 +156,58 @@ def test_bf16_rounding_helper(workloads):
     theirs = torch.from_numpy(values).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
     np.testing.assert_array_equal(ours, theirs)
     np.testing.assert_array_equal(workloads.bf16_bits_to_float(ours), torch.from_numpy(values).to(torch.bfloat16).to(torch.float32).numpy())
+
+
+def test_port_matches_golden_speculative_verification(port):
+    """The accept loop of speculative decoding (session.cpp:776-880) as executed by the reference,
+    and the reference's own sample_residual_distribution (:150-202) driven by std::mt19937_64."""
+    g = np.load(GOLDEN / "speculative_reference.npz")
+    pinned_residuals = 0
+    rejections = 0
+    for index in range(int(g["case_count"][0])):
+        tag = f"case{index}_"
+        temperature, top_k, top_p, min_p = (float(v) for v in g[tag + "options"])
+        got = port.speculative_verify(g[tag + "target"], g[tag + "draft"], g[tag + "proposed"], g[tag + "uniforms"], temperature, int(top_k), top_p, min_p)
+        accepted, next_token, used = (int(v) for v in g[tag + "accepted"])
+        assert got["status"] == 0
+        assert (got["accepted"], got["next_token"], got["uniforms_used"]) == (accepted, next_token, used)
+        np.testing.assert_array_equal(bits(got["accepted_probability"]), bits(g[tag + "accepted_probability"]))
+        assert bits(np.array([got["next_probability"]], np.float32))[0] == bits(g[tag + "next_probability"])[0]
+        rejections += accepted < g[tag + "proposed"].size
+        # residual: force a rejection of the draft's own best token at position 0, then draw with the
+        # uniform the reference's generator produced; equal to the reference function's own result
+        status, token, _seed = (int(v) for v in g[tag + "residual"])
+        if status != 0:
+            continue
+        residual_temperature = max(temperature, 0.5)
+        target, draft = g[tag + "target"][0], g[tag + "draft"][0]
+        proposal = np.array([int(np.argmax(draft))], np.int32)
+        uniforms = np.array([np.float32(0.99999994), g[tag + "residual_uniform"][0], 0.5], np.float32)
+        forced = port.speculative_verify(np.stack([target, target]), draft[None], proposal, uniforms, residual_temperature, int(top_k), top_p, min_p)
+        if forced["status"] == 0 and forced["accepted"] == 0:
+            assert forced["next_token"] == token
+            assert bits(np.array([forced["next_probability"]], np.float32))[0] == bits(g[tag + "residual_probability"])[0]
+            pinned_residuals += 1
+    assert rejections >= 4 and pinned_residuals >= 4
+
+
+def test_port_speculative_matches_compiled_reference(port, oracle_module):
+    ref = oracle_module.reference()
+    if ref is None:
+        pytest.skip("the compiled reference is not present")
+    rng = np.random.default_rng(8)
+    vocab, count = 900, 3
+    for case in range(40):
+        temperature = float(rng.choice([0.0, 0.6, 1.0, 1.4]))
+        top_k, top_p, min_p = int(rng.choice([0, 6, 60])), float(rng.choice([1.0, 0.9, 0.5])), float(rng.choice([0.0, 0.03]))
+        target = (2.5 * rng.standard_normal((count + 1, vocab))).astype(np.float32)
+        draft = (target[:count] + rng.choice([0.05, 0.6, 2.0]) * rng.standard_normal((count, vocab))).astype(np.float32)
+        proposed = np.array([int(np.argmax(draft[j])) if temperature == 0.0 or rng.random() < 0.3
+                             else port.sample(draft[j], float(rng.random()), temperature, top_k, top_p, min_p)[1] for j in range(count)], np.int32)
+        uniforms = rng.random(count + 2).astype(np.float32)
+        a = port.speculative_verify(target, draft, proposed, uniforms, temperature, top_k, top_p, min_p)
+        b = ref.speculative_verify(target, draft, proposed, uniforms, temperature, top_k, top_p, min_p)
+        assert (a["status"], a["message"], a["accepted"], a["next_token"], a["uniforms_used"]) == \
+               (b["status"], b["message"], b["accepted"], b["next_token"], b["uniforms_used"])
+        np.testing.assert_array_equal(bits(a["accepted_probability"]), bits(b["accepted_probability"]))
+        assert bits(np.array([a["next_probability"]], np.float32))[0] == bits(np.array([b["next_probability"]], np.float32))[0]
