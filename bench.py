@@ -279,6 +279,66 @@ def run_router_bench(args):
     return 0
 
 
+def run_speculative_bench(args):
+    """Speculative-decoding verification (session.cpp:776-880): 4 proposed tokens per step against
+    5 target and 4 draft rows of vocab 201088 fp32, T=1 / top_k 40 / top_p 0.95.  Three kernels and a
+    40-byte upload per step: latency-bound, reported as time per verification."""
+    import torch
+    package = graft.load_package()
+    torch.cuda.set_device(0)
+    from oracle import oracle as oracle_module
+    oracle = oracle_module.best()
+    vocab, draft_count = 201088, 4
+    options = (1.0, 40, 0.95, 0.0)
+    rng = np.random.default_rng(31)
+    cases = []
+    for case in range(4):
+        target = (2.5 * rng.standard_normal((draft_count + 1, vocab))).astype(np.float32)
+        draft = (target[:draft_count] + [0.05, 0.3, 0.6, 1.2][case] * rng.standard_normal((draft_count, vocab)).astype(np.float32)).astype(np.float32)
+        proposed = np.array([oracle.sample(draft[j], float(rng.random()), *options)[1] for j in range(draft_count)], dtype=np.int32)
+        cases.append((target, draft, proposed))
+    device_cases = [(torch.from_numpy(t).cuda(), torch.from_numpy(d).cuda(), torch.from_numpy(p).cuda()) for t, d, p in cases]
+    params = np.zeros(1, dtype=package.ROW_PARAMS_DTYPE)
+    params["temperature"], params["top_k"], params["top_p"], params["min_p"] = options
+    params["seed"], params["row_id"] = 9, 0
+    sampler = package.Sampler(max_rows=2 * draft_count + 1, max_vocab=vocab)
+    # parity of every case first (also the warm-up)
+    equal = 0
+    t_cpu = 0.0
+    for index, ((target, draft, proposed), device) in enumerate(zip(cases, device_cases)):
+        params["step"] = 7 * index
+        got = sampler.speculative_verify(device[0], device[1], device[2], params)
+        uniforms = np.array([package.philox_uniform(9, 0, 7 * index + i) for i in range(draft_count + 2)], dtype=np.float32)
+        t0 = time.perf_counter()
+        want = oracle.speculative_verify(target, draft, proposed, uniforms, *options)
+        t_cpu += time.perf_counter() - t0
+        equal += int(got["status"] == want["status"] == 0 and got["accepted"] == want["accepted"] and got["next_token"] == want["next_token"]
+                     and got["uniforms_used"] == want["uniforms_used"])
+    out = None
+    for i in range(max(args.warmup, 3)):
+        out = sampler.speculative_verify(*device_cases[i % 4], params, out=out, sync=False)
+    torch.cuda.synchronize()
+    steps = min(args.steps, 512)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(steps):
+        sampler.speculative_verify(*device_cases[i % 4], params, out=out, sync=False)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / steps
+    line = {"metric": "speculative verifications/s, 4 proposed tokens, vocab 201088", "value": 1e3 / ms, "unit": "verifications/s", "n_gpus": 1,
+            "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "5 target + 4 draft rows x 201088 fp32 2.5*N(0,1) (draft = target + noise), T=1 top_k=40 top_p=0.95; direct C-ABI calls, "
+                                   "device-resident logits, 4 cases rotated", "kernels_per_step": 3, "bytes_read_per_step": 9 * vocab * 4},
+            "gpu_launches": 3 * steps,
+            "cpu_baseline": {"value": len(cases) / t_cpu, "unit": "verifications/s", "cores": 1, "kind": oracle.kind,
+                             "sample": f"{len(cases)} verifications, single thread (a Session verifies on its own thread)"},
+            "results_equal_to_reference": f"{equal}/{len(cases)}"}
+    print(json.dumps(line), flush=True)
+    sampler.close()
+    return 0
+
+
 def run_vocab_sharded_bench(args):
     """Config 5a across N GPUs: each rank owns a vocabulary slice, all-gathers k candidates per row, merges."""
     import torch
@@ -353,7 +413,7 @@ def main() -> int:
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=2000)
     parser.add_argument("--warmup", type=int, default=20)
-    parser.add_argument("--workload", default="headline", choices=sorted(WORKLOADS) + ["config5b"])
+    parser.add_argument("--workload", default="headline", choices=sorted(WORKLOADS) + ["config5b", "speculative"])
     parser.add_argument("--sharding", default="rows", choices=["rows", "vocab"], help="vocab: config 5a split by vocabulary slice with a candidate all-gather")
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--e2e-steps", type=int, default=20)
@@ -365,6 +425,8 @@ def main() -> int:
 
     if args.workload == "config5b":
         return run_router_bench(args)
+    if args.workload == "speculative":
+        return run_speculative_bench(args)
     if args.sharding == "vocab":
         return run_vocab_sharded_bench(args)
     if args.impl == "reference":

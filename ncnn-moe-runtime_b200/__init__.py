@@ -237,11 +237,12 @@ class Sampler:
                                                _dev_ptr(out.get("topk")), int(topk_stride)))
         return out
 
-    def speculative_verify(self, target_logits, draft_logits, proposed, params, stream=None):
+    def speculative_verify(self, target_logits, draft_logits, proposed, params, stream=None, out=None, sync=True):
         """Verification step of speculative decoding for one Session (moe_speculative_verify).
         target_logits: CUDA [draft_count + 1, row_stride]; draft_logits: CUDA [draft_count, row_stride];
         proposed: CUDA int32 [draft_count]; params: one ROW_PARAMS_DTYPE entry.
-        Returns dict(accepted, next_token, next_probability, uniforms_used, status, accepted_probability) on the host."""
+        Returns dict(accepted, next_token, next_probability, uniforms_used, status, accepted_probability) on the host
+        (sync=False: the device tensors, to be passed back as `out`)."""
         import torch
         draft_count = int(proposed.numel())
         rows, row_stride = target_logits.shape
@@ -249,13 +250,17 @@ class Sampler:
         dtype = DTYPE_F32 if target_logits.dtype == torch.float32 else DTYPE_BF16
         device = target_logits.device
         params = np.ascontiguousarray(params, dtype=ROW_PARAMS_DTYPE).reshape(1)
-        accepted_probability = torch.zeros(max(draft_count, 1), dtype=torch.float32, device=device)
-        result = torch.zeros(SPECULATIVE_RESULT_DTYPE.itemsize, dtype=torch.uint8, device=device)
+        if out is None:
+            out = (torch.zeros(max(draft_count, 1), dtype=torch.float32, device=device),
+                   torch.zeros(SPECULATIVE_RESULT_DTYPE.itemsize, dtype=torch.uint8, device=device))
+        accepted_probability, result = out
         stream_handle = torch.cuda.current_stream(device).cuda_stream if stream is None else stream
         self._check(self._lib.moe_speculative_verify(self._handle, C.c_void_p(stream_handle), _dev_ptr(target_logits),
                                                      _dev_ptr(draft_logits) if draft_count else None, dtype, draft_count, row_stride,
                                                      target_logits.stride(0), _dev_ptr(proposed) if draft_count else None, _np_ptr(params),
                                                      _dev_ptr(accepted_probability), _dev_ptr(result)))
+        if not sync:
+            return out   # device tensors (accepted_probability, raw result record); nothing was waited for
         torch.cuda.synchronize(device)
         record = result.cpu().numpy().view(SPECULATIVE_RESULT_DTYPE)[0]
         out = {name: record[name].item() for name in SPECULATIVE_RESULT_DTYPE.names}
