@@ -48,7 +48,7 @@ FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only when ME
 # kernel on the headline workload, from the ncu capture summarised in
 # profiles/ (None until a capture exists for the workload).
 NCU_TRAFFIC_BYTES = {
-    "headline": 220_030_000,  # 213.59 MB read + 6.44 MB written, profiles/sample_rows_kernel_f32_headline.md
+    "headline": 220_590_000,  # 213.64 MB read + 6.95 MB written (mean of two captured launches), profiles/sample_rows_kernel_f32_headline.md
 }
 
 WORKLOADS = {
@@ -497,6 +497,16 @@ def main() -> int:
         torch.cuda.synchronize()
     replays = args.steps // chunk if graph is not None else 0
     remainder = args.steps - replays * chunk if graph is not None else args.steps
+    # the steps that do not fill a whole chunk get a graph of their own, so that the timed
+    # region holds no per-step host work at all
+    tail_graph = None
+    if graph is not None and remainder > 1:
+        tail_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(tail_graph):
+            for i in range(remainder):
+                step(args.warmup + i)
+        tail_graph.replay()
+        torch.cuda.synchronize()
 
     clocks = ClockSampler(local_rank)
     start_event = torch.cuda.Event(enable_timing=True)
@@ -508,8 +518,11 @@ def main() -> int:
     start_event.record()
     for _ in range(replays):
         graph.replay()
-    for i in range(remainder):
-        step(args.warmup + i)
+    if tail_graph is not None:
+        tail_graph.replay()
+    else:
+        for i in range(remainder):
+            step(args.warmup + i)
     stop_event.record()
     torch.cuda.synchronize()
     clocks.stop()
@@ -591,7 +604,8 @@ def main() -> int:
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_label,
         "data": "synthetic",
         "config": {"workload": description, "rows_per_gpu": rows, "vocab": vocab, "sharding": "rows" if world > 1 else "none",
-                   "launch": (f"CUDA graph of {chunk} steps replayed {replays}x + {remainder} direct calls" if graph is not None else "direct calls")
+                   "launch": (f"CUDA graph of {chunk} steps replayed {replays}x + " + (f"one graph of {remainder} steps" if tail_graph is not None else f"{remainder} direct calls")
+                              if graph is not None else "direct calls")
                              + ("" if args.no_overlap else "; consecutive launches overlap (programmatic dependent launch, the batches are independent)"),
                    "serialized_direct_calls": {"ms_per_step": serial_ms_per_step, "rows_per_s": rows / (serial_ms_per_step * 1e-3),
                                                "note": "same steps without overlap, one direct C-ABI call per step, host launch overhead included"},
