@@ -560,6 +560,11 @@ def main() -> int:
     if distributed:
         dist.all_reduce(elapsed_tensor, op=dist.ReduceOp.MAX)
     worst_ms = float(elapsed_tensor.item())
+    per_rank_ms = [elapsed_ms / args.steps]
+    if distributed:
+        gathered = [torch.zeros(1, dtype=torch.float64, device="cuda") for _ in range(world)]
+        dist.all_gather(gathered, torch.tensor([elapsed_ms / args.steps], dtype=torch.float64, device="cuda"))
+        per_rank_ms = [float(t.item()) for t in gathered]
     total_rows = rows * world
     value = total_rows * args.steps / (worst_ms * 1e-3)
     ms_per_step = worst_ms / args.steps
@@ -614,6 +619,7 @@ def main() -> int:
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d_bytes), "d2h_bytes_per_step": int(d2h_bytes), "steps": e2e_steps,
                 "path": "moe_sample_batch_host, pinned host logits"},
         "gpu_launches": launches_per_step * args.steps,
+        "per_rank_ms_per_step": per_rank_ms,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
                      "kernel": "sample_rows_kernel", "algorithmic_bytes_per_launch": bytes_per_step, "peak_source": peak_source},
     }

@@ -212,6 +212,13 @@ int moe_speculative_verify(moe_sampler* sampler, void* stream, const void* targe
                            uint32_t draft_count, uint32_t vocab, size_t row_stride, const int32_t* proposed_tokens,
                            const moe_row_params* params, float* accepted_probability, moe_speculative_result* result);
 
+/* moe_speculative_verify with every buffer in HOST memory (the reference holds
+ * target and draft logits as std::vector<float>, session.cpp:760-769).  Copies
+ * in, verifies, copies out and synchronises before returning. */
+int moe_speculative_verify_host(moe_sampler* sampler, const void* target_logits, const void* draft_logits, int dtype, uint32_t draft_count,
+                                uint32_t vocab, size_t row_stride, const int32_t* proposed_tokens, const moe_row_params* params,
+                                float* accepted_probability, moe_speculative_result* result);
+
 /* Same operation with every buffer in HOST memory (what a Session-shaped
  * caller holds: LogitsOutput::values is a std::vector<float>, session.h:30-33).
  * Copies in, samples, copies out and synchronises before returning. */

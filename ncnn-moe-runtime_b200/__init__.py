@@ -53,7 +53,7 @@ class RouterOptions(C.Structure):
 
 EXPORTED_SYMBOLS = [
     "moe_sampler_create", "moe_sampler_destroy", "moe_sampler_last_error", "moe_row_status_message", "moe_row_status_error_code",
-    "moe_philox_uniform", "moe_host_alloc", "moe_host_free", "moe_sample_batch", "moe_sample_batch_ex", "moe_speculative_verify", "moe_sample_batch_host",
+    "moe_philox_uniform", "moe_host_alloc", "moe_host_free", "moe_sample_batch", "moe_sample_batch_ex", "moe_speculative_verify", "moe_speculative_verify_host", "moe_sample_batch_host",
     "moe_sample_local_candidates", "moe_sample_merge_candidates", "moe_router_dispatch", "moe_router_status_message",
     "moe_router_status_error_code", "moe_router_check_options", "moe_router_dispatch_host", "moe_regroup_gather",
     "moe_router_dispatch_static", "moe_sampler_set_overlap",
@@ -95,6 +95,7 @@ def library() -> C.CDLL:
     lib.moe_sample_batch.argtypes = [vp, vp, vp, C.c_int, u32, u32, sz, vp, u64, vp, vp, vp, vp, vp, vp, vp, u32]
     lib.moe_sample_batch_ex.argtypes = [vp, vp, vp, C.c_int, u32, u32, sz, vp, u64, vp, vp, C.POINTER(SampleOutputs)]
     lib.moe_speculative_verify.argtypes = [vp, vp, vp, vp, C.c_int, u32, u32, sz, vp, vp, vp, vp]
+    lib.moe_speculative_verify_host.argtypes = [vp, vp, vp, C.c_int, u32, u32, sz, vp, vp, vp, vp]
     lib.moe_sample_batch_host.argtypes = [vp, vp, C.c_int, u32, u32, sz, vp, vp, vp, vp, vp, vp, vp, vp, u32]
     lib.moe_sample_local_candidates.argtypes = [vp, vp, vp, C.c_int, u32, u32, sz, u32, u32, vp]
     lib.moe_sample_merge_candidates.argtypes = [vp, vp, vp, u32, u32, u32, vp, u64, vp, vp, vp, vp, vp, u32]
@@ -266,6 +267,24 @@ class Sampler:
         out = {name: record[name].item() for name in SPECULATIVE_RESULT_DTYPE.names}
         out["next_probability"] = np.float32(record["next_probability"])
         out["accepted_probability"] = accepted_probability.cpu().numpy()[:out["accepted"]]
+        return out
+
+    def speculative_verify_host(self, target_logits, draft_logits, proposed, params):
+        """moe_speculative_verify_host: numpy float32 logits [draft_count + 1, vocab] / [draft_count, vocab], numpy int32 proposals."""
+        target_logits = np.ascontiguousarray(target_logits, dtype=np.float32)
+        proposed = np.ascontiguousarray(proposed, dtype=np.int32)
+        draft_count = proposed.size
+        draft_logits = np.ascontiguousarray(draft_logits, dtype=np.float32).reshape(draft_count, target_logits.shape[1])
+        params = np.ascontiguousarray(params, dtype=ROW_PARAMS_DTYPE).reshape(1)
+        accepted_probability = np.zeros(max(draft_count, 1), dtype=np.float32)
+        record = np.zeros(1, dtype=SPECULATIVE_RESULT_DTYPE)
+        self._check(self._lib.moe_speculative_verify_host(self._handle, _np_ptr(target_logits), _np_ptr(draft_logits) if draft_count else None, DTYPE_F32,
+                                                          draft_count, target_logits.shape[1], target_logits.shape[1],
+                                                          _np_ptr(proposed) if draft_count else None, _np_ptr(params), _np_ptr(accepted_probability),
+                                                          _np_ptr(record)))
+        out = {name: record[0][name].item() for name in SPECULATIVE_RESULT_DTYPE.names}
+        out["next_probability"] = np.float32(record[0]["next_probability"])
+        out["accepted_probability"] = accepted_probability[:out["accepted"]]
         return out
 
     # ---- host buffers (numpy) ----------------------------------------------------

@@ -573,6 +573,55 @@ int moe_sample_batch_host(moe_sampler* sampler, const void* logits, int dtype, u
     return MOE_STATUS_OK;
 }
 
+int moe_speculative_verify_host(moe_sampler* sampler, const void* target_logits, const void* draft_logits, int dtype, uint32_t draft_count,
+                                uint32_t vocab, size_t row_stride, const int32_t* proposed_tokens, const moe_row_params* params,
+                                float* accepted_probability, moe_speculative_result* result)
+{
+    const uint32_t rows = 2u * draft_count + 1u;
+    if (int status = check_shape(sampler, dtype, rows, vocab, row_stride))
+        return status;
+    if (draft_count > MOE_SPECULATIVE_MAX_DRAFT)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "draft_count exceeds MOE_SPECULATIVE_MAX_DRAFT");
+    if (target_logits == nullptr || params == nullptr || result == nullptr ||
+        (draft_count > 0 && (draft_logits == nullptr || proposed_tokens == nullptr || accepted_probability == nullptr)))
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "target_logits, draft_logits, proposed_tokens, params, accepted_probability and result must not be null");
+    DeviceGuard guard(sampler->device);
+    cudaStream_t stream = sampler->stream;
+    const size_t element = dtype == MOE_DTYPE_F32 ? 4 : 2;
+    const size_t target_bytes = (static_cast<size_t>(draft_count) * row_stride + vocab) * element;
+    const size_t draft_bytes = draft_count > 0 ? ((static_cast<size_t>(draft_count) - 1) * row_stride + vocab) * element : 0;
+    const size_t draft_offset = (target_bytes + 255u) & ~static_cast<size_t>(255u);
+    // staging: both logit blocks, then the proposed tokens, the accepted probabilities and the result record
+    const size_t tokens_offset = (draft_offset + draft_bytes + 255u) & ~static_cast<size_t>(255u);
+    const size_t accepted_offset = tokens_offset + sizeof(int32_t) * MOE_SPECULATIVE_MAX_DRAFT;
+    const size_t result_offset = accepted_offset + sizeof(float) * MOE_SPECULATIVE_MAX_DRAFT;
+    const size_t bytes = result_offset + sizeof(moe_speculative_result);
+    if (bytes > sampler->logits_dev_bytes)
+    {
+        unsigned char* pointer = static_cast<unsigned char*>(sampler->logits_dev);
+        MOE_CUDA_CHECK(sampler, grow(pointer, sampler->logits_dev_bytes, bytes));
+        sampler->logits_dev = pointer;
+    }
+    unsigned char* const staging = static_cast<unsigned char*>(sampler->logits_dev);
+    MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(staging, target_logits, target_bytes, cudaMemcpyHostToDevice, stream));
+    if (draft_count > 0)
+    {
+        MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(staging + draft_offset, draft_logits, draft_bytes, cudaMemcpyHostToDevice, stream));
+        MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(staging + tokens_offset, proposed_tokens, sizeof(int32_t) * draft_count, cudaMemcpyHostToDevice, stream));
+    }
+    const int status = moe_speculative_verify(sampler, stream, staging, staging + draft_offset, dtype, draft_count, vocab, row_stride,
+                                              reinterpret_cast<const int32_t*>(staging + tokens_offset), params,
+                                              reinterpret_cast<float*>(staging + accepted_offset),
+                                              reinterpret_cast<moe_speculative_result*>(staging + result_offset));
+    if (status != MOE_STATUS_OK)
+        return status;
+    if (draft_count > 0)
+        MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(accepted_probability, staging + accepted_offset, sizeof(float) * draft_count, cudaMemcpyDeviceToHost, stream));
+    MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(result, staging + result_offset, sizeof(moe_speculative_result), cudaMemcpyDeviceToHost, stream));
+    MOE_CUDA_CHECK(sampler, cudaStreamSynchronize(stream));
+    return MOE_STATUS_OK;
+}
+
 int moe_sample_local_candidates(moe_sampler* sampler, void* stream_handle, const void* logits, int dtype, uint32_t rows, uint32_t vocab,
                                 size_t row_stride, uint32_t vocab_begin, uint32_t top_k, uint64_t* candidates)
 {

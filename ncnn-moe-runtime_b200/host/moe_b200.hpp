@@ -8,6 +8,7 @@
 //
 //   DeviceSampler::sample          stands in for Session::sample            (session.h:326)
 //   DeviceSampler::sample_batch    stands in for the per-Session loop of    examples/internal/run_model.cpp:776-809
+//   DeviceSampler::verify_speculative   for the verification step of        src/engine/session.cpp:776-880
 //   DeviceExpertDispatcher::dispatch / dispatch_into   for ExpertDispatcher (expert_dispatcher.h:57-60)
 //
 // Errors are values, never exceptions, and carry the reference's messages.
@@ -249,6 +250,40 @@ public:
                 results.emplace_back(SampledToken{token[r], probability[r], (flags[r] & MOE_ROW_FLAG_STOP_TOKEN) != 0});
         }
         return results;
+    }
+
+    // The verification step of Session::generate's speculative branch
+    // (src/engine/session.cpp:776-880): `proposed` tokens of the draft model
+    // against target_logits [(proposed.size() + 1) x vocab] and draft_logits
+    // [proposed.size() x vocab] (host).  Returns the tokens the reference would
+    // emit: the accepted proposals with their reported probabilities, then the
+    // token that follows them.  The stream advances by the uniforms consumed.
+    [[nodiscard]] Result<std::vector<SampledToken>> verify_speculative(std::span<const float> target_logits, std::span<const float> draft_logits,
+                                                                        uint32_t vocab, std::span<const int32_t> proposed, const SamplingOptions& options = {})
+    {
+        const uint32_t draft_count = static_cast<uint32_t>(proposed.size());
+        if (vocab == 0)
+            return Error{ErrorCode::InvalidArgument, "cannot sample empty logits"};
+        if (draft_count > MOE_SPECULATIVE_MAX_DRAFT || target_logits.size() != static_cast<size_t>(draft_count + 1) * vocab ||
+            draft_logits.size() != static_cast<size_t>(draft_count) * vocab)
+            return Error{ErrorCode::InvalidArgument, "logits do not match the number of proposed tokens"};
+        const moe_row_params row{options.temperature, options.top_k, options.top_p, options.min_p, seed_, session_id_, step_};
+        std::vector<float> accepted_probability(draft_count + 1u);
+        moe_speculative_result outcome{};
+        const int status = moe_speculative_verify_host(handle_.get(), target_logits.data(), draft_count > 0 ? draft_logits.data() : nullptr, MOE_DTYPE_F32,
+                                                       draft_count, vocab, vocab, draft_count > 0 ? proposed.data() : nullptr, &row,
+                                                       accepted_probability.data(), &outcome);
+        if (status != MOE_STATUS_OK)
+            return Error{detail::to_error_code(status), moe_sampler_last_error(handle_.get())};
+        if (outcome.status != MOE_ROW_OK)
+            return Error{detail::to_error_code(moe_row_status_error_code(outcome.status)), moe_row_status_message(outcome.status)};
+        step_ += outcome.uniforms_used;
+        std::vector<SampledToken> tokens;
+        tokens.reserve(outcome.accepted + 1u);
+        for (uint32_t index = 0; index < outcome.accepted; ++index)
+            tokens.push_back(SampledToken{proposed[index], accepted_probability[index], false});
+        tokens.push_back(SampledToken{outcome.next_token, outcome.next_probability, false});
+        return tokens;
     }
 
     [[nodiscard]] uint64_t step() const noexcept { return step_; }

@@ -163,12 +163,83 @@ static void test_expert_dispatcher()
     check(routed.value().batches[1].expert_id == 3);
 }
 
+// The verification step of speculative decoding (src/engine/session.cpp:776-880
+// of the reference) on cases small enough to follow by hand.
+static void test_speculative_verification()
+{
+    auto created = DeviceSampler::create(77, 0, 1u << 12, 64);
+    check(static_cast<bool>(created));
+    DeviceSampler& session = *created.value();
+    const uint32_t vocab = 3;
+
+    // greedy: proposals are accepted while they equal the target's best token (:778-794)
+    SamplingOptions greedy;
+    greedy.temperature = 0.0f;
+    const std::vector<float> target = {0.0f, 5.0f, 1.0f, 9.0f, 0.0f, 0.0f, 0.0f, 0.0f, 7.0f};
+    const std::vector<float> draft = {0.0f, 4.0f, 0.0f, 3.0f, 0.0f, 0.0f};
+    std::vector<int32_t> proposed = {1, 0};
+    auto emitted = session.verify_speculative(target, draft, vocab, proposed, greedy);
+    check(static_cast<bool>(emitted));
+    check(emitted.value().size() == 3);
+    check(emitted.value()[0].token_id == 1 && emitted.value()[1].token_id == 0 && emitted.value()[2].token_id == 2);
+    check_near(emitted.value()[0].probability, 1.0f, 0.0f);
+    check_near(emitted.value()[2].probability, 1.0f, 0.0f);
+    check(session.step() == 0); // greedy consumes no uniform
+
+    proposed = {1, 2};
+    emitted = session.verify_speculative(target, draft, vocab, proposed, greedy);
+    check(static_cast<bool>(emitted));
+    check(emitted.value().size() == 2);
+    check(emitted.value()[0].token_id == 1 && emitted.value()[1].token_id == 0); // the target's own token replaces the wrong proposal
+
+    // identical models: the acceptance probability is 1, every proposal passes (:822-835)
+    SamplingOptions plain;
+    const std::vector<float> flat(9, 0.0f);
+    const std::vector<float> flat_draft(6, 0.0f);
+    proposed = {2, 0};
+    emitted = session.verify_speculative(flat, flat_draft, vocab, proposed, plain);
+    check(static_cast<bool>(emitted));
+    check(emitted.value().size() == 3);
+    check(emitted.value()[0].token_id == 2 && emitted.value()[1].token_id == 0);
+    check_near(emitted.value()[0].probability, 1.0f / 3.0f, 1e-6f);
+    check_near(emitted.value()[2].probability, 1.0f / 3.0f, 1e-6f);
+    check(session.step() == 3); // two acceptance tests and the sample of the third row
+
+    // a proposal the draft distribution does not contain is the reference's internal error (:813-821)
+    SamplingOptions top_one;
+    top_one.top_k = 1;
+    proposed = {2, 0};
+    emitted = session.verify_speculative(target, draft, vocab, proposed, top_one);
+    check(!emitted);
+    check(emitted.error().code == ErrorCode::InternalError);
+    check(emitted.error().message == "sampled draft token has zero probability");
+
+    // models that disagree completely: the proposal is rejected (unless the uniform is below 5e-5)
+    // and the residual max(0, target - draft) has all its mass on the target's token (:150-202)
+    const std::vector<float> sure_target = {10.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    const std::vector<float> sure_draft = {0.0f, 10.0f, 0.0f};
+    proposed = {1};
+    const uint64_t before = session.step();
+    emitted = session.verify_speculative(sure_target, sure_draft, vocab, proposed, plain);
+    check(static_cast<bool>(emitted));
+    check(emitted.value().size() == 1);
+    check(emitted.value()[0].token_id == 0);
+    check_near(emitted.value()[0].probability, 1.0f, 1e-6f);
+    check(session.step() == before + 2); // the acceptance test and the residual draw
+
+    // shape errors are values too
+    emitted = session.verify_speculative(sure_target, sure_draft, vocab, std::vector<int32_t>{1, 1}, plain);
+    check(!emitted);
+    check(emitted.error().code == ErrorCode::InvalidArgument);
+}
+
 int main()
 {
     try
     {
         test_sampling();
         test_expert_dispatcher();
+        test_speculative_verification();
     }
     catch (const std::exception& error)
     {

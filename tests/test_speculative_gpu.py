@@ -101,3 +101,25 @@ def test_verification_edge_cases(pkg, parity, torch_cuda):
         _compare(pkg, sampler, torch_cuda, parity, target, draft, proposed, (1.0, 10, 1.0, 0.0), seed=2, row_id=3, step=0)
     finally:
         sampler.close()
+
+
+def test_host_buffer_entry_point_gives_the_same_outcome(pkg, parity, torch_cuda):
+    """moe_speculative_verify_host (host logits, what a Session holds) against the device-buffer call."""
+    rng = np.random.default_rng(12)
+    vocab, draft_count = 4099, 3
+    sampler = pkg.Sampler(max_rows=2 * draft_count + 1, max_vocab=vocab)
+    try:
+        for case, options in enumerate([(1.0, 30, 0.9, 0.0), (0.0, 0, 1.0, 0.0), (0.9, 0, 0.8, 0.01)]):
+            target, draft, proposed = _case(rng, vocab, draft_count, *options, 0.5, parity.port)
+            params = np.zeros(1, dtype=pkg.ROW_PARAMS_DTYPE)
+            params["temperature"], params["top_k"], params["top_p"], params["min_p"] = options
+            params["seed"], params["row_id"], params["step"] = 4, case, 2
+            device = sampler.speculative_verify(torch_cuda.from_numpy(target).cuda(), torch_cuda.from_numpy(draft).cuda(),
+                                                torch_cuda.from_numpy(proposed).cuda(), params)
+            host = sampler.speculative_verify_host(target, draft, proposed, params)
+            for key in ("accepted", "next_token", "uniforms_used", "status"):
+                assert host[key] == device[key], (key, host, device)
+            assert host["next_probability"].view(np.uint32) == device["next_probability"].view(np.uint32)
+            np.testing.assert_array_equal(host["accepted_probability"].view(np.uint32), device["accepted_probability"].view(np.uint32))
+    finally:
+        sampler.close()
