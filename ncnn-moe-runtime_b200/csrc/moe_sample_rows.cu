@@ -106,6 +106,19 @@ constexpr int kItems = kCapLarge / kThreads; // most records per thread in block
 #ifndef MOE_TILE
 #define MOE_TILE 2
 #endif
+// Logits a slice expects above its sampled threshold: MOE_WANTED_PER_K * k + MOE_WANTED_EXTRA.
+// The threshold is the r-th largest thread maximum of the first tile, and the
+// number of logits of the slice above an r-th order statistic varies like a
+// Gamma(r) variate: with 3k + 48 (r = 8 at k = 50, 100 k logits per slice)
+// about one slice in a thousand found fewer than k and streamed a second
+// time, alone and latency-bound (+25 us for that launch); 4k + 64 gives
+// r = 11 and about one slice in 10^5, for 1 us more select work per launch.
+#ifndef MOE_WANTED_PER_K
+#define MOE_WANTED_PER_K 4.0f
+#endif
+#ifndef MOE_WANTED_EXTRA
+#define MOE_WANTED_EXTRA 64.0f
+#endif
 #ifndef MOE_RESIDENT
 #define MOE_RESIDENT 5
 #endif
@@ -594,7 +607,7 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
     if (mode == kTopK)
     {
         const float slice_elements = static_cast<float>(group_end - group_begin) * (kThreads * W::kWidth);
-        const float wanted = 3.0f * static_cast<float>(k) + 48.0f;
+        const float wanted = MOE_WANTED_PER_K * static_cast<float>(k) + MOE_WANTED_EXTRA;
         const float p_element = fminf(1.0f, wanted / slice_elements);
         const float p_thread = 1.0f - __expf(static_cast<float>(kGroupsPerTile * W::kWidth) * log1pf(-fminf(p_element, 0.999f)));
         r = static_cast<uint32_t>(ceilf(p_thread * kThreads));
@@ -846,6 +859,42 @@ __device__ __forceinline__ void reduce_buffer(Ctx& c, bool sort)
         }
         c.sorted = true;
         return;
+    }
+    if (c.mode != kLive && n <= 2u * kThreads && c.k <= kThreads / 2u)
+    {
+        // A little over one record per thread: sort the first kThreads, keep
+        // their k best, and let only the spare records that beat the k-th of
+        // them join a second, much smaller sort.
+        const uint32_t tid = threadIdx.x;
+        const uint32_t extra = n - kThreads;
+        const uint64_t spare = tid < extra ? c.rec[kThreads + tid] : 0ull;
+        if (tid == 0)
+            s.sel.out_count = 0;
+        block_rank_sort_descending<kThreads>(c.rec, kThreads); // ends with a barrier
+        const uint64_t pivot = c.rec[c.k - 1u];
+        const bool joins = spare > pivot;
+        const unsigned voters = __ballot_sync(kFullMask, joins);
+        uint32_t base = 0;
+        if ((tid & 31u) == 0u && voters != 0u)
+            base = atomicAdd(&s.sel.out_count, static_cast<uint32_t>(__popc(voters)));
+        base = __shfl_sync(kFullMask, base, 0);
+        __syncthreads(); // every thread has read the pivot
+        if (joins)
+            c.rec[c.k + base + __popc(voters & ((1u << (tid & 31u)) - 1u))] = spare;
+        __syncthreads();
+        const uint32_t merged = c.k + s.sel.out_count; // at most k + kThreads <= cap
+        if (merged <= kThreads)
+        {
+            block_rank_sort_descending<kThreads>(c.rec, merged);
+            if (tid == 0)
+                s.count = c.k;
+            __syncthreads();
+            c.sorted = true;
+            return;
+        }
+        if (tid == 0)
+            s.count = merged;
+        __syncthreads();
     }
     flush_buffer(c);
     if (sort && !c.aborted && s.count <= kThreads)
