@@ -48,7 +48,7 @@ FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only when ME
 # kernel on the headline workload, from the ncu capture summarised in
 # profiles/ (None until a capture exists for the workload).
 NCU_TRAFFIC_BYTES = {
-    "headline": 220_590_000,  # 213.64 MB read + 6.95 MB written (mean of two captured launches), profiles/sample_rows_kernel_f32_headline.md
+    "headline": 223_360_000,  # 216.78 MB read + 6.58 MB written (mean of two captured launches), profiles/sample_rows_kernel_f32_headline.md
 }
 
 WORKLOADS = {
