@@ -94,9 +94,9 @@ int moe_sampler_create(int device, uint32_t max_rows, uint32_t max_vocab, moe_sa
 void moe_sampler_destroy(moe_sampler* sampler);
 /* Back-to-back sampling calls on one stream normally run one after the other.
  * With overlap enabled, moe_sample_batch launches its kernel with programmatic
- * stream serialization: it may start reading its logits while the previous
- * kernel of the stream is still in its last microseconds (selecting, sorting,
- * drawing), and waits for that kernel to complete before it writes anything.
+ * stream serialization: its CTAs may take the SM slots the previous sampling
+ * kernel of the stream leaves free and read their logits while that kernel is
+ * still running, and they wait for it to complete before they write anything.
  * Results are unchanged.  Enable it only when the logits of a call do not
  * depend on the kernel launched immediately before it on the same stream
  * (independent batches, or logits produced earlier): that kernel is not waited
