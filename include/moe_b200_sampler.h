@@ -323,7 +323,7 @@ int moe_router_dispatch_host(moe_sampler* sampler, const float* router_logits, u
  * error_text may be NULL. */
 #define MOE_ROUTER_STATIC_MAX_ROUTES 65536u
 #define MOE_ROUTER_STATIC_MAX_EXPERTS 4096u
-#define MOE_ROUTER_STATIC_SCRATCH_BYTES (544u * 1024u)
+#define MOE_ROUTER_STATIC_SCRATCH_BYTES (1568u * 1024u)
 int moe_router_dispatch_static(void* stream, const float* router_logits, uint32_t token_count,
                                const moe_router_options* options, uint32_t* expert_offsets, uint32_t* route_token,
                                uint32_t* route_rank, float* route_weight, int32_t* plan_status, char* error_text,

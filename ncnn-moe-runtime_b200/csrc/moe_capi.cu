@@ -63,6 +63,9 @@ struct moe_sampler
     uint32_t* expert_counts = nullptr;
     size_t expert_counts_capacity = 0;
     unsigned long long* router_error = nullptr;
+    uint32_t* router_scan_done = nullptr;    // one word, 0 between calls
+    uint32_t* router_block_counts = nullptr; // [MOE_ROUTER_BLOCK_TABLE_ENTRIES], allocated by the first router call
+    int32_t* gather_status = nullptr;        // one word: set when moe_regroup_gather met a token index out of range
     // router host staging
     float* router_logits_dev = nullptr;
     size_t router_logits_capacity = 0;
@@ -182,14 +185,28 @@ int upload_rows(moe_sampler* sampler, cudaStream_t stream, uint32_t rows, const 
     return MOE_STATUS_OK;
 }
 
-// Slices per row; MOE_B200_SPLITS (1, 2, 4 or 8) overrides the built-in policy for tuning runs.
+// The exact kernel's per-slot sort scratch (16 bytes per vocabulary entry and
+// slot) is only needed by batches that contain rows without Top-K: it is
+// allocated when the first such batch arrives, not with the handle.
+int ensure_exact_scratch(moe_sampler* sampler, cudaStream_t stream)
+{
+    Workspace& ws = sampler->ws;
+    if (ws.sort_keys != nullptr)
+        return MOE_STATUS_OK;
+    const size_t stride = (static_cast<size_t>(ws.max_vocab) + 3u) & ~static_cast<size_t>(3u);
+    MOE_CUDA_CHECK(sampler, cudaStreamSynchronize(stream));
+    MOE_CUDA_CHECK(sampler, cudaMalloc(reinterpret_cast<void**>(&ws.sort_keys), sizeof(uint32_t) * 4u * stride * ws.slots));
+    return MOE_STATUS_OK;
+}
+
+// Slices per row; MOE_B200_SPLITS (1..32) overrides the built-in policy for tuning runs.
 uint32_t pick_splits(const moe_sampler* sampler, uint32_t rows, uint32_t vocab, int dtype, bool large_top_k, bool overlapped = false)
 {
     uint32_t splits = choose_splits(rows, vocab, dtype, sampler->sm_count, sampler->ws.slice_slots, large_top_k, overlapped);
     if (const char* forced = std::getenv("MOE_B200_SPLITS"))
     {
         const long value = std::strtol(forced, nullptr, 10);
-        if ((value == 1 || value == 2 || value == 4 || value == 8) && static_cast<uint64_t>(rows) * value <= sampler->ws.slice_slots)
+        if (value >= 1 && value <= 32 && static_cast<uint64_t>(rows) * value <= sampler->ws.slice_slots)
             splits = static_cast<uint32_t>(value);
     }
     return splits;
@@ -243,7 +260,6 @@ int moe_sampler_create(int device, uint32_t max_rows, uint32_t max_vocab, moe_sa
     ws.max_rows = max_rows;
     ws.max_vocab = max_vocab;
     ws.slots = max_rows < static_cast<uint32_t>(sampler->sm_count) ? max_rows : static_cast<uint32_t>(sampler->sm_count);
-    const size_t stride = (static_cast<size_t>(max_vocab) + 3u) & ~static_cast<size_t>(3u);
     cudaError_t status = cudaSuccess;
     auto allocate = [&](void** pointer, size_t bytes) {
         if (status == cudaSuccess)
@@ -252,7 +268,6 @@ int moe_sampler_create(int device, uint32_t max_rows, uint32_t max_vocab, moe_sa
     uint32_t* counters = nullptr;
     allocate(reinterpret_cast<void**>(&counters), 2 * sizeof(uint32_t));
     allocate(reinterpret_cast<void**>(&ws.exact_rows), sizeof(uint32_t) * max_rows);
-    allocate(reinterpret_cast<void**>(&ws.sort_keys), sizeof(uint32_t) * 4u * stride * ws.slots);
     ws.slice_slots = static_cast<uint32_t>(sampler->sm_count) * 6u * 2u + 64u;
     allocate(reinterpret_cast<void**>(&ws.slice_records), sizeof(uint64_t) * MOE_SLICE_SLOT_RECORDS * ws.slice_slots);
     allocate(reinterpret_cast<void**>(&ws.slice_header), sizeof(uint32_t) * 4u * ws.slice_slots);
@@ -264,6 +279,8 @@ int moe_sampler_create(int device, uint32_t max_rows, uint32_t max_vocab, moe_sa
     allocate(reinterpret_cast<void**>(&sampler->flags_dev), sizeof(uint32_t) * max_rows);
     allocate(reinterpret_cast<void**>(&sampler->status_dev), sizeof(int32_t) * max_rows);
     allocate(reinterpret_cast<void**>(&sampler->router_error), sizeof(unsigned long long));
+    allocate(reinterpret_cast<void**>(&sampler->router_scan_done), sizeof(uint32_t));
+    allocate(reinterpret_cast<void**>(&sampler->gather_status), sizeof(int32_t));
     allocate(reinterpret_cast<void**>(&sampler->router_status_dev), sizeof(int32_t));
     if (status == cudaSuccess)
         status = cudaMemset(counters, 0, 2 * sizeof(uint32_t));
@@ -271,6 +288,10 @@ int moe_sampler_create(int device, uint32_t max_rows, uint32_t max_vocab, moe_sa
         status = cudaMemset(ws.row_arrivals, 0, sizeof(uint32_t) * max_rows);
     if (status == cudaSuccess)
         status = cudaMemset(sampler->router_error, 0xFF, sizeof(unsigned long long));
+    if (status == cudaSuccess)
+        status = cudaMemset(sampler->router_scan_done, 0, sizeof(uint32_t));
+    if (status == cudaSuccess)
+        status = cudaMemset(sampler->gather_status, 0, sizeof(int32_t));
     if (status == cudaSuccess)
         status = cudaStreamCreateWithFlags(&sampler->stream, cudaStreamNonBlocking);
     if (status == cudaSuccess)
@@ -296,7 +317,8 @@ void moe_sampler_destroy(moe_sampler* sampler)
                         sampler->ws.slice_header, sampler->ws.row_arrivals, sampler->params_dev, sampler->stop_offsets_dev,
                         sampler->stop_tokens_dev, sampler->logits_dev, sampler->token_dev, sampler->probability_dev, sampler->flags_dev,
                         sampler->status_dev, sampler->topk_dev, sampler->selected_expert, sampler->selected_weight, sampler->expert_counts,
-                        sampler->router_error, sampler->router_logits_dev, sampler->router_bias_dev, sampler->router_explicit_dev,
+                        sampler->router_error, sampler->router_scan_done, sampler->router_block_counts, sampler->gather_status,
+                        sampler->router_logits_dev, sampler->router_bias_dev, sampler->router_explicit_dev,
                         sampler->router_offsets_dev, sampler->router_token_dev, sampler->router_rank_dev, sampler->router_weight_dev,
                         sampler->router_status_dev, sampler->spec_kept_token, sampler->spec_kept_probability, sampler->spec_kept_count,
                         sampler->spec_token, sampler->spec_probability, sampler->spec_flags, sampler->spec_status, sampler->spec_dense,
@@ -437,7 +459,11 @@ int moe_sample_batch_ex(moe_sampler* sampler, void* stream_handle, const void* l
     const uint32_t splits = pick_splits(sampler, rows, vocab, dtype, args.large_top_k, args.overlap_previous);
     MOE_CUDA_CHECK(sampler, launch_sample_rows(args, sampler->ws, splits, stream));
     if (sampler->resident_needs_exact)
+    {
+        if (int status = ensure_exact_scratch(sampler, stream))
+            return status;
         MOE_CUDA_CHECK(sampler, launch_sample_exact(args, sampler->ws, stream));
+    }
     return MOE_STATUS_OK;
 }
 
@@ -508,7 +534,11 @@ int moe_speculative_verify(moe_sampler* sampler, void* stream_handle, const void
         const uint32_t splits = pick_splits(sampler, args.rows, vocab, dtype, args.large_top_k);
         MOE_CUDA_CHECK(sampler, launch_sample_rows(args, sampler->ws, splits, stream));
         if (sampler->resident_needs_exact)
+        {
+            if (int status = ensure_exact_scratch(sampler, stream))
+                return status;
             MOE_CUDA_CHECK(sampler, launch_sample_exact(args, sampler->ws, stream));
+        }
     }
     SpeculativeArgs verify = {};
     verify.draft_count = draft_count;
@@ -741,8 +771,9 @@ int moe_router_dispatch(moe_sampler* sampler, void* stream_handle, const float* 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
     DeviceGuard guard(sampler->device);
     const size_t routes = static_cast<size_t>(token_count) * options->top_k;
-    if (routes > sampler->selected_capacity || options->expert_count > sampler->expert_counts_capacity)
+    if (routes > sampler->selected_capacity || options->expert_count > sampler->expert_counts_capacity || sampler->router_block_counts == nullptr)
     {
+        // earlier calls on this stream may still use the scratch that is replaced here
         MOE_CUDA_CHECK(sampler, cudaStreamSynchronize(stream));
         if (routes > sampler->selected_capacity)
         {
@@ -750,10 +781,13 @@ int moe_router_dispatch(moe_sampler* sampler, void* stream_handle, const float* 
             MOE_CUDA_CHECK(sampler, grow(sampler->selected_expert, capacity, routes));
             MOE_CUDA_CHECK(sampler, grow(sampler->selected_weight, sampler->selected_capacity, routes));
         }
+        // every call rewrites the counts it reads (per block, then per expert): nothing to clear
         if (options->expert_count > sampler->expert_counts_capacity)
-        {
             MOE_CUDA_CHECK(sampler, grow(sampler->expert_counts, sampler->expert_counts_capacity, options->expert_count));
-            MOE_CUDA_CHECK(sampler, cudaMemset(sampler->expert_counts, 0, sizeof(uint32_t) * sampler->expert_counts_capacity));
+        if (sampler->router_block_counts == nullptr)
+        {
+            size_t capacity = 0;
+            MOE_CUDA_CHECK(sampler, grow(sampler->router_block_counts, capacity, MOE_ROUTER_BLOCK_TABLE_ENTRIES));
         }
     }
     RouterArgs args = {};
@@ -767,7 +801,8 @@ int moe_router_dispatch(moe_sampler* sampler, void* stream_handle, const float* 
     args.plan_status = plan_status;
     args.selected_expert = sampler->selected_expert;
     args.selected_weight = sampler->selected_weight;
-    MOE_CUDA_CHECK(sampler, launch_router_dispatch_kernels(args, sampler->expert_counts, sampler->router_error, stream));
+    args.block_counts = sampler->router_block_counts;
+    MOE_CUDA_CHECK(sampler, launch_router_dispatch_kernels(args, sampler->expert_counts, sampler->router_scan_done, sampler->router_error, stream));
     return MOE_STATUS_OK;
 }
 
@@ -834,13 +869,13 @@ int moe_regroup_gather(moe_sampler* sampler, void* stream_handle, const float* h
 {
     if (sampler == nullptr)
         return MOE_STATUS_INVALID_ARGUMENT;
-    (void)token_count;
     if (route_count == 0 || columns == 0)
         return MOE_STATUS_OK;
     if (hidden == nullptr || route_token == nullptr || gathered == nullptr)
         return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "gather buffers must not be null");
     DeviceGuard guard(sampler->device);
-    MOE_CUDA_CHECK(sampler, launch_regroup_gather(hidden, columns, route_token, route_count, gathered, static_cast<cudaStream_t>(stream_handle)));
+    MOE_CUDA_CHECK(sampler, launch_regroup_gather(hidden, token_count, columns, route_token, route_count, gathered, sampler->gather_status,
+                                                  static_cast<cudaStream_t>(stream_handle)));
     return MOE_STATUS_OK;
 }
 

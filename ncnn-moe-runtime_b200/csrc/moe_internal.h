@@ -9,8 +9,11 @@
 #include "../../include/moe_b200_sampler.h"
 
 #define MOE_SLICE_SLOT_RECORDS 1024u
-// largest top_k the small-buffer kernel instantiation serves (3 * k + 48 sampled records must fit 2048)
+// largest top_k the small-buffer kernel instantiation serves (the 4 * k + 64 records a slice expects above its sampled
+// threshold must fit the 2048-record buffer with room for their spread)
 #define MOE_SAMPLER_TOPK_SMALL_MAX 448u
+// entries of the router's [expert][block] count table (expert_count * blocks of the select kernel never exceeds it)
+#define MOE_ROUTER_BLOCK_TABLE_ENTRIES 262144u
 
 namespace moe {
 
@@ -116,10 +119,54 @@ struct RouterArgs
     // scratch
     uint32_t* selected_expert; // [token_count * top_k]
     float* selected_weight;    // [token_count * top_k]
+    uint32_t* block_counts;    // [MOE_ROUTER_BLOCK_TABLE_ENTRIES]: routes per (expert, block of the select kernel)
+    uint32_t tokens_per_block; // filled in by the launcher
 };
-cudaError_t launch_router_dispatch_kernels(const RouterArgs& args, uint32_t* expert_counts, unsigned long long* error_word, cudaStream_t stream);
-cudaError_t launch_regroup_gather(const float* hidden, uint32_t columns, const uint32_t* route_token, uint32_t route_count, float* gathered,
-                                  cudaStream_t stream);
+struct RouterPartition
+{
+    uint32_t tokens_per_block;
+    uint32_t blocks;
+};
+RouterPartition router_partition(uint32_t token_count, uint32_t experts);
+// expert_counts: [expert_count] scratch; scan_done: one word that is 0 between calls; error_word: ~0 between calls
+cudaError_t launch_router_dispatch_kernels(const RouterArgs& args, uint32_t* expert_counts, uint32_t* scan_done, unsigned long long* error_word,
+                                           cudaStream_t stream);
+// out_of_range: one device word, set to 1 when a route_token entry is >= token_count (its row is zero-filled)
+cudaError_t launch_regroup_gather(const float* hidden, uint32_t token_count, uint32_t columns, const uint32_t* route_token, uint32_t route_count,
+                                  float* gathered, int32_t* out_of_range, cudaStream_t stream);
+
+// Kernels that need more than 48 KiB of dynamic shared memory must opt in with
+// cudaFuncSetAttribute, which applies to the current device only: what has been
+// configured is remembered per device ordinal (one SharedOptIn per kernel).
+constexpr int kMaxDevices = 64;
+struct SharedOptIn
+{
+    size_t bytes[kMaxDevices] = {};
+};
+// true when `shared_bytes` still has to be configured on `device`; records it as configured
+inline bool opt_in_needed(SharedOptIn& state, int device, size_t shared_bytes)
+{
+    if (device < 0 || device >= kMaxDevices)
+        return true; // untracked ordinal: configure on every launch
+    if (state.bytes[device] >= shared_bytes)
+        return false;
+    state.bytes[device] = shared_bytes; // racing host threads write the same value
+    return true;
+}
+template<typename Kernel>
+cudaError_t opt_in_shared(SharedOptIn& state, Kernel kernel, size_t shared_bytes)
+{
+    int device = 0;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status != cudaSuccess)
+        return status;
+    if (!opt_in_needed(state, device, shared_bytes))
+        return cudaSuccess;
+    status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared_bytes));
+    if (status != cudaSuccess && device >= 0 && device < kMaxDevices)
+        state.bytes[device] = 0;
+    return status;
+}
 
 uint32_t choose_splits(uint32_t rows, uint32_t vocab, int dtype, int sm_count, uint32_t slice_slots, bool large_top_k, bool overlapped);
 

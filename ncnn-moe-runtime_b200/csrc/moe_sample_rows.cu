@@ -1,8 +1,10 @@
 // Streaming sampler kernel: one pass over each logit row.
 //
 // A row is cut into `splits` contiguous slices, one CTA each.  A CTA streams its
-// slice with 128-bit loads and keeps, in shared memory, only the records that
-// can still matter:
+// slice through a shared-memory ring that the copy engine fills with bulk
+// asynchronous copies (cp.async.bulk + mbarrier, no cluster forms), reads it
+// back with 128-bit shared loads and keeps only the records that can still
+// matter:
 //   greedy rows      the best finite logit so far              (session.cpp:404-424)
 //   Top-K rows       the k best records so far                 (session.cpp:80-87)
 //   full-vocab rows  the records whose softmax numerator could be >= 2^-26
@@ -20,6 +22,8 @@
 // Rows whose live set does not fit on chip, and draws that fall through to a
 // numerically dead candidate, are appended to a list that the exact kernel
 // (moe_sample_exact.cu) finishes.
+
+#include <cstdlib>
 
 #include "moe_common.cuh"
 #include "moe_epilogue.cuh"
@@ -82,6 +86,16 @@ __device__ __forceinline__ unsigned long long moe_globaltimer()
 #define MOE_PHASE_MARK(slot) do {} while (0)
 #define MOE_PHASE_BEGIN() do {} while (0)
 #endif
+#ifdef MOE_PHASE_TIMERS
+// per-warp stopwatches inside the streaming loop (lane 0 adds them up at the end)
+#define MOE_LAP_DECLARE() long long moe_lap_start = clock64(); long long moe_lap[4] = {0, 0, 0, 0}
+#define MOE_LAP(slot) do { const long long moe_lap_now = clock64(); moe_lap[slot] += moe_lap_now - moe_lap_start; moe_lap_start = moe_lap_now; } while (0)
+#define MOE_LAP_FLUSH() do { if ((threadIdx.x & 31) == 0) for (int moe_l = 0; moe_l < 4; ++moe_l) atomicAdd(&g_phase_cycles[11 + moe_l], static_cast<unsigned long long>(moe_lap[moe_l])); } while (0)
+#else
+#define MOE_LAP_DECLARE() do {} while (0)
+#define MOE_LAP(slot) do {} while (0)
+#define MOE_LAP_FLUSH() do {} while (0)
+#endif
 
 namespace moe {
 
@@ -100,30 +114,13 @@ __device__ __forceinline__ void grid_dependency_release()
 }
 
 constexpr int kThreads = 256;
-constexpr int kCapSmall = 2048;           // records a CTA can hold: batches whose Top-K sizes are small (6 CTAs per SM)
-constexpr int kCapLarge = 4096;           // ... and batches with top_k up to MOE_SAMPLER_TOPK_FAST_MAX (4 CTAs per SM)
+constexpr int kWarps = kThreads / 32;
+constexpr int kCapSmall = 2048;           // records a CTA can hold: batches whose Top-K sizes are small
+constexpr int kCapLarge = 4096;           // ... and batches with top_k up to MOE_SAMPLER_TOPK_FAST_MAX
 constexpr int kItems = kCapLarge / kThreads; // most records per thread in block-wide passes
-#ifndef MOE_TILE
-#define MOE_TILE 2
-#endif
-// Logits a slice expects above its sampled threshold: MOE_WANTED_PER_K * k + MOE_WANTED_EXTRA.
-// The threshold is the r-th largest thread maximum of the first tile, and the
-// number of logits of the slice above an r-th order statistic varies like a
-// Gamma(r) variate: with 3k + 48 (r = 8 at k = 50, 100 k logits per slice)
-// about one slice in a thousand found fewer than k and streamed a second
-// time, alone and latency-bound (+25 us for that launch); 4k + 64 gives
-// r = 11 and about one slice in 10^5, for 1 us more select work per launch.
-#ifndef MOE_WANTED_PER_K
-#define MOE_WANTED_PER_K 4.0f
-#endif
-#ifndef MOE_WANTED_EXTRA
-#define MOE_WANTED_EXTRA 64.0f
-#endif
-#ifndef MOE_RESIDENT
-#define MOE_RESIDENT 5
-#endif
-constexpr int kGroupsPerTile = MOE_TILE;  // vector loads in flight per thread
-constexpr uint32_t kWarpHitCap = 128;      // vectors a warp of the barrier-free loop can queue per slice
+constexpr int kMaxStages = 8;             // ring slots per warp, at most
+constexpr uint32_t kHitQueue = 64;        // queued hit vectors per warp (a vote adds at most 32)
+constexpr int kGroupsPerTile = 2;         // careful loop: 128-bit loads in flight per thread
 // live mode: the buffer is re-tested against the running maximum at half fill;
 // more survivors than live_abort(cap) send the row to the exact kernel
 __host__ __device__ constexpr uint32_t live_abort(uint32_t cap)
@@ -150,10 +147,14 @@ struct __align__(16) RowShared
     uint32_t maxkey;
     uint32_t abort_flag;
     uint32_t overflow;
-    // barrier-free loop: per warp, the indices of the 32-byte vectors whose
-    // maximum reached the threshold; each warp unpacks its own queue after its
-    // part of the stream, outside the hot loop
-    uint32_t hit_queue[kThreads / 32][kWarpHitCap];
+    // completion barriers of the streaming ring: one per warp and slot
+    uint64_t ring_full[kWarps][kMaxStages];
+    // per warp, the 16-byte vectors whose maximum reached the threshold and the
+    // index of their first logit: queued by the streaming loop with no
+    // divergence, unpacked one vector per lane when the queue runs full
+    uint4 hit_vector[kWarps][kHitQueue];
+    uint32_t hit_index[kWarps][kHitQueue];
+    uint32_t hit_count[kWarps];
 };
 
 struct Ctx
@@ -238,66 +239,6 @@ struct Unpack<__nv_bfloat16>
     __device__ static __forceinline__ uint4 nan_vector()
     {
         return make_uint4(0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u);
-    }
-};
-
-// 256-bit vectors of the barrier-free loop.
-template<typename T>
-struct Wide;
-
-template<>
-struct Wide<float>
-{
-    static constexpr int kWidth = 8;
-    __device__ static __forceinline__ void values(const Vec32& v, float (&x)[8])
-    {
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-            x[i] = __uint_as_float(v.w[i]);
-    }
-    __device__ static __forceinline__ float maximum(const Vec32& v)
-    {
-        const float a = fmaxf(fmaxf(__uint_as_float(v.w[0]), __uint_as_float(v.w[1])), fmaxf(__uint_as_float(v.w[2]), __uint_as_float(v.w[3])));
-        const float b = fmaxf(fmaxf(__uint_as_float(v.w[4]), __uint_as_float(v.w[5])), fmaxf(__uint_as_float(v.w[6]), __uint_as_float(v.w[7])));
-        return fmaxf(a, b);
-    }
-    __device__ static __forceinline__ Vec32 nan_vector()
-    {
-        Vec32 v;
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-            v.w[i] = 0x7FC00000u;
-        return v;
-    }
-};
-
-template<>
-struct Wide<__nv_bfloat16>
-{
-    static constexpr int kWidth = 16;
-    __device__ static __forceinline__ void values(const Vec32& v, float (&x)[16])
-    {
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-        {
-            x[2 * i] = __uint_as_float(v.w[i] << 16);
-            x[2 * i + 1] = __uint_as_float(v.w[i] & 0xFFFF0000u);
-        }
-    }
-    __device__ static __forceinline__ float maximum(const Vec32& v)
-    {
-        const uint32_t a = max_bf16x2(max_bf16x2(v.w[0], v.w[1]), max_bf16x2(v.w[2], v.w[3]));
-        const uint32_t b = max_bf16x2(max_bf16x2(v.w[4], v.w[5]), max_bf16x2(v.w[6], v.w[7]));
-        const uint32_t bits = max_bf16x2(a, b);
-        return fmaxf(__uint_as_float(bits << 16), __uint_as_float(bits & 0xFFFF0000u));
-    }
-    __device__ static __forceinline__ Vec32 nan_vector()
-    {
-        Vec32 v;
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-            v.w[i] = 0x7FC07FC0u;
-        return v;
     }
 };
 
@@ -555,125 +496,339 @@ __device__ __forceinline__ void offer_values(RowShared& s, uint64_t* rec, uint32
     }
 }
 
-// Unpacks a warp's queued vectors: re-reads each 32-byte vector and appends the
-// logits that reach the threshold.  Called by whole warps, at the end of the
-// warp's part of the stream and whenever its queue is nearly full.  Out of line
-// so that the streaming loop stays small.
-template<typename T>
-__device__ __forceinline__ void drain_warp_queue(RowShared& s, uint64_t* rec, uint32_t cap, Mode mode, float tau, const Vec32* vector_base,
-                                              uint32_t head, const uint32_t* queue, uint32_t queued)
+// ---- shared-memory ring fed by bulk asynchronous copies -------------------------
+// Bytes in flight are what a bandwidth-bound stream needs, and registers are the
+// wrong place to hold them: every warp owns `stages` ring slots of kChunkBytes
+// in shared memory, lane 0 asks the copy engine for the warp's next chunks
+// (cp.async.bulk, global -> shared, completion counted in bytes on one mbarrier
+// per slot) and the warp filters a chunk as soon as it has landed.  A warp only
+// ever waits for its own slots, so the stream has no block barrier, and the
+// copies of the next chunks proceed while hits are unpacked.
+
+#ifndef MOE_RING_VECTORS
+#define MOE_RING_VECTORS 8
+#endif
+constexpr int kVectorsPerLane = MOE_RING_VECTORS;            // 16-byte vectors a lane takes from one chunk
+constexpr uint32_t kChunkVectors = 32u * kVectorsPerLane;    // 16-byte vectors per chunk
+constexpr uint32_t kChunkBytes = kChunkVectors * 16u;
+constexpr uint32_t kSpinLimit = 1u << 20;                    // polls of one slot before the stream gives up on the ring
+
+__device__ __forceinline__ uint32_t shared_address(const void* pointer)
 {
-    using W = Wide<T>;
+    return static_cast<uint32_t>(__cvta_generic_to_shared(pointer));
+}
+
+__device__ __forceinline__ void barrier_init(uint64_t* barrier, uint32_t arrivals)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(shared_address(barrier)), "r"(arrivals) : "memory");
+}
+
+// one arrival that also announces `bytes` of copy traffic for the current phase
+__device__ __forceinline__ void barrier_expect_bytes(uint64_t* barrier, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(shared_address(barrier)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool barrier_test(uint64_t* barrier, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(shared_address(barrier)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Bounded: a slot that never completes makes the caller fall back to plain loads.
+__device__ __forceinline__ bool barrier_wait(uint64_t* barrier, uint32_t parity)
+{
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+        if (barrier_test(barrier, parity))
+            return true;
+    return false;
+}
+
+__device__ __forceinline__ uint64_t evict_first_policy()
+{
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+
+// `bytes` (a multiple of 16) from 16-byte aligned global memory into this CTA's shared memory
+__device__ __forceinline__ void bulk_copy_to_shared(void* destination, const void* source, uint32_t bytes, uint64_t* barrier, uint64_t policy)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+                     shared_address(destination)),
+                 "l"(__cvta_generic_to_global(source)), "r"(bytes), "r"(shared_address(barrier)), "l"(policy)
+                 : "memory");
+}
+
+// A warp's view of its ring.  All fields are warp-uniform.
+struct Ring
+{
+    unsigned char* data;   // stages * kChunkBytes
+    uint64_t* full;        // one barrier per slot
+    uint32_t stages;
+    uint32_t issue_slot;   // slot the next request goes to
+    uint32_t wait_slot;    // slot of the oldest outstanding request
+    uint32_t wait_parity;  // phase parity that request completes
+    uint32_t outstanding;  // requests not yet consumed
+    uint64_t policy;
+};
+
+// lane 0 only; the other lanes call ring_count_request to keep their cursors equal
+__device__ __forceinline__ void ring_issue(const Ring& ring, const void* source, uint32_t bytes)
+{
+    uint64_t* barrier = ring.full + ring.issue_slot;
+    barrier_expect_bytes(barrier, bytes);
+    bulk_copy_to_shared(ring.data + ring.issue_slot * kChunkBytes, source, bytes, barrier, ring.policy);
+}
+__device__ __forceinline__ void ring_count_request(Ring& ring)
+{
+    ring.issue_slot = (ring.issue_slot + 1u == ring.stages) ? 0u : ring.issue_slot + 1u;
+    ++ring.outstanding;
+}
+// whole warps only; the answer is the same for every lane
+__device__ __forceinline__ bool ring_acquire(const Ring& ring)
+{
+    return __all_sync(kFullMask, barrier_wait(ring.full + ring.wait_slot, ring.wait_parity)) != 0;
+}
+// the q-th outstanding request (q < stages), without consuming anything
+__device__ __forceinline__ bool ring_acquire_ahead(const Ring& ring, uint32_t q)
+{
+    uint32_t slot = ring.wait_slot + q;
+    uint32_t parity = ring.wait_parity;
+    if (slot >= ring.stages)
+    {
+        slot -= ring.stages;
+        parity ^= 1u;
+    }
+    return __all_sync(kFullMask, barrier_wait(ring.full + slot, parity)) != 0;
+}
+__device__ __forceinline__ const uint4* ring_ahead(const Ring& ring, uint32_t q)
+{
+    uint32_t slot = ring.wait_slot + q;
+    if (slot >= ring.stages)
+        slot -= ring.stages;
+    return reinterpret_cast<const uint4*>(ring.data + slot * kChunkBytes);
+}
+__device__ __forceinline__ const uint4* ring_front(const Ring& ring)
+{
+    return reinterpret_cast<const uint4*>(ring.data + ring.wait_slot * kChunkBytes);
+}
+__device__ __forceinline__ void ring_release(Ring& ring)
+{
+    if (ring.wait_slot + 1u == ring.stages)
+    {
+        ring.wait_slot = 0u;
+        ring.wait_parity ^= 1u;
+    }
+    else
+    {
+        ++ring.wait_slot;
+    }
+    --ring.outstanding;
+}
+// Waits (bounded) for every copy still in flight: shared memory must not be
+// written after the CTA has moved on.
+__device__ __forceinline__ bool ring_drain(Ring& ring)
+{
+    bool ok = true;
+    while (ring.outstanding != 0u)
+    {
+        ok = ring_acquire(ring) && ok;
+        ring_release(ring);
+    }
+    return ok;
+}
+
+// Unpacks a warp's queued hit vectors, one per lane and round, and appends the
+// logits that reach the threshold.  Called by whole warps.
+template<typename T>
+__device__ __forceinline__ void drain_hit_queue(RowShared& s, uint64_t* rec, uint32_t cap, Mode mode, float tau, uint32_t queued)
+{
+    using U = Unpack<T>;
     const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warp = threadIdx.x >> 5;
+    __syncwarp();
     for (uint32_t i = lane; i < queued; i += 32)
     {
-        const uint32_t vi = queue[i];
-        const Vec32 again = load_stream_32(vector_base + vi);
-        float x[W::kWidth];
-        W::values(again, x);
-        offer_values<W::kWidth>(s, rec, cap, mode, tau, x, head + vi * W::kWidth);
+        float x[U::kWidth];
+        U::values(s.hit_vector[warp][i], x);
+        offer_values<U::kWidth>(s, rec, cap, mode, tau, x, s.hit_index[warp][i]);
     }
     __syncwarp();
 }
 
-// The barrier-free streaming loop.  The first tile of the slice estimates a
-// threshold from the per-thread maxima (their r-th largest, r chosen so that a
-// few times k logits of the whole slice are expected above it; live mode uses
-// the tile maximum), then every other tile is filtered against that threshold
-// with one packed max, one compare and one warp vote per 256-bit load and no
-// block barrier.  A vector that reaches the threshold only has its index put
-// on its warp's queue (slot = running count + rank among the voting lanes: no
-// atomics, no divergence); each warp re-reads and unpacks its queued vectors
-// once its part of the stream is over.
-// All logits >= threshold end up in the buffer, so if at least k were found the
-// slice's k best are among them regardless of the order of the logits.  Returns
-// false (buffer reset) when fewer than k were found or the buffer overflowed;
-// the caller then runs the careful loop.
-template<typename T>
-__device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, uint32_t cap, Mode mode, uint32_t k, float temperature, const T* row_pointer, uint32_t vocab,
-                                                  uint32_t head, uint32_t vectors, uint32_t tail_begin, uint32_t group_begin, uint32_t group_end,
-                                                  bool first_rank, bool last_rank)
+enum StreamResult : int
 {
-    using W = Wide<T>;
+    kStreamCareful = 0, // not finished here: the careful loop must take the slice
+    kStreamDone = 1,    // every logit >= threshold is in the buffer and there are enough of them
+    kStreamTooLarge = 2 // live row whose live set cannot fit on chip: the exact kernel takes the row
+};
+
+// Rank (1 = largest) of the thread maximum of the sample that becomes the
+// threshold of a Top-K slice.  The sample holds `sample_elements` of the
+// slice's `slice_elements` logits, so the number of the slice's k best that
+// fall into it is Poisson with mean lambda = k * sample / slice; taking the
+// r-th largest sampled value with r = lambda + 4.3 sqrt(lambda) + 3 leaves
+// fewer than k logits of the slice above the threshold with probability below
+// 1e-5 (lambda 1: r = 9, tail 1e-6; lambda 4: r = 16, 5e-6; lambda 8: r = 24,
+// 5e-6; lambda 50: r = 84, 1e-6), and lets about r * slice / sample through.
+__device__ __forceinline__ uint32_t threshold_rank(uint32_t k, float slice_elements, float sample_elements)
+{
+    const float lambda = static_cast<float>(k) * fminf(1.0f, sample_elements / slice_elements);
+    return static_cast<uint32_t>(ceilf(lambda + 4.3f * sqrtf(lambda) + 3.0f));
+}
+
+// The barrier-free streaming loop.  The chunks that fill the ring first (one
+// "sample" of the slice) estimate a threshold from the per-thread maxima —
+// their r-th largest, see threshold_rank; live mode uses the sample maximum —
+// then every chunk is filtered against that threshold: one packed max per
+// vector, one compare and one warp vote per chunk.  A lane whose maximum
+// reached the threshold copies the vectors concerned to its warp's queue (slot
+// from a shared counter); the queue is unpacked one vector per lane when it is
+// half full and at the end.
+// All logits >= threshold end up in the buffer, so if at least k were found the
+// slice's k best are among them regardless of the order of the logits.
+template<typename T>
+__device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, uint64_t* rec, uint32_t cap, Mode mode, uint32_t k, float temperature,
+                                                 const T* row_pointer, uint32_t vocab, uint32_t head, uint32_t vectors, uint32_t tail_begin,
+                                                 uint32_t chunk_begin, uint32_t chunk_end, bool first_rank, bool last_rank)
+{
+    using U = Unpack<T>;
     const int tid = threadIdx.x;
-    const Vec32* vector_base = reinterpret_cast<const Vec32*>(row_pointer + head);
-    const uint32_t full_groups = vectors / kThreads;
-    const uint32_t full_end = min(group_end, full_groups);
-    if (group_begin + kGroupsPerTile > full_end)
-        return false; // not even one full tile
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    // the sample: the chunks every warp has on request when the stream starts, all of them complete
+    const uint32_t rounds_available = (chunk_end - chunk_begin) / kWarps;
+    const uint32_t complete_chunks = vectors / kChunkVectors;
+    uint32_t sample_rounds = min(ring.stages, rounds_available);
+    if (chunk_begin + kWarps * sample_rounds > complete_chunks)
+        sample_rounds = (complete_chunks > chunk_begin) ? (complete_chunks - chunk_begin) / kWarps : 0u;
+    if (sample_rounds == 0u)
+        return kStreamCareful;
 
     // rank r of the thread maximum that becomes the threshold
     uint32_t r = 1;
     if (mode == kTopK)
     {
-        const float slice_elements = static_cast<float>(group_end - group_begin) * (kThreads * W::kWidth);
-        const float wanted = MOE_WANTED_PER_K * static_cast<float>(k) + MOE_WANTED_EXTRA;
-        const float p_element = fminf(1.0f, wanted / slice_elements);
-        const float p_thread = 1.0f - __expf(static_cast<float>(kGroupsPerTile * W::kWidth) * log1pf(-fminf(p_element, 0.999f)));
-        r = static_cast<uint32_t>(ceilf(p_thread * kThreads));
-        r = max(r, min(k, 4u));
+        const float slice_elements = static_cast<float>(chunk_end - chunk_begin) * (kChunkVectors * U::kWidth);
+        const float sample_elements = static_cast<float>(sample_rounds) * (kWarps * kChunkVectors * U::kWidth);
+        r = threshold_rank(k, slice_elements, sample_elements);
         if (r > (3u * kThreads) / 4u)
-            return false; // the threshold would pass nearly everything
+            return kStreamCareful; // the threshold would pass nearly everything
     }
 
-    Vec32 v[kGroupsPerTile];
-#pragma unroll
-    for (int j = 0; j < kGroupsPerTile; ++j)
-        v[j] = load_stream_32(vector_base + (group_begin + j) * kThreads + tid);
-    float top = W::maximum(v[0]);
-#pragma unroll
-    for (int j = 1; j < kGroupsPerTile; ++j)
-        top = fmaxf(top, W::maximum(v[j]));
-    const uint32_t my_key = (top == top) ? ordered_key(top) : 0u;
-    // Each warp sorts its 32 thread maxima with a shuffle network; the block-wide
-    // rank of a maximum is its warp rank plus, for every other warp, the number
-    // of larger maxima found by binary search in that warp's sorted list.
-    const int lane = tid & 31;
-    const int warp = tid >> 5;
-    uint32_t sorted_key = my_key; // descending by lane after the network
-#pragma unroll
-    for (int size = 2; size <= 32; size <<= 1)
-    {
-#pragma unroll
-        for (int stride = size >> 1; stride > 0; stride >>= 1)
-        {
-            const uint32_t other = __shfl_xor_sync(kFullMask, sorted_key, stride);
-            const bool descending = (lane & size) == 0;
-            const bool lower_lane = (lane & stride) == 0;
-            sorted_key = (descending == lower_lane) ? max(sorted_key, other) : min(sorted_key, other);
-        }
-    }
+    const unsigned char* body = reinterpret_cast<const unsigned char*>(row_pointer + head);
+    // this warp's chunks: chunk_begin + warp, + kWarps, ...
+    const uint32_t my_chunks = (chunk_end - chunk_begin - static_cast<uint32_t>(warp) + kWarps - 1u) / kWarps;
+    const auto request = [&](uint32_t i) {
+        const uint32_t chunk = chunk_begin + static_cast<uint32_t>(warp) + kWarps * i;
+        const uint32_t first_vector = chunk * kChunkVectors;
+        const uint32_t count = min(kChunkVectors, vectors - first_vector);
+        if (lane == 0)
+            ring_issue(ring, body + static_cast<size_t>(chunk) * kChunkBytes, count * 16u);
+        ring_count_request(ring);
+    };
+
+    MOE_LAP_DECLARE();
     uint32_t* lists = s.sel.hist; // kThreads entries, untouched while streaming
-    lists[tid] = sorted_key;
-    uint32_t* const my_queue = s.hit_queue[warp];
-    const unsigned lanes_below = (1u << lane) - 1u;
-
+    uint32_t* const hit_count = &s.hit_count[warp];
+    uint32_t sorted_key = 0;
     uint32_t live_maximum = 0; // live mode, second attempt: the slice maximum found by the first
+    bool fault = false;
     for (int attempt = 0;; ++attempt)
     {
-        // Threshold = the r-th largest thread maximum: at least r logits of the tile reach it.
+        const uint32_t ahead = min(ring.stages, my_chunks);
+        for (uint32_t i = 0; i < ahead; ++i)
+            request(i);
+
+        if (attempt == 0)
+        {
+            // Each warp sorts its 32 thread maxima with a shuffle network; the block-wide
+            // rank of a maximum is its warp rank plus, for every other warp, the number
+            // of larger maxima in that warp's sorted list.
+            float top = __uint_as_float(0x7FC00000u);
+            for (uint32_t q = 0; q < sample_rounds; ++q)
+            {
+                if (!ring_acquire_ahead(ring, q))
+                {
+                    fault = true;
+                    break;
+                }
+                const uint4* sample = ring_ahead(ring, q);
+#pragma unroll
+                for (int j = 0; j < kVectorsPerLane; ++j)
+                    top = fmaxf(top, U::maximum(sample[j * 32 + lane]));
+            }
+            sorted_key = (top == top) ? ordered_key(top) : 0u; // descending by lane after the network
+#pragma unroll
+            for (int size = 2; size <= 32; size <<= 1)
+            {
+#pragma unroll
+                for (int stride = size >> 1; stride > 0; stride >>= 1)
+                {
+                    const uint32_t other = __shfl_xor_sync(kFullMask, sorted_key, stride);
+                    const bool descending = (lane & size) == 0;
+                    const bool lower_lane = (lane & stride) == 0;
+                    sorted_key = (descending == lower_lane) ? max(sorted_key, other) : min(sorted_key, other);
+                }
+            }
+            lists[tid] = sorted_key;
+        }
+
+        // Threshold = the r-th largest thread maximum: at least r logits of the sample reach it.
         if (tid == 0)
             s.sel.bucket = 0;
+        if (lane == 0)
+            *hit_count = 0;
         __syncthreads();
         if (static_cast<uint32_t>(lane) < r)
         {
             uint32_t rank_in_block = lane; // keys strictly greater, plus equal keys of earlier warps, precede this one
-            for (int w = 0; w < kThreads / 32; ++w)
+            if (r <= 32u)
             {
-                if (w == warp)
-                    continue;
-                const uint32_t* list = lists + w * 32;
-                uint32_t lo = 0, hi = 32;
-                while (lo < hi)
+                // Only rank r - 1 is looked for: a list cannot hold more than r - 1 keys ahead of
+                // that one, so its first r entries decide (independent loads, no search).
+#pragma unroll
+                for (int w = 0; w < kWarps; ++w)
                 {
-                    const uint32_t mid = (lo + hi) >> 1;
-                    const uint32_t value = list[mid];
-                    if ((value > sorted_key) || (value == sorted_key && w < warp))
-                        lo = mid + 1;
-                    else
-                        hi = mid;
+                    if (w == warp)
+                        continue;
+                    const uint32_t* list = lists + w * 32;
+                    for (uint32_t q = 0; q < r; ++q)
+                    {
+                        const uint32_t value = list[q];
+                        rank_in_block += ((value > sorted_key) || (value == sorted_key && w < warp)) ? 1u : 0u;
+                    }
                 }
-                rank_in_block += lo;
+            }
+            else
+            {
+                for (int w = 0; w < kWarps; ++w)
+                {
+                    if (w == warp)
+                        continue;
+                    const uint32_t* list = lists + w * 32;
+                    uint32_t lo = 0, hi = 32;
+                    while (lo < hi)
+                    {
+                        const uint32_t mid = (lo + hi) >> 1;
+                        const uint32_t value = list[mid];
+                        if ((value > sorted_key) || (value == sorted_key && w < warp))
+                            lo = mid + 1;
+                        else
+                            hi = mid;
+                    }
+                    rank_in_block += lo;
+                }
             }
             if (rank_in_block == r - 1)
                 s.sel.bucket = sorted_key;
@@ -681,120 +836,161 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
         __syncthreads();
         // a live row whose first attempt overflowed knows its true maximum now: use it
         const uint32_t threshold_key = (live_maximum != 0u) ? live_maximum : s.sel.bucket;
-        if (threshold_key <= kKeyNegInf)
-            return false; // the tile holds (almost) nothing finite
-        float tau;
-        if (mode == kLive)
+        bool usable = threshold_key > kKeyNegInf; // else the sample holds (almost) nothing finite
+        float tau = 0.0f;
+        if (usable)
         {
-            if (tid == 0)
-                atomicMax(&s.maxkey, threshold_key);
-            tau = live_threshold(threshold_key, temperature);
-        }
-        else
-        {
-            tau = key_to_float(threshold_key);
+            if (mode == kLive)
+            {
+                if (tid == 0)
+                    atomicMax(&s.maxkey, threshold_key);
+                tau = live_threshold(threshold_key, temperature);
+            }
+            else
+            {
+                tau = key_to_float(threshold_key);
+            }
         }
 
-        uint32_t g = group_begin;
-        uint32_t my_hits = 0;
+        MOE_LAP(0); // threshold estimate
         uint32_t seen_max = threshold_key; // live mode: the largest key this warp knows of
-        if (attempt > 0)
+        // live mode, first attempt, buffer already overflowed: only the maximum is still of interest
+        bool maximum_only = false;
+        for (uint32_t i = 0; usable && !fault && i < my_chunks; ++i)
         {
-#pragma unroll
-            for (int j = 0; j < kGroupsPerTile; ++j)
-                v[j] = load_stream_32(vector_base + (g + j) * kThreads + tid);
-        }
-        for (;;)
-        {
-#pragma unroll
-            for (int j = 0; j < kGroupsPerTile; ++j)
+            if (!ring_acquire(ring))
             {
-                const float best = W::maximum(v[j]);
-                const bool hit = best >= tau;
-                const unsigned voters = __ballot_sync(kFullMask, hit);
-                if (voters != 0)
+                fault = true;
+                break;
+            }
+            MOE_LAP(1); // waiting for the copy engine
+            const uint4* front = ring_front(ring);
+            uint4 v[kVectorsPerLane];
+#pragma unroll
+            for (int j = 0; j < kVectorsPerLane; ++j)
+                v[j] = front[j * 32 + lane];
+            const uint32_t first_vector = (chunk_begin + static_cast<uint32_t>(warp) + kWarps * i) * kChunkVectors;
+            if (first_vector + kChunkVectors > vectors)
+            {
+                // the ragged last chunk of the row: slots beyond it hold stale bytes
+#pragma unroll
+                for (int j = 0; j < kVectorsPerLane; ++j)
+                    if (first_vector + j * 32 + lane >= vectors)
+                        v[j] = U::nan_vector();
+            }
+            float top[kVectorsPerLane];
+#pragma unroll
+            for (int j = 0; j < kVectorsPerLane; ++j)
+                top[j] = U::maximum(v[j]);
+            float best = top[0];
+#pragma unroll
+            for (int j = 1; j < kVectorsPerLane; ++j)
+                best = fmaxf(best, top[j]);
+            const bool hit = best >= tau;
+            // the vote needs every lane's values, so all reads of the slot are complete behind it
+            const unsigned voters = __ballot_sync(kFullMask, hit);
+            ring_release(ring);
+            if (i + ring.stages < my_chunks)
+                request(i + ring.stages);
+            MOE_LAP(2); // filter + refill request
+            if (voters != 0)
+            {
+                if (maximum_only)
                 {
-                    const uint32_t slot = my_hits + __popc(voters & lanes_below);
-                    if (hit && slot < kWarpHitCap)
-                        my_queue[slot] = (g + j) * kThreads + tid;
-                    my_hits += __popc(voters);
-                    if (mode == kLive && hit && ordered_key(best) > seen_max)
+                    if (hit && ordered_key(best) > seen_max)
                         atomicMax(&s.maxkey, ordered_key(best));
-                    if (my_hits > kWarpHitCap - 32)
+                }
+                else
+                {
+                    if (hit)
                     {
-                        // the next vote might not fit: unpack what is queued now (rare; live rows with a late maximum)
+                        // only the few lanes that have something to queue come here
+#pragma unroll
+                        for (int j = 0; j < kVectorsPerLane; ++j)
+                        {
+                            if (!(top[j] >= tau))
+                                continue;
+                            const uint32_t first_index = head + (first_vector + j * 32 + lane) * U::kWidth;
+                            const uint32_t slot = atomicAdd(hit_count, 1u);
+                            if (slot < kHitQueue)
+                            {
+                                s.hit_vector[warp][slot] = v[j];
+                                s.hit_index[warp][slot] = first_index;
+                            }
+                            else
+                            {
+                                // the queue is full (a chunk in which nearly everything passes): unpack in place
+                                float x[U::kWidth];
+                                U::values(v[j], x);
+                                offer_values<U::kWidth>(s, rec, cap, mode, tau, x, first_index);
+                            }
+                            if (mode == kLive && ordered_key(top[j]) > seen_max)
+                                atomicMax(&s.maxkey, ordered_key(top[j]));
+                        }
+                    }
+                    __syncwarp();
+                    const uint32_t queued = min(*reinterpret_cast<volatile uint32_t*>(hit_count), kHitQueue);
+                    if (queued >= kHitQueue / 2u)
+                    {
+                        if (mode == kLive)
+                            tau = fmaxf(tau, live_threshold(*reinterpret_cast<volatile uint32_t*>(&s.maxkey), temperature));
+                        drain_hit_queue<T>(s, rec, cap, mode, tau, queued);
+                        if (lane == 0)
+                            *hit_count = 0;
                         __syncwarp();
-                        drain_warp_queue<T>(s, rec, cap, mode, tau, vector_base, head, my_queue, my_hits);
-                        my_hits = 0;
+                        if (*reinterpret_cast<volatile uint32_t*>(&s.overflow) != 0u)
+                        {
+                            if (mode == kLive && live_maximum == 0u)
+                                maximum_only = true; // keep looking for the row's maximum
+                            else
+                                break;
+                        }
                     }
                 }
             }
-            g += kGroupsPerTile;
-            if (g + kGroupsPerTile > full_end)
-                break;
-#pragma unroll
-            for (int j = 0; j < kGroupsPerTile; ++j)
-                v[j] = load_stream_32(vector_base + (g + j) * kThreads + tid);
             if (mode == kLive)
             {
                 seen_max = *reinterpret_cast<volatile uint32_t*>(&s.maxkey);
                 tau = fmaxf(tau, live_threshold(seen_max, temperature));
             }
+            MOE_LAP(3); // hits
         }
-        // full groups that do not fill a tile, then the ragged last group
-        for (; g < group_end; ++g)
-        {
-            const uint32_t vi = g * kThreads + tid;
-            const Vec32 one = (vi < vectors) ? load_stream_32(vector_base + vi) : W::nan_vector();
-            const float best = W::maximum(one);
-            const bool hit = best >= tau;
-            const unsigned voters = __ballot_sync(kFullMask, hit);
-            if (voters != 0)
-            {
-                const uint32_t slot = my_hits + __popc(voters & lanes_below);
-                if (hit && slot < kWarpHitCap)
-                    my_queue[slot] = vi;
-                my_hits += __popc(voters);
-                if (mode == kLive && hit && ordered_key(best) > seen_max)
-                    atomicMax(&s.maxkey, ordered_key(best));
-                if (my_hits > kWarpHitCap - 32)
-                {
-                    __syncwarp();
-                    drain_warp_queue<T>(s, rec, cap, mode, tau, vector_base, head, my_queue, my_hits);
-                    my_hits = 0;
-                }
-            }
-        }
-        // logits before / after the 32-byte aligned body of the row
-        if (first_rank && tid < static_cast<int>(head))
-        {
-            const float x[1] = {LogitTraits<T>::widen(row_pointer, tid)};
-            offer_values<1>(s, rec, cap, mode, tau, x, static_cast<uint32_t>(tid));
-        }
-        if (last_rank && tail_begin + tid < vocab)
-        {
-            const float x[1] = {LogitTraits<T>::widen(row_pointer, tail_begin + tid)};
-            offer_values<1>(s, rec, cap, mode, tau, x, tail_begin + tid);
-        }
-        // this warp's queued vectors: a re-read of 32 bytes each, unpacked against the latest threshold
-        __syncwarp();
         if (mode == kLive)
             tau = fmaxf(tau, live_threshold(*reinterpret_cast<volatile uint32_t*>(&s.maxkey), temperature));
-        drain_warp_queue<T>(s, rec, cap, mode, tau, vector_base, head, my_queue, my_hits);
-        __syncthreads();
+        __syncwarp();
+        drain_hit_queue<T>(s, rec, cap, mode, tau, min(*reinterpret_cast<volatile uint32_t*>(hit_count), kHitQueue));
+        MOE_LAP(3);
+        MOE_LAP_FLUSH();
+        if (!ring_drain(ring))
+            fault = true;
+        if (usable && !fault)
+        {
+            // logits before / after the 16-byte aligned body of the row
+            if (first_rank && tid < static_cast<int>(head))
+            {
+                const float x[1] = {LogitTraits<T>::widen(row_pointer, tid)};
+                offer_values<1>(s, rec, cap, mode, tau, x, static_cast<uint32_t>(tid));
+            }
+            if (last_rank && tail_begin + tid < vocab)
+            {
+                const float x[1] = {LogitTraits<T>::widen(row_pointer, tail_begin + tid)};
+                offer_values<1>(s, rec, cap, mode, tau, x, tail_begin + tid);
+            }
+        }
+        const bool any_fault = __syncthreads_or(fault ? 1 : 0) != 0;
         const uint32_t found = s.count;
         const bool overflow = s.overflow != 0;
+        const uint32_t seen_maximum = s.maxkey;
         __syncthreads();
-        if (!overflow && (mode == kLive || found >= k))
-            return true;
+        if (usable && !any_fault && !overflow && (mode == kLive || found >= k))
+            return kStreamDone;
         // Too few logits reached the sampled threshold (or far too many): forget
         // them.  A short count is retried once or twice with a lower threshold —
         // the slice is in L2 now — before the careful loop takes over.  A live
         // row that overflowed (its maximum came late, so the threshold of the
-        // first tile let too much through) has seen its true maximum by now and
-        // is streamed once more against it.
-        const uint32_t seen_maximum = s.maxkey;
-        __syncthreads();
+        // sample let too much through) has seen its true maximum by now and
+        // is streamed once more against it; if it overflows again its live set
+        // really is too large for the chip.
         if (tid == 0)
         {
             s.count = 0;
@@ -802,16 +998,20 @@ __device__ __forceinline__ bool stream_slice_fast(RowShared& s, uint64_t* rec, u
             s.overflow = 0;
         }
         __syncthreads();
+        if (!usable || any_fault)
+            return kStreamCareful;
         if (mode == kLive)
         {
-            if (live_maximum != 0u || seen_maximum == 0u)
-                return false; // already retried with the true maximum: the live set really is large
+            if (live_maximum != 0u)
+                return kStreamTooLarge;
+            if (seen_maximum == 0u)
+                return kStreamCareful;
             live_maximum = seen_maximum;
             continue;
         }
         const uint32_t limit = (3u * kThreads) / 4u;
         if (overflow || r >= limit || attempt >= 2)
-            return false;
+            return kStreamCareful;
         r = min(limit, 4u * r + 16u);
     }
 }
@@ -828,27 +1028,39 @@ __device__ __forceinline__ void reduce_buffer(Ctx& c, bool sort)
     if (c.aborted)
         return;
     const uint32_t n = s.count;
-    if (n <= kThreads)
+    if (n <= 2u * kThreads)
     {
-        // One record per thread.  Live mode first blanks the records that fell
-        // out of the live window of the final maximum (0 sorts last and is not
-        // counted); then one sort puts the survivors in rank order.
+        // At most two records per thread.  Live mode first blanks the records that
+        // fell out of the live window of the final maximum (0 sorts last and is
+        // not counted); then one sort puts the survivors in rank order, and the
+        // k best of a Top-K buffer are its front.
         uint32_t kept = n;
         if (c.mode == kLive)
         {
             const uint32_t tid = threadIdx.x;
             const float peak = __fdiv_rn(key_to_float(s.maxkey), c.temperature);
-            bool keep = false;
-            if (tid < n)
+            uint32_t keeps = 0;
+            for (uint32_t i = tid; i < n; i += kThreads)
             {
-                const float offset = scaled_offset(key_to_float(record_key(c.rec[tid])), c.temperature, peak);
-                keep = !(offset < kDeadOffset); // keeps NaN offsets: the epilogue reports them
-                if (!keep)
-                    c.rec[tid] = 0ull;
+                const float offset = scaled_offset(key_to_float(record_key(c.rec[i])), c.temperature, peak);
+                if (offset < kDeadOffset) // keeps NaN offsets: the epilogue reports them
+                    c.rec[i] = 0ull;
+                else
+                    ++keeps;
             }
-            kept = static_cast<uint32_t>(__syncthreads_count(keep));
+            keeps = __reduce_add_sync(kFullMask, keeps);
+            if (tid == 0)
+                s.sel.out_count = 0;
+            __syncthreads();
+            if ((tid & 31u) == 0u && keeps != 0u)
+                atomicAdd(&s.sel.out_count, keeps);
+            __syncthreads();
+            kept = s.sel.out_count;
         }
-        block_rank_sort_descending<kThreads>(c.rec, n);
+        if (n <= kThreads)
+            block_rank_sort_descending<kThreads>(c.rec, n);
+        else
+            block_rank_sort_descending2<kThreads>(c.rec, n);
         if (c.mode != kLive)
             kept = min(n, c.k);
         if (kept != n)
@@ -860,46 +1072,13 @@ __device__ __forceinline__ void reduce_buffer(Ctx& c, bool sort)
         c.sorted = true;
         return;
     }
-    if (c.mode != kLive && n <= 2u * kThreads && c.k <= kThreads / 2u)
-    {
-        // A little over one record per thread: sort the first kThreads, keep
-        // their k best, and let only the spare records that beat the k-th of
-        // them join a second, much smaller sort.
-        const uint32_t tid = threadIdx.x;
-        const uint32_t extra = n - kThreads;
-        const uint64_t spare = tid < extra ? c.rec[kThreads + tid] : 0ull;
-        if (tid == 0)
-            s.sel.out_count = 0;
-        block_rank_sort_descending<kThreads>(c.rec, kThreads); // ends with a barrier
-        const uint64_t pivot = c.rec[c.k - 1u];
-        const bool joins = spare > pivot;
-        const unsigned voters = __ballot_sync(kFullMask, joins);
-        uint32_t base = 0;
-        if ((tid & 31u) == 0u && voters != 0u)
-            base = atomicAdd(&s.sel.out_count, static_cast<uint32_t>(__popc(voters)));
-        base = __shfl_sync(kFullMask, base, 0);
-        __syncthreads(); // every thread has read the pivot
-        if (joins)
-            c.rec[c.k + base + __popc(voters & ((1u << (tid & 31u)) - 1u))] = spare;
-        __syncthreads();
-        const uint32_t merged = c.k + s.sel.out_count; // at most k + kThreads <= cap
-        if (merged <= kThreads)
-        {
-            block_rank_sort_descending<kThreads>(c.rec, merged);
-            if (tid == 0)
-                s.count = c.k;
-            __syncthreads();
-            c.sorted = true;
-            return;
-        }
-        if (tid == 0)
-            s.count = merged;
-        __syncthreads();
-    }
     flush_buffer(c);
-    if (sort && !c.aborted && s.count <= kThreads)
+    if (sort && !c.aborted && s.count <= 2u * kThreads)
     {
-        block_rank_sort_descending<kThreads>(c.rec, s.count);
+        if (s.count <= kThreads)
+            block_rank_sort_descending<kThreads>(c.rec, s.count);
+        else
+            block_rank_sort_descending2<kThreads>(c.rec, s.count);
         c.sorted = true;
     }
 }
@@ -924,6 +1103,10 @@ __device__ __forceinline__ void finish_row_block(const SampleArgs& a, RowShared&
         if (n <= kThreads)
         {
             block_rank_sort_descending<kThreads>(c.rec, n);
+        }
+        else if (n <= 2u * kThreads)
+        {
+            block_rank_sort_descending2<kThreads>(c.rec, n);
         }
         else
         {
@@ -1008,18 +1191,24 @@ __device__ __forceinline__ void finish_row_block(const SampleArgs& a, RowShared&
     }
 }
 
-__host__ __device__ constexpr size_t shared_bytes_for(uint32_t cap)
+// Shared memory of a CTA: ring | RowShared | cap records | cap floats.
+__host__ __device__ constexpr size_t ring_bytes_for(uint32_t stages)
 {
-    return sizeof(RowShared) + static_cast<size_t>(cap) * (sizeof(uint64_t) + sizeof(float));
+    return static_cast<size_t>(stages) * kWarps * kChunkBytes;
+}
+__host__ __device__ constexpr size_t shared_bytes_for(uint32_t cap, uint32_t stages = 0)
+{
+    return ring_bytes_for(stages) + sizeof(RowShared) + static_cast<size_t>(cap) * (sizeof(uint64_t) + sizeof(float));
 }
 
-template<typename T, int kResident>
-__global__ void __launch_bounds__(kThreads, kResident) sample_rows_kernel(const SampleArgs a, const Workspace ws, const uint32_t splits)
+template<typename T, bool kLargeBuffer>
+__global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(const SampleArgs a, const Workspace ws, const uint32_t splits, const uint32_t stages)
 {
-    extern __shared__ __align__(16) unsigned char shared_raw[];
-    RowShared& s = *reinterpret_cast<RowShared*>(shared_raw);
-    constexpr uint32_t kCapacity = (kResident >= 5) ? kCapSmall : kCapLarge;
-    uint64_t* const records = reinterpret_cast<uint64_t*>(shared_raw + sizeof(RowShared));
+    extern __shared__ __align__(128) unsigned char shared_raw[];
+    constexpr uint32_t kCapacity = kLargeBuffer ? kCapLarge : kCapSmall;
+    unsigned char* const ring_base = shared_raw;
+    RowShared& s = *reinterpret_cast<RowShared*>(shared_raw + ring_bytes_for(stages));
+    uint64_t* const records = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(&s) + sizeof(RowShared));
     float* const scratch = reinterpret_cast<float*>(records + kCapacity);
     const uint32_t row = blockIdx.x / splits;
     const uint32_t rank = blockIdx.x - row * splits;
@@ -1100,37 +1289,58 @@ __global__ void __launch_bounds__(kThreads, kResident) sample_rows_kernel(const 
         s.abort_flag = 0;
         s.overflow = 0;
     }
+    Ring ring;
+    ring.data = ring_base + static_cast<size_t>(tid >> 5) * stages * kChunkBytes;
+    ring.full = s.ring_full[tid >> 5];
+    ring.stages = stages;
+    ring.issue_slot = ring.wait_slot = ring.wait_parity = ring.outstanding = 0u;
+    ring.policy = evict_first_policy();
+    if ((tid & 31) == 0)
+    {
+        for (uint32_t slot = 0; slot < stages; ++slot)
+            barrier_init(ring.full + slot, 1u);
+        // make the initialised barriers visible to the copy engine
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
     __syncthreads();
 
     // ---- the slice of this CTA -------------------------------------------------
     const T* row_pointer = static_cast<const T*>(a.logits) + static_cast<size_t>(row) * a.row_stride;
     const uint32_t vocab = a.vocab;
-    // the row body is walked in 32-byte vectors from the first 32-byte boundary;
-    // `groups` of kThreads vectors are dealt to the row's CTAs in contiguous runs
+    // the row body is walked in 16-byte vectors from the first 32-byte boundary;
+    // `groups` of kThreads vectors (two ring chunks of every warp's size) are
+    // dealt to the row's CTAs in contiguous runs
     const uint32_t misaligned = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(row_pointer) & 31u);
     uint32_t head = ((32u - misaligned) & 31u) / static_cast<uint32_t>(sizeof(T));
     head = min(head, vocab);
-    const uint32_t vectors = (vocab - head) / Wide<T>::kWidth;
-    const uint32_t tail_begin = head + vectors * Wide<T>::kWidth;
-    const uint32_t groups = (vectors + kThreads - 1) / kThreads;
+    const uint32_t vectors = (vocab - head) / Unpack<T>::kWidth;
+    const uint32_t tail_begin = head + vectors * Unpack<T>::kWidth;
+    constexpr uint32_t kGroupVectors = (kChunkVectors > kThreads) ? kChunkVectors : static_cast<uint32_t>(kThreads);
+    const uint32_t groups = (vectors + kGroupVectors - 1) / kGroupVectors;
     const uint32_t group_begin = static_cast<uint32_t>(static_cast<uint64_t>(rank) * groups / splits);
     const uint32_t group_end = static_cast<uint32_t>(static_cast<uint64_t>(rank + 1) * groups / splits);
+    const uint32_t chunks = (vectors + kChunkVectors - 1) / kChunkVectors;
+    const uint32_t chunk_begin = group_begin * (kGroupVectors / kChunkVectors);
+    const uint32_t chunk_end = min(group_end * (kGroupVectors / kChunkVectors), chunks);
 
     MOE_PHASE_MARK(0);
-    const bool streamed = stream_slice_fast<T>(s, c.rec, c.cap, c.mode, c.k, p.temperature, row_pointer, vocab, head, vectors, tail_begin, group_begin,
-                                               group_end, rank == 0, rank == splits - 1);
+    const int streamed = stream_slice_ring<T>(s, ring, c.rec, c.cap, c.mode, c.k, p.temperature, row_pointer, vocab, head, vectors, tail_begin, chunk_begin,
+                                              chunk_end, rank == 0, rank == splits - 1);
     MOE_PHASE_MARK(1);
     MOE_TRACE(1);
 #ifdef MOE_PHASE_TIMERS
     if (tid == 0)
     {
-        atomicAdd(&g_phase_cycles[10], static_cast<unsigned long long>(streamed ? s.count : 0u));
-        atomicAdd(&g_phase_cycles[9], streamed ? 0ull : 1ull);
+        atomicAdd(&g_phase_cycles[10], static_cast<unsigned long long>(streamed == kStreamDone ? s.count : 0u));
+        atomicAdd(&g_phase_cycles[9], streamed == kStreamDone ? 0ull : 1ull);
     }
 #endif
-    if (!streamed)
-        stream_slice_safe<T>(c, row_pointer, vocab, head, 2u * vectors, tail_begin, 2u * group_begin, min(2u * group_end, (2u * vectors + kThreads - 1) / kThreads),
-                             rank, splits); // the same logits in 16-byte vectors
+    if (streamed == kStreamTooLarge)
+        c.aborted = true;
+    else if (streamed == kStreamCareful)
+        stream_slice_safe<T>(c, row_pointer, vocab, head, vectors, tail_begin, group_begin * (kGroupVectors / kThreads),
+                             min(group_end * (kGroupVectors / kThreads), (vectors + kThreads - 1) / kThreads), rank, splits);
     MOE_PHASE_MARK(2);
     if (a.overlap_previous)
     {
@@ -1228,7 +1438,7 @@ __global__ void __launch_bounds__(kThreads, kResident) sample_rows_kernel(const 
 __global__ void __launch_bounds__(kThreads, 4) merge_candidates_kernel(const uint64_t* gathered, uint32_t shards, uint32_t rows, uint32_t top_k,
                                                                         const SampleArgs a)
 {
-    extern __shared__ __align__(16) unsigned char shared_raw[];
+    extern __shared__ __align__(128) unsigned char shared_raw[];
     RowShared& s = *reinterpret_cast<RowShared*>(shared_raw);
     uint64_t* const records = reinterpret_cast<uint64_t*>(shared_raw + sizeof(RowShared));
     float* const scratch = reinterpret_cast<float*>(records + kCapLarge);
@@ -1310,21 +1520,17 @@ __global__ void __launch_bounds__(kThreads, 4) merge_candidates_kernel(const uin
     finish_row_block(a, s, c, p, row, nullptr, nullptr);
 }
 
-template<typename T, int kResident>
-cudaError_t launch_typed(const SampleArgs& args, const Workspace& ws, uint32_t splits, cudaStream_t stream)
+template<typename T, bool kLargeBuffer>
+cudaError_t launch_typed(const SampleArgs& args, const Workspace& ws, uint32_t splits, uint32_t stages, cudaStream_t stream)
 {
-    static bool configured = false; // per instantiation; the attribute is per device function
-    const size_t shared_bytes = shared_bytes_for(kResident >= 5 ? kCapSmall : kCapLarge);
-    if (!configured)
-    {
-        cudaError_t status = cudaFuncSetAttribute(sample_rows_kernel<T, kResident>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared_bytes));
-        if (status != cudaSuccess)
-            return status;
-        configured = true;
-    }
+    static SharedOptIn opt_in;
+    const size_t shared_bytes = shared_bytes_for(kLargeBuffer ? kCapLarge : kCapSmall, stages);
+    cudaError_t status = opt_in_shared(opt_in, sample_rows_kernel<T, kLargeBuffer>, shared_bytes);
+    if (status != cudaSuccess)
+        return status;
     if (!args.overlap_previous)
     {
-        sample_rows_kernel<T, kResident><<<args.rows * splits, kThreads, shared_bytes, stream>>>(args, ws, splits);
+        sample_rows_kernel<T, kLargeBuffer><<<args.rows * splits, kThreads, shared_bytes, stream>>>(args, ws, splits, stages);
         return cudaGetLastError();
     }
     cudaLaunchConfig_t config = {};
@@ -1337,7 +1543,29 @@ cudaError_t launch_typed(const SampleArgs& args, const Workspace& ws, uint32_t s
     attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
     config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, sample_rows_kernel<T, kResident>, args, ws, splits);
+    return cudaLaunchKernelEx(&config, sample_rows_kernel<T, kLargeBuffer>, args, ws, splits, stages);
+}
+
+// Ring slots per warp and CTAs per SM that go with them.  Two CTAs per SM with
+// two slots of kChunkBytes (4 KiB) per warp keep 128 KiB per SM on request.
+uint32_t ring_stages(bool large_top_k)
+{
+    static const uint32_t forced = [] {
+        const char* text = std::getenv("MOE_B200_RING_STAGES");
+        const long value = text != nullptr ? std::strtol(text, nullptr, 10) : 0;
+        return (value >= 1 && value <= kMaxStages) ? static_cast<uint32_t>(value) : 0u;
+    }();
+    if (forced != 0u)
+        return forced;
+    return large_top_k ? 1u : 2u;
+}
+
+uint32_t resident_per_sm(bool large_top_k, uint32_t stages)
+{
+    // 227 KiB per SM, 1 KiB reserved per CTA
+    const size_t per_cta = shared_bytes_for(large_top_k ? kCapLarge : kCapSmall, stages) + 1024u;
+    const uint32_t fit = static_cast<uint32_t>((227u * 1024u) / per_cta);
+    return fit < 1u ? 1u : (fit > 8u ? 8u : fit); // 8 CTAs of 256 threads fill an SM's 2048 thread slots
 }
 
 } // namespace
@@ -1346,15 +1574,16 @@ cudaError_t launch_sample_rows(const SampleArgs& args, const Workspace& ws, uint
 {
     if (args.rows == 0)
         return cudaSuccess;
+    const uint32_t stages = ring_stages(args.large_top_k);
     if (args.large_top_k)
     {
         if (args.dtype == MOE_DTYPE_F32)
-            return launch_typed<float, 4>(args, ws, splits, stream);
-        return launch_typed<__nv_bfloat16, 4>(args, ws, splits, stream);
+            return launch_typed<float, true>(args, ws, splits, stages, stream);
+        return launch_typed<__nv_bfloat16, true>(args, ws, splits, stages, stream);
     }
     if (args.dtype == MOE_DTYPE_F32)
-        return launch_typed<float, MOE_RESIDENT>(args, ws, splits, stream);
-    return launch_typed<__nv_bfloat16, MOE_RESIDENT>(args, ws, splits, stream);
+        return launch_typed<float, false>(args, ws, splits, stages, stream);
+    return launch_typed<__nv_bfloat16, false>(args, ws, splits, stages, stream);
 }
 
 cudaError_t launch_merge_candidates(const uint64_t* gathered, uint32_t shards, uint32_t rows, uint32_t top_k, const moe_row_params* params,
@@ -1363,15 +1592,10 @@ cudaError_t launch_merge_candidates(const uint64_t* gathered, uint32_t shards, u
 {
     if (rows == 0)
         return cudaSuccess;
-    static bool configured = false;
+    static SharedOptIn opt_in;
     const size_t shared_bytes = shared_bytes_for(kCapLarge);
-    if (!configured)
-    {
-        cudaError_t status = cudaFuncSetAttribute(merge_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared_bytes));
-        if (status != cudaSuccess)
-            return status;
-        configured = true;
-    }
+    if (cudaError_t status = opt_in_shared(opt_in, merge_candidates_kernel, shared_bytes))
+        return status;
     SampleArgs a = {};
     a.rows = rows;
     a.params = params;
@@ -1388,21 +1612,22 @@ cudaError_t launch_merge_candidates(const uint64_t* gathered, uint32_t shards, u
 
 uint32_t choose_splits(uint32_t rows, uint32_t vocab, int dtype, int sm_count, uint32_t slice_slots, bool large_top_k, bool overlapped)
 {
-    // Cut rows into slices only while all CTAs of the launch stay resident at
-    // once (5 per SM, 4 with the large record buffer): a single wave has no ragged second wave, and the fixed
-    // per-slice work (threshold estimate, select, publication) stays small
-    // next to a slice of at least 64 KiB.  When consecutive launches overlap,
-    // the SMs are kept busy by several launches at once and what counts is
-    // the share of a CTA's residency spent streaming: slices of at least
-    // 384 KiB measured best (256 x 201088 bf16: 20.6 us with one slice per row, 28.7 us with two).
+    // A row is cut into slices only while all CTAs of the launch stay resident
+    // at once: a single wave has no ragged second wave, and the fixed per-slice
+    // work (threshold estimate, select, publication) stays small next to a
+    // slice of at least 128 KiB.  The ring decouples the bytes on request from
+    // the number of CTAs, so one CTA per row is enough once there are about as
+    // many rows as resident CTAs.
+    (void)overlapped;
     const uint64_t row_bytes = static_cast<uint64_t>(vocab) * (dtype == MOE_DTYPE_F32 ? 4u : 2u);
-    const uint64_t by_size = row_bytes / ((overlapped ? 384u : 64u) * 1024u);
-    const uint64_t resident = static_cast<uint64_t>(sm_count) * (large_top_k ? 4u : static_cast<unsigned>(MOE_RESIDENT));
-    uint32_t splits = 1;
-    while (splits < 8u && static_cast<uint64_t>(rows) * splits * 2u <= resident && splits * 2u <= by_size &&
-           static_cast<uint64_t>(rows) * splits * 2u <= slice_slots)
-        splits *= 2u;
-    return splits;
+    const uint64_t by_size = row_bytes / (128u * 1024u);
+    const uint64_t resident = static_cast<uint64_t>(sm_count) * resident_per_sm(large_top_k, ring_stages(large_top_k));
+    uint64_t splits = rows > 0 ? resident / rows : 1u;
+    splits = splits < by_size ? splits : by_size;
+    splits = splits < 32u ? splits : 32u;
+    if (rows > 0 && splits * rows > slice_slots)
+        splits = slice_slots / rows;
+    return splits < 1u ? 1u : static_cast<uint32_t>(splits);
 }
 
 } // namespace moe

@@ -288,68 +288,102 @@ __device__ __noinline__ void block_sort_descending(uint64_t* records, uint32_t p
     }
 }
 
-// Sorts records[0..n) descending for n <= kThreads (kThreads <= 256... any
-// multiple of 32).  Each warp sorts its 32 records in registers with a shuffle
-// network; a record's final position is its position in its own run plus, for
-// every other run, the number of larger records found by binary search.
+// Position of `mine` among the records of a descending run of 32 (zeros pad
+// the tail): the number of entries larger than it.
+__device__ __forceinline__ uint32_t count_larger_in_run(const uint64_t* run, uint64_t mine)
+{
+    uint32_t lo = 0, hi = 32;
+#pragma unroll
+    for (int step = 0; step < 5; ++step)
+    {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (run[mid] > mine)
+            lo = mid + 1;
+        else
+            hi = mid;
+    }
+    if (lo < 32 && run[lo] > mine)
+        ++lo;
+    return lo;
+}
+
+// Sorts records[0..n) descending for n <= kItems * kThreads (kItems 1 or 2).
+// Each warp sorts runs of 32 records in registers with a shuffle network; a
+// record's final position is its position in its own run plus, for every other
+// run, the number of larger records found by binary search — the searches of
+// the different runs are independent, so they are unrolled side by side.
 // Records are unique and 0 pads the tail, so positions are unique.  Three
 // barriers, no atomics: the cheapest order for the few hundred survivors a
 // slice or a row usually has.  Ends with a barrier.
-template<int kThreads>
-__device__ __noinline__ void block_rank_sort_descending(uint64_t* records, uint32_t n)
+template<int kThreads, int kItems>
+__device__ __forceinline__ void block_rank_sort_items(uint64_t* records, uint32_t n)
 {
+    constexpr uint32_t kRunsPerItem = kThreads / 32;
     const uint32_t tid = threadIdx.x;
     const uint32_t lane = tid & 31u;
     const uint32_t warp = tid >> 5;
     const uint32_t runs = (n + 31u) >> 5;
-    uint64_t mine = (tid < n) ? records[tid] : 0ull;
-    if (warp < runs)
+    uint64_t mine[kItems];
+#pragma unroll
+    for (int j = 0; j < kItems; ++j)
+        mine[j] = (tid + j * kThreads < n) ? records[tid + j * kThreads] : 0ull;
+#pragma unroll
+    for (uint32_t size = 2; size <= 32; size <<= 1)
     {
 #pragma unroll
-        for (uint32_t size = 2; size <= 32; size <<= 1)
+        for (uint32_t stride = size >> 1; stride > 0; stride >>= 1)
         {
+            const bool descending = (lane & size) == 0;
+            const bool lower_lane = (lane & stride) == 0;
+            const bool take_max = (descending == lower_lane);
 #pragma unroll
-            for (uint32_t stride = size >> 1; stride > 0; stride >>= 1)
+            for (int j = 0; j < kItems; ++j)
             {
-                const uint32_t other_lo = __shfl_xor_sync(kFullMask, static_cast<uint32_t>(mine), stride);
-                const uint32_t other_hi = __shfl_xor_sync(kFullMask, static_cast<uint32_t>(mine >> 32), stride);
+                const uint32_t other_lo = __shfl_xor_sync(kFullMask, static_cast<uint32_t>(mine[j]), stride);
+                const uint32_t other_hi = __shfl_xor_sync(kFullMask, static_cast<uint32_t>(mine[j] >> 32), stride);
                 const uint64_t other = (static_cast<uint64_t>(other_hi) << 32) | other_lo;
-                const bool descending = (lane & size) == 0;
-                const bool lower_lane = (lane & stride) == 0;
-                const bool take_max = (descending == lower_lane);
-                mine = ((mine > other) == take_max) ? mine : other;
+                mine[j] = ((mine[j] > other) == take_max) ? mine[j] : other;
             }
         }
-        records[tid] = mine; // run `warp`, descending, zeros last
     }
-    __syncthreads();
-    uint32_t position = lane;
-    if (warp < runs && mine != 0ull)
-    {
-        for (uint32_t w = 0; w < runs; ++w)
-        {
-            if (w == warp)
-                continue;
-            const uint64_t* run = records + w * 32u;
-            uint32_t lo = 0, hi = 32;
 #pragma unroll
-            for (int step = 0; step < 5; ++step)
-            {
-                const uint32_t mid = (lo + hi) >> 1;
-                if (run[mid] > mine)
-                    lo = mid + 1;
-                else
-                    hi = mid;
-            }
-            if (lo < 32 && run[lo] > mine)
-                ++lo;
-            position += lo;
+    for (int j = 0; j < kItems; ++j)
+        if (warp + j * kRunsPerItem < runs)
+            records[tid + j * kThreads] = mine[j]; // run `warp + j * kRunsPerItem`, descending, zeros last
+    __syncthreads();
+    uint32_t position[kItems];
+#pragma unroll
+    for (int j = 0; j < kItems; ++j)
+    {
+        position[j] = lane;
+        const uint32_t own = warp + j * kRunsPerItem;
+        if (mine[j] != 0ull)
+        {
+#pragma unroll
+            for (uint32_t w = 0; w < kItems * kRunsPerItem; ++w)
+                if (w < runs && w != own)
+                    position[j] += count_larger_in_run(records + w * 32u, mine[j]);
         }
     }
     __syncthreads();
-    if (warp < runs && mine != 0ull)
-        records[position] = mine;
+#pragma unroll
+    for (int j = 0; j < kItems; ++j)
+        if (mine[j] != 0ull)
+            records[position[j]] = mine[j];
     __syncthreads();
+}
+
+template<int kThreads>
+__device__ __noinline__ void block_rank_sort_descending(uint64_t* records, uint32_t n)
+{
+    block_rank_sort_items<kThreads, 1>(records, n);
+}
+
+// n <= 2 * kThreads
+template<int kThreads>
+__device__ __noinline__ void block_rank_sort_descending2(uint64_t* records, uint32_t n)
+{
+    block_rank_sort_items<kThreads, 2>(records, n);
 }
 
 __device__ __forceinline__ uint32_t next_pow2(uint32_t v)
