@@ -131,6 +131,73 @@ __device__ __forceinline__ Vec32 load_stream_32(const void* pointer)
     return v;
 }
 
+// ---- shared-memory accesses with the state space spelled out -------------------
+// A pointer into dynamic shared memory that has travelled through a struct or a
+// function argument is a generic pointer to the compiler, and generic loads go
+// down the global-memory path (long-scoreboard latency) before they reach
+// shared memory.  The hot loops therefore address shared memory by its 32-bit
+// window address.
+__device__ __forceinline__ uint32_t shared_address(const void* pointer)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(pointer));
+}
+__device__ __forceinline__ uint4 load_shared_16(uint32_t address)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address));
+    return v;
+}
+__device__ __forceinline__ void store_shared_16(uint32_t address, const uint4& v)
+{
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(address), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ ulonglong2 load_shared_2x64(uint32_t address)
+{
+    ulonglong2 v;
+    asm volatile("ld.shared.v2.u64 {%0,%1}, [%2];" : "=l"(v.x), "=l"(v.y) : "r"(address));
+    return v;
+}
+__device__ __forceinline__ uint64_t load_shared_64(uint32_t address)
+{
+    unsigned long long v;
+    asm volatile("ld.shared.u64 %0, [%1];" : "=l"(v) : "r"(address));
+    return v;
+}
+__device__ __forceinline__ void store_shared_64(uint32_t address, uint64_t v)
+{
+    asm volatile("st.shared.u64 [%0], %1;" ::"r"(address), "l"(static_cast<unsigned long long>(v)) : "memory");
+}
+__device__ __forceinline__ uint32_t load_shared_32(uint32_t address)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(address));
+    return v;
+}
+__device__ __forceinline__ uint32_t load_shared_32_volatile(uint32_t address)
+{
+    uint32_t v;
+    asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(address) : "memory");
+    return v;
+}
+__device__ __forceinline__ void store_shared_32(uint32_t address, uint32_t v)
+{
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(address), "r"(v) : "memory");
+}
+__device__ __forceinline__ float load_shared_f32(uint32_t address)
+{
+    return __uint_as_float(load_shared_32(address));
+}
+__device__ __forceinline__ uint32_t atomic_add_shared(uint32_t address, uint32_t value)
+{
+    uint32_t old;
+    asm volatile("atom.shared.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(address), "r"(value) : "memory");
+    return old;
+}
+__device__ __forceinline__ void atomic_max_shared(uint32_t address, uint32_t value)
+{
+    asm volatile("red.shared.max.u32 [%0], %1;" ::"r"(address), "r"(value) : "memory");
+}
+
 template<typename T>
 struct LogitTraits;
 

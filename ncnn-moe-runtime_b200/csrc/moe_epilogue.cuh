@@ -4,10 +4,10 @@
 // step: every sum is a left-to-right fp32 accumulation in rank order, because
 // the reference's results (the Top-P cut in particular) depend on that order.
 // The expensive per-candidate work (exp, divisions) is done one candidate per
-// lane into a scratch array; the running sums are then replayed by every lane
-// redundantly over that array (broadcast loads, unrolled so that only the
-// dependent adds are on the critical path), so all 32 lanes hold the same
-// accumulator and take the same branches.
+// lane into a scratch array; the running sums are then replayed in order by the
+// whole warp (addends broadcast by shuffle, so that only the dependent adds are
+// on the critical path), every lane holding the same accumulator, and the
+// places where a sum crosses a bound are found with a vote.
 #pragma once
 
 #include "moe_common.cuh"
@@ -48,12 +48,75 @@ __device__ __forceinline__ KeptList kept_list_of_row(int32_t* token, float* prob
     return list;
 }
 
+// Left-to-right fp32 accumulation of x[0..n) (shared memory) from zero by one warp, 32
+// addends per round: every lane fetches one addend, the dependent adds walk
+// the lanes in order (the shuffles do not depend on the accumulator, so only
+// the adds are on the critical path) and each lane keeps the accumulator as it
+// stood right after its own addend.  All lanes hold the same accumulator.
+enum SeqStopKind : int
+{
+    kSeqWarpAll = 0,    // add everything
+    kSeqWarpReach = 1,  // stop behind the first addend after which acc >= bound
+    kSeqWarpExceed = 2  // stop behind the first addend after which bound < acc
+};
+
+struct SeqWarpResult
+{
+    float acc;      // accumulator after the stopping addend, or after all n
+    uint32_t index; // position of the stopping addend, n when none stopped
+};
+
+template<int kKind>
+__device__ __forceinline__ SeqWarpResult warp_sequential_sum(const float* x, uint32_t n, float bound)
+{
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t addends = shared_address(x);
+    float acc = 0.0f;
+    for (uint32_t base = 0; base < n; base += 32)
+    {
+        const uint32_t i = base + lane;
+        const float mine = (i < n) ? load_shared_f32(addends + 4u * i) : 0.0f;
+        float after = 0.0f; // accumulator right after this lane's addend
+        if (n - base >= 32u)
+        {
+#pragma unroll
+            for (uint32_t j = 0; j < 32; ++j)
+            {
+                acc = __fadd_rn(acc, __shfl_sync(kFullMask, mine, j));
+                after = (lane == j) ? acc : after;
+            }
+        }
+        else
+        {
+            const uint32_t steps = n - base;
+            for (uint32_t j = 0; j < steps; ++j)
+            {
+                acc = __fadd_rn(acc, __shfl_sync(kFullMask, mine, j));
+                after = (lane == j) ? acc : after;
+            }
+        }
+        if (kKind != kSeqWarpAll)
+        {
+            const bool stop = (i < n) && (kKind == kSeqWarpReach ? (after >= bound) : (bound < after));
+            const unsigned stoppers = __ballot_sync(kFullMask, stop);
+            if (stoppers != 0u)
+            {
+                const int first = __ffs(stoppers) - 1;
+                return SeqWarpResult{__shfl_sync(kFullMask, after, first), base + static_cast<uint32_t>(first)};
+            }
+        }
+    }
+    return SeqWarpResult{acc, n};
+}
+
 // records[0..count): sorted descending.  work[0..count): scratch floats.
 // tail_may_exist: the list is only the numerically live prefix of the row's
 // candidates (every omitted candidate has exp(x - peak) < 2^-26, so it cannot
 // change any of the four running sums, but it could still be the fall-back
 // "last candidate" of session.cpp:441-442).
-__device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, uint32_t count, float* work, float temperature,
+// numerators_ready: work[i] already holds exp(logit_i / T - peak) for every
+// finite candidate the Top-K truncation leaves (computed by the whole block).
+__device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, uint32_t count, float* work, bool numerators_ready, float temperature,
                                                        uint32_t top_k, float top_p, float min_p, float uniform, bool tail_may_exist,
                                                        const KeptList& kept_list)
 {
@@ -89,49 +152,53 @@ __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, u
     }
 
     // softmax numerators and their sequential sum (session.cpp:89-101)
-    const float peak = __fdiv_rn(key_to_float(head_key), temperature);
-    for (uint32_t i = lane; i < finite; i += 32)
-        work[i] = exact_expf(scaled_offset(key_to_float(record_key(records[i])), temperature, peak));
+    if (!numerators_ready)
+    {
+        const float peak = __fdiv_rn(key_to_float(head_key), temperature);
+        for (uint32_t i = lane; i < finite; i += 32)
+            work[i] = exact_expf(scaled_offset(key_to_float(record_key(records[i])), temperature, peak));
+    }
     __syncwarp();
-    float total = 0.0f;
-#pragma unroll 8
-    for (uint32_t i = 0; i < finite; ++i)
-        total = __fadd_rn(total, work[i]);
+    const float total = warp_sequential_sum<kSeqWarpAll>(work, finite, 0.0f).acc;
     if (finite == 0 || !(total - total == 0.0f) || total <= 0.0f)
     {
         out.status = MOE_ROW_INVALID_DISTRIBUTION; // session.cpp:102-103
         return out;
     }
 
-    // probabilities, Min-P floor, Top-P prefix (session.cpp:104-128)
+    // probabilities, Min-P floor, Top-P prefix (session.cpp:104-128).  The
+    // reference walks the candidates once, leaving at the first one below the
+    // Min-P floor or right behind the one whose running sum reaches top_p.
+    // Probabilities do not increase along the list, so the candidates that pass
+    // the floor are a prefix: find its length with votes, then run the
+    // sequential sum over that prefix only.
     __syncwarp();
     for (uint32_t i = lane; i < finite; i += 32)
         work[i] = __fdiv_rn(work[i], total);
     __syncwarp();
-    const float floor_probability = __fmul_rn(work[0], min_p);
-    float running = 0.0f;
-    uint32_t kept = 0;
-    bool cut = false; // Min-P or Top-P closed the list: no omitted candidate can follow it
-#pragma unroll 4
-    for (uint32_t i = 0; i < finite; ++i)
+    uint32_t allowed = finite;
+    if (min_p > 0.0f)
     {
-        const float probability = work[i];
-        if (min_p > 0.0f && !(probability >= floor_probability))
+        const float floor_probability = __fmul_rn(work[0], min_p);
+        for (uint32_t base = 0; base < finite; base += 32)
         {
-            cut = true; // probabilities are non-increasing: nothing after this passes either
-            break;
-        }
-        running = __fadd_rn(running, probability);
-        ++kept;
-        if (running >= top_p)
-        {
-            cut = true;
-            break;
+            const uint32_t i = base + lane;
+            const bool below = (i < finite) && !(work[i] >= floor_probability);
+            const unsigned voters = __ballot_sync(kFullMask, below);
+            if (voters != 0u)
+            {
+                allowed = base + static_cast<uint32_t>(__ffs(voters) - 1);
+                break;
+            }
         }
     }
+    const SeqWarpResult nucleus = warp_sequential_sum<kSeqWarpReach>(work, allowed, top_p);
+    const uint32_t kept = nucleus.index < allowed ? nucleus.index + 1u : allowed;
+    // Min-P or Top-P closed the list: no omitted candidate can follow it
+    const bool cut = nucleus.index < allowed || allowed < finite;
 
     // renormaliser (session.cpp:130-134): the same adds over the same prefix from the same zero as the loop above
-    const float kept_total = running;
+    const float kept_total = nucleus.acc;
 
     if (kept_list.count != nullptr && !list_is_complete && !cut)
     {
@@ -174,18 +241,12 @@ __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, u
                 kept_list.probability[i] = work[i];
         }
     }
-    running = 0.0f;
-#pragma unroll 4
-    for (uint32_t i = 0; i < kept; ++i)
+    const SeqWarpResult draw = warp_sequential_sum<kSeqWarpExceed>(work, kept, uniform);
+    if (draw.index < kept)
     {
-        const float q = work[i];
-        running = __fadd_rn(running, q);
-        if (uniform < running)
-        {
-            out.token = static_cast<int32_t>(record_index(records[i]));
-            out.probability = q;
-            return out;
-        }
+        out.token = static_cast<int32_t>(record_index(records[draw.index]));
+        out.probability = work[draw.index];
+        return out;
     }
     if (!list_is_complete && !cut)
     {

@@ -87,6 +87,13 @@ __device__ __forceinline__ unsigned long long moe_globaltimer()
 #define MOE_PHASE_BEGIN() do {} while (0)
 #endif
 #ifdef MOE_PHASE_TIMERS
+#define MOE_SUB_BEGIN() long long moe_sub_start = clock64()
+#define MOE_SUB(slot) do { if (threadIdx.x == 0) { const long long moe_sub_now = clock64(); atomicAdd(&g_phase_cycles[slot], static_cast<unsigned long long>(moe_sub_now - moe_sub_start)); moe_sub_start = moe_sub_now; } } while (0)
+#else
+#define MOE_SUB_BEGIN() do {} while (0)
+#define MOE_SUB(slot) do {} while (0)
+#endif
+#ifdef MOE_PHASE_TIMERS
 // per-warp stopwatches inside the streaming loop (lane 0 adds them up at the end)
 #define MOE_LAP_DECLARE() long long moe_lap_start = clock64(); long long moe_lap[4] = {0, 0, 0, 0}
 #define MOE_LAP(slot) do { const long long moe_lap_now = clock64(); moe_lap[slot] += moe_lap_now - moe_lap_start; moe_lap_start = moe_lap_now; } while (0)
@@ -120,6 +127,14 @@ constexpr int kCapLarge = 4096;           // ... and batches with top_k up to MO
 constexpr int kItems = kCapLarge / kThreads; // most records per thread in block-wide passes
 constexpr int kMaxStages = 8;             // ring slots per warp, at most
 constexpr uint32_t kHitQueue = 64;        // queued hit vectors per warp (a vote adds at most 32)
+// A Top-K slice lets about 200 logits through its sampled threshold, spread
+// like a Gamma variate, and ordering more than kThreads survivors costs two
+// sorts instead of one.  When the buffer holds kTightenAt records, the k-th
+// best of them is a lower bound of the slice's k-th best: raising the
+// threshold to it leaves only a handful of later arrivals.
+constexpr uint32_t kTightenAt = 176;
+constexpr uint32_t kTightenWindow = 256;  // records looked at (zeroed at kernel start, so an unwritten slot reads as absent)
+constexpr uint32_t kTightenTopKMax = 128;
 constexpr int kGroupsPerTile = 2;         // careful loop: 128-bit loads in flight per thread
 // live mode: the buffer is re-tested against the running maximum at half fill;
 // more survivors than live_abort(cap) send the row to the exact kernel
@@ -155,6 +170,11 @@ struct __align__(16) RowShared
     uint4 hit_vector[kWarps][kHitQueue];
     uint32_t hit_index[kWarps][kHitQueue];
     uint32_t hit_count[kWarps];
+    float uniform; // the row's Philox uniform, computed off the critical path
+    // Top-K streams: once enough records are in the buffer, one warp finds their
+    // k-th best key and every warp raises its threshold to it
+    uint32_t tighten_claimed;
+    uint32_t tighten_key;
 };
 
 struct Ctx
@@ -485,13 +505,13 @@ __device__ __forceinline__ void offer_values(RowShared& s, uint64_t* rec, uint32
         if (pass)
         {
             const uint32_t key = ordered_key(v);
-            const uint32_t slot = atomicAdd(&s.count, 1u);
+            const uint32_t slot = atomic_add_shared(shared_address(&s.count), 1u);
             if (slot < cap)
-                rec[slot] = make_record(key, first_index + e);
+                store_shared_64(shared_address(rec + slot), make_record(key, first_index + e));
             else
-                s.overflow = 1u;
+                store_shared_32(shared_address(&s.overflow), 1u);
             if (mode == kLive)
-                atomicMax(&s.maxkey, key);
+                atomic_max_shared(shared_address(&s.maxkey), key);
         }
     }
 }
@@ -513,23 +533,19 @@ constexpr uint32_t kChunkVectors = 32u * kVectorsPerLane;    // 16-byte vectors 
 constexpr uint32_t kChunkBytes = kChunkVectors * 16u;
 constexpr uint32_t kSpinLimit = 1u << 20;                    // polls of one slot before the stream gives up on the ring
 
-__device__ __forceinline__ uint32_t shared_address(const void* pointer)
+// barriers and ring slots are named by their shared-window addresses
+__device__ __forceinline__ void barrier_init(uint32_t barrier, uint32_t arrivals)
 {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(pointer));
-}
-
-__device__ __forceinline__ void barrier_init(uint64_t* barrier, uint32_t arrivals)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(shared_address(barrier)), "r"(arrivals) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(barrier), "r"(arrivals) : "memory");
 }
 
 // one arrival that also announces `bytes` of copy traffic for the current phase
-__device__ __forceinline__ void barrier_expect_bytes(uint64_t* barrier, uint32_t bytes)
+__device__ __forceinline__ void barrier_expect_bytes(uint32_t barrier, uint32_t bytes)
 {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(shared_address(barrier)), "r"(bytes) : "memory");
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(barrier), "r"(bytes) : "memory");
 }
 
-__device__ __forceinline__ bool barrier_test(uint64_t* barrier, uint32_t parity)
+__device__ __forceinline__ bool barrier_test(uint32_t barrier, uint32_t parity)
 {
     uint32_t done;
     asm volatile(
@@ -539,13 +555,13 @@ __device__ __forceinline__ bool barrier_test(uint64_t* barrier, uint32_t parity)
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(done)
-        : "r"(shared_address(barrier)), "r"(parity)
+        : "r"(barrier), "r"(parity)
         : "memory");
     return done != 0;
 }
 
 // Bounded: a slot that never completes makes the caller fall back to plain loads.
-__device__ __forceinline__ bool barrier_wait(uint64_t* barrier, uint32_t parity)
+__device__ __forceinline__ bool barrier_wait(uint32_t barrier, uint32_t parity)
 {
     for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
         if (barrier_test(barrier, parity))
@@ -561,19 +577,18 @@ __device__ __forceinline__ uint64_t evict_first_policy()
 }
 
 // `bytes` (a multiple of 16) from 16-byte aligned global memory into this CTA's shared memory
-__device__ __forceinline__ void bulk_copy_to_shared(void* destination, const void* source, uint32_t bytes, uint64_t* barrier, uint64_t policy)
+__device__ __forceinline__ void bulk_copy_to_shared(uint32_t destination, const void* source, uint32_t bytes, uint32_t barrier, uint64_t policy)
 {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
-                     shared_address(destination)),
-                 "l"(__cvta_generic_to_global(source)), "r"(bytes), "r"(shared_address(barrier)), "l"(policy)
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(destination),
+                 "l"(__cvta_generic_to_global(source)), "r"(bytes), "r"(barrier), "l"(policy)
                  : "memory");
 }
 
 // A warp's view of its ring.  All fields are warp-uniform.
 struct Ring
 {
-    unsigned char* data;   // stages * kChunkBytes
-    uint64_t* full;        // one barrier per slot
+    uint32_t data;         // shared-window address of this warp's slots: stages * kChunkBytes
+    uint32_t full;         // ... and of its barriers, one per slot
     uint32_t stages;
     uint32_t issue_slot;   // slot the next request goes to
     uint32_t wait_slot;    // slot of the oldest outstanding request
@@ -585,7 +600,7 @@ struct Ring
 // lane 0 only; the other lanes call ring_count_request to keep their cursors equal
 __device__ __forceinline__ void ring_issue(const Ring& ring, const void* source, uint32_t bytes)
 {
-    uint64_t* barrier = ring.full + ring.issue_slot;
+    const uint32_t barrier = ring.full + 8u * ring.issue_slot;
     barrier_expect_bytes(barrier, bytes);
     bulk_copy_to_shared(ring.data + ring.issue_slot * kChunkBytes, source, bytes, barrier, ring.policy);
 }
@@ -597,7 +612,7 @@ __device__ __forceinline__ void ring_count_request(Ring& ring)
 // whole warps only; the answer is the same for every lane
 __device__ __forceinline__ bool ring_acquire(const Ring& ring)
 {
-    return __all_sync(kFullMask, barrier_wait(ring.full + ring.wait_slot, ring.wait_parity)) != 0;
+    return __all_sync(kFullMask, barrier_wait(ring.full + 8u * ring.wait_slot, ring.wait_parity)) != 0;
 }
 // the q-th outstanding request (q < stages), without consuming anything
 __device__ __forceinline__ bool ring_acquire_ahead(const Ring& ring, uint32_t q)
@@ -609,18 +624,19 @@ __device__ __forceinline__ bool ring_acquire_ahead(const Ring& ring, uint32_t q)
         slot -= ring.stages;
         parity ^= 1u;
     }
-    return __all_sync(kFullMask, barrier_wait(ring.full + slot, parity)) != 0;
+    return __all_sync(kFullMask, barrier_wait(ring.full + 8u * slot, parity)) != 0;
 }
-__device__ __forceinline__ const uint4* ring_ahead(const Ring& ring, uint32_t q)
+// shared-window address of the q-th outstanding chunk / of the oldest one
+__device__ __forceinline__ uint32_t ring_ahead(const Ring& ring, uint32_t q)
 {
     uint32_t slot = ring.wait_slot + q;
     if (slot >= ring.stages)
         slot -= ring.stages;
-    return reinterpret_cast<const uint4*>(ring.data + slot * kChunkBytes);
+    return ring.data + slot * kChunkBytes;
 }
-__device__ __forceinline__ const uint4* ring_front(const Ring& ring)
+__device__ __forceinline__ uint32_t ring_front(const Ring& ring)
 {
-    return reinterpret_cast<const uint4*>(ring.data + ring.wait_slot * kChunkBytes);
+    return ring.data + ring.wait_slot * kChunkBytes;
 }
 __device__ __forceinline__ void ring_release(Ring& ring)
 {
@@ -657,14 +673,47 @@ __device__ __forceinline__ void drain_hit_queue(RowShared& s, uint64_t* rec, uin
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warp = threadIdx.x >> 5;
     __syncwarp();
+    const uint32_t vectors = shared_address(&s.hit_vector[warp][0]);
+    const uint32_t indices = shared_address(&s.hit_index[warp][0]);
     for (uint32_t i = lane; i < queued; i += 32)
     {
         float x[U::kWidth];
-        U::values(s.hit_vector[warp][i], x);
-        offer_values<U::kWidth>(s, rec, cap, mode, tau, x, s.hit_index[warp][i]);
+        U::values(load_shared_16(vectors + 16u * i), x);
+        offer_values<U::kWidth>(s, rec, cap, mode, tau, x, load_shared_32(indices + 4u * i));
     }
     __syncwarp();
 }
+
+// The chunks one warp streams: chunk_begin + warp, + kWarps, ... of the row body.
+struct SliceFeed
+{
+    const unsigned char* body; // first 16-byte vector of the row body
+    uint32_t vectors;          // 16-byte vectors in the row body
+    uint32_t chunk_begin;      // the slice: [chunk_begin, chunk_end)
+    uint32_t chunk_end;
+    uint32_t my_chunks;        // chunks of the slice that are this warp's
+
+    __device__ __forceinline__ uint32_t chunk_of(uint32_t i) const
+    {
+        return chunk_begin + (threadIdx.x >> 5) + kWarps * i;
+    }
+    // asks for this warp's i-th chunk (whole warps call it; lane 0 issues)
+    __device__ __forceinline__ void request(Ring& ring, uint32_t i) const
+    {
+        const uint32_t chunk = chunk_of(i);
+        const uint32_t count = min(kChunkVectors, vectors - chunk * kChunkVectors);
+        if ((threadIdx.x & 31u) == 0u)
+            ring_issue(ring, body + static_cast<size_t>(chunk) * kChunkBytes, count * 16u);
+        ring_count_request(ring);
+    }
+    // fills the ring before anything else is known about the row
+    __device__ __forceinline__ void prefetch(Ring& ring) const
+    {
+        const uint32_t ahead = min(ring.stages, my_chunks);
+        for (uint32_t i = 0; i < ahead; ++i)
+            request(ring, i);
+    }
+};
 
 enum StreamResult : int
 {
@@ -672,6 +721,34 @@ enum StreamResult : int
     kStreamDone = 1,    // every logit >= threshold is in the buffer and there are enough of them
     kStreamTooLarge = 2 // live row whose live set cannot fit on chip: the exact kernel takes the row
 };
+
+// One warp: the largest key K such that at least k of records[0..m) (m <=
+// kTightenWindow) have a key >= K, by binary search over the 32 key bits; 0 when
+// fewer than k records are present.  Slots still being written read as 0.
+__device__ __forceinline__ uint32_t warp_kth_key(const uint64_t* rec, uint32_t m, uint32_t k)
+{
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t base = shared_address(rec);
+    uint32_t keys[kTightenWindow / 32];
+#pragma unroll
+    for (uint32_t j = 0; j < kTightenWindow / 32; ++j)
+    {
+        const uint32_t i = lane + 32u * j;
+        keys[j] = i < m ? static_cast<uint32_t>(load_shared_64(base + 8u * i) >> 32) : 0u;
+    }
+    uint32_t result = 0;
+    for (int bit = 31; bit >= 0; --bit)
+    {
+        const uint32_t candidate = result | (1u << bit);
+        uint32_t reached = 0;
+#pragma unroll
+        for (uint32_t j = 0; j < kTightenWindow / 32; ++j)
+            reached += keys[j] >= candidate ? 1u : 0u;
+        if (__reduce_add_sync(kFullMask, reached) >= k)
+            result = candidate;
+    }
+    return result;
+}
 
 // Rank (1 = largest) of the thread maximum of the sample that becomes the
 // threshold of a Top-K slice.  The sample holds `sample_elements` of the
@@ -698,14 +775,18 @@ __device__ __forceinline__ uint32_t threshold_rank(uint32_t k, float slice_eleme
 // All logits >= threshold end up in the buffer, so if at least k were found the
 // slice's k best are among them regardless of the order of the logits.
 template<typename T>
-__device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, uint64_t* rec, uint32_t cap, Mode mode, uint32_t k, float temperature,
-                                                 const T* row_pointer, uint32_t vocab, uint32_t head, uint32_t vectors, uint32_t tail_begin,
-                                                 uint32_t chunk_begin, uint32_t chunk_end, bool first_rank, bool last_rank)
+__device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, const SliceFeed& feed, uint64_t* rec, uint32_t cap, Mode mode, uint32_t k,
+                                                 float temperature, const T* row_pointer, uint32_t vocab, uint32_t head, uint32_t tail_begin,
+                                                 bool first_rank, bool last_rank)
 {
     using U = Unpack<T>;
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
+    const uint32_t vectors = feed.vectors;
+    const uint32_t chunk_begin = feed.chunk_begin;
+    const uint32_t chunk_end = feed.chunk_end;
+    const uint32_t my_chunks = feed.my_chunks;
     // the sample: the chunks every warp has on request when the stream starts, all of them complete
     const uint32_t rounds_available = (chunk_end - chunk_begin) / kWarps;
     const uint32_t complete_chunks = vectors / kChunkVectors;
@@ -713,7 +794,10 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, uint6
     if (chunk_begin + kWarps * sample_rounds > complete_chunks)
         sample_rounds = (complete_chunks > chunk_begin) ? (complete_chunks - chunk_begin) / kWarps : 0u;
     if (sample_rounds == 0u)
+    {
+        ring_drain(ring);
         return kStreamCareful;
+    }
 
     // rank r of the thread maximum that becomes the threshold
     uint32_t r = 1;
@@ -723,32 +807,29 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, uint6
         const float sample_elements = static_cast<float>(sample_rounds) * (kWarps * kChunkVectors * U::kWidth);
         r = threshold_rank(k, slice_elements, sample_elements);
         if (r > (3u * kThreads) / 4u)
+        {
+            ring_drain(ring);
             return kStreamCareful; // the threshold would pass nearly everything
+        }
     }
-
-    const unsigned char* body = reinterpret_cast<const unsigned char*>(row_pointer + head);
-    // this warp's chunks: chunk_begin + warp, + kWarps, ...
-    const uint32_t my_chunks = (chunk_end - chunk_begin - static_cast<uint32_t>(warp) + kWarps - 1u) / kWarps;
-    const auto request = [&](uint32_t i) {
-        const uint32_t chunk = chunk_begin + static_cast<uint32_t>(warp) + kWarps * i;
-        const uint32_t first_vector = chunk * kChunkVectors;
-        const uint32_t count = min(kChunkVectors, vectors - first_vector);
-        if (lane == 0)
-            ring_issue(ring, body + static_cast<size_t>(chunk) * kChunkBytes, count * 16u);
-        ring_count_request(ring);
-    };
 
     MOE_LAP_DECLARE();
     uint32_t* lists = s.sel.hist; // kThreads entries, untouched while streaming
-    uint32_t* const hit_count = &s.hit_count[warp];
+    const uint32_t hit_count = shared_address(&s.hit_count[warp]);
+    const uint32_t hit_vectors = shared_address(&s.hit_vector[warp][0]);
+    const uint32_t hit_indices = shared_address(&s.hit_index[warp][0]);
+    const uint32_t overflow_flag = shared_address(&s.overflow);
+    const uint32_t maximum_key = shared_address(&s.maxkey);
+    const uint32_t record_count = shared_address(&s.count);
+    const uint32_t tighten_claimed = shared_address(&s.tighten_claimed);
+    const uint32_t tighten_key = shared_address(&s.tighten_key);
     uint32_t sorted_key = 0;
     uint32_t live_maximum = 0; // live mode, second attempt: the slice maximum found by the first
     bool fault = false;
     for (int attempt = 0;; ++attempt)
     {
-        const uint32_t ahead = min(ring.stages, my_chunks);
-        for (uint32_t i = 0; i < ahead; ++i)
-            request(i);
+        if (ring.outstanding == 0u)
+            feed.prefetch(ring); // the first attempt finds the ring filled by the kernel's first instructions
 
         if (attempt == 0)
         {
@@ -763,10 +844,10 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, uint6
                     fault = true;
                     break;
                 }
-                const uint4* sample = ring_ahead(ring, q);
+                const uint32_t sample = ring_ahead(ring, q) + 16u * lane;
 #pragma unroll
                 for (int j = 0; j < kVectorsPerLane; ++j)
-                    top = fmaxf(top, U::maximum(sample[j * 32 + lane]));
+                    top = fmaxf(top, U::maximum(load_shared_16(sample + 512u * j)));
             }
             sorted_key = (top == top) ? ordered_key(top) : 0u; // descending by lane after the network
 #pragma unroll
@@ -788,7 +869,7 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, uint6
         if (tid == 0)
             s.sel.bucket = 0;
         if (lane == 0)
-            *hit_count = 0;
+            store_shared_32(hit_count, 0u);
         __syncthreads();
         if (static_cast<uint32_t>(lane) < r)
         {
@@ -856,6 +937,8 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, uint6
         uint32_t seen_max = threshold_key; // live mode: the largest key this warp knows of
         // live mode, first attempt, buffer already overflowed: only the maximum is still of interest
         bool maximum_only = false;
+        // only the first attempt finds the record buffer zeroed beyond what has been written
+        const bool tightening = mode == kTopK && attempt == 0 && k <= kTightenTopKMax;
         for (uint32_t i = 0; usable && !fault && i < my_chunks; ++i)
         {
             if (!ring_acquire(ring))
@@ -864,12 +947,18 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, uint6
                 break;
             }
             MOE_LAP(1); // waiting for the copy engine
-            const uint4* front = ring_front(ring);
+            if (tightening)
+            {
+                const uint32_t tighter = load_shared_32_volatile(tighten_key);
+                if (tighter != 0u)
+                    tau = fmaxf(tau, key_to_float(tighter));
+            }
+            const uint32_t front = ring_front(ring) + 16u * lane;
             uint4 v[kVectorsPerLane];
 #pragma unroll
             for (int j = 0; j < kVectorsPerLane; ++j)
-                v[j] = front[j * 32 + lane];
-            const uint32_t first_vector = (chunk_begin + static_cast<uint32_t>(warp) + kWarps * i) * kChunkVectors;
+                v[j] = load_shared_16(front + 512u * j);
+            const uint32_t first_vector = feed.chunk_of(i) * kChunkVectors;
             if (first_vector + kChunkVectors > vectors)
             {
                 // the ragged last chunk of the row: slots beyond it hold stale bytes
@@ -891,14 +980,14 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, uint6
             const unsigned voters = __ballot_sync(kFullMask, hit);
             ring_release(ring);
             if (i + ring.stages < my_chunks)
-                request(i + ring.stages);
+                feed.request(ring, i + ring.stages);
             MOE_LAP(2); // filter + refill request
             if (voters != 0)
             {
                 if (maximum_only)
                 {
                     if (hit && ordered_key(best) > seen_max)
-                        atomicMax(&s.maxkey, ordered_key(best));
+                        atomic_max_shared(maximum_key, ordered_key(best));
                 }
                 else
                 {
@@ -911,11 +1000,11 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, uint6
                             if (!(top[j] >= tau))
                                 continue;
                             const uint32_t first_index = head + (first_vector + j * 32 + lane) * U::kWidth;
-                            const uint32_t slot = atomicAdd(hit_count, 1u);
+                            const uint32_t slot = atomic_add_shared(hit_count, 1u);
                             if (slot < kHitQueue)
                             {
-                                s.hit_vector[warp][slot] = v[j];
-                                s.hit_index[warp][slot] = first_index;
+                                store_shared_16(hit_vectors + 16u * slot, v[j]);
+                                store_shared_32(hit_indices + 4u * slot, first_index);
                             }
                             else
                             {
@@ -925,20 +1014,38 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, uint6
                                 offer_values<U::kWidth>(s, rec, cap, mode, tau, x, first_index);
                             }
                             if (mode == kLive && ordered_key(top[j]) > seen_max)
-                                atomicMax(&s.maxkey, ordered_key(top[j]));
+                                atomic_max_shared(maximum_key, ordered_key(top[j]));
                         }
                     }
                     __syncwarp();
-                    const uint32_t queued = min(*reinterpret_cast<volatile uint32_t*>(hit_count), kHitQueue);
+                    const uint32_t queued = min(load_shared_32_volatile(hit_count), kHitQueue);
                     if (queued >= kHitQueue / 2u)
                     {
                         if (mode == kLive)
-                            tau = fmaxf(tau, live_threshold(*reinterpret_cast<volatile uint32_t*>(&s.maxkey), temperature));
+                            tau = fmaxf(tau, live_threshold(load_shared_32_volatile(maximum_key), temperature));
                         drain_hit_queue<T>(s, rec, cap, mode, tau, queued);
                         if (lane == 0)
-                            *hit_count = 0;
+                            store_shared_32(hit_count, 0u);
                         __syncwarp();
-                        if (*reinterpret_cast<volatile uint32_t*>(&s.overflow) != 0u)
+                        if (tightening)
+                        {
+                            // the first warp to see kTightenAt records in the buffer raises everybody's threshold
+                            uint32_t present = 0;
+                            if (lane == 0)
+                            {
+                                present = load_shared_32_volatile(record_count);
+                                if (present < kTightenAt || atomic_add_shared(tighten_claimed, 1u) != 0u)
+                                    present = 0;
+                            }
+                            present = __shfl_sync(kFullMask, present, 0);
+                            if (present != 0u)
+                            {
+                                const uint32_t kth = warp_kth_key(rec, min(present, kTightenWindow), k);
+                                if (kth > kKeyNegInf && lane == 0)
+                                    store_shared_32(tighten_key, kth);
+                            }
+                        }
+                        if (load_shared_32_volatile(overflow_flag) != 0u)
                         {
                             if (mode == kLive && live_maximum == 0u)
                                 maximum_only = true; // keep looking for the row's maximum
@@ -950,15 +1057,21 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, uint6
             }
             if (mode == kLive)
             {
-                seen_max = *reinterpret_cast<volatile uint32_t*>(&s.maxkey);
+                seen_max = load_shared_32_volatile(maximum_key);
                 tau = fmaxf(tau, live_threshold(seen_max, temperature));
             }
             MOE_LAP(3); // hits
         }
         if (mode == kLive)
-            tau = fmaxf(tau, live_threshold(*reinterpret_cast<volatile uint32_t*>(&s.maxkey), temperature));
+            tau = fmaxf(tau, live_threshold(load_shared_32_volatile(maximum_key), temperature));
+        if (tightening)
+        {
+            const uint32_t tighter = load_shared_32_volatile(tighten_key);
+            if (tighter != 0u)
+                tau = fmaxf(tau, key_to_float(tighter));
+        }
         __syncwarp();
-        drain_hit_queue<T>(s, rec, cap, mode, tau, min(*reinterpret_cast<volatile uint32_t*>(hit_count), kHitQueue));
+        drain_hit_queue<T>(s, rec, cap, mode, tau, min(load_shared_32_volatile(hit_count), kHitQueue));
         MOE_LAP(3);
         MOE_LAP_FLUSH();
         if (!ring_drain(ring))
@@ -1057,10 +1170,43 @@ __device__ __forceinline__ void reduce_buffer(Ctx& c, bool sort)
             __syncthreads();
             kept = s.sel.out_count;
         }
+        MOE_SUB_BEGIN();
         if (n <= kThreads)
+        {
             block_rank_sort_descending<kThreads>(c.rec, n);
+        }
+        else if (c.mode != kLive && c.k <= kThreads / 2u)
+        {
+            // A little over one record per thread: sort the first kThreads, and
+            // let only the spare records that beat their k-th join a second,
+            // much smaller sort of the k best so far.
+            const uint32_t tid = threadIdx.x;
+            const uint64_t spare = kThreads + tid < n ? c.rec[kThreads + tid] : 0ull;
+            if (tid == 0)
+                s.sel.out_count = 0;
+            block_rank_sort_descending<kThreads>(c.rec, kThreads); // ends with a barrier
+            const uint64_t pivot = c.rec[c.k - 1u];
+            const bool joins = spare > pivot;
+            const unsigned voters = __ballot_sync(kFullMask, joins);
+            uint32_t base = 0;
+            if ((tid & 31u) == 0u && voters != 0u)
+                base = atomicAdd(&s.sel.out_count, static_cast<uint32_t>(__popc(voters)));
+            base = __shfl_sync(kFullMask, base, 0);
+            __syncthreads(); // every thread has read the pivot
+            if (joins)
+                c.rec[c.k + base + __popc(voters & ((1u << (tid & 31u)) - 1u))] = spare;
+            __syncthreads();
+            const uint32_t merged = c.k + s.sel.out_count; // at most k + kThreads
+            if (merged <= kThreads)
+                block_rank_sort_descending<kThreads>(c.rec, merged);
+            else
+                block_rank_sort_descending2<kThreads>(c.rec, merged);
+        }
         else
+        {
             block_rank_sort_descending2<kThreads>(c.rec, n);
+        }
+        MOE_SUB(3);
         if (c.mode != kLive)
             kept = min(n, c.k);
         if (kept != n)
@@ -1130,12 +1276,40 @@ __device__ __forceinline__ void finish_row_block(const SampleArgs& a, RowShared&
         return;
     }
 
+    MOE_SUB_BEGIN();
     if (a.topk_index != nullptr)
     {
         const uint32_t listed = (c.mode == kTopK) ? min(n, c.k) : 0u;
         for (uint32_t i = tid; i < a.topk_stride; i += kThreads)
             a.topk_index[static_cast<size_t>(row) * a.topk_stride + i] = (i < listed) ? static_cast<int32_t>(record_index(c.rec[i])) : -1;
     }
+    MOE_SUB(4);
+
+    // The expensive, order-independent part of the epilogue runs on all warps:
+    // one softmax numerator per thread (session.cpp:94-100; a double-precision
+    // exp each), and the row's uniform on a warp of its own.  What is left for
+    // the first warp are the sums that have to be replayed in rank order.
+    bool numerators_ready = false;
+    if (c.mode != kGreedy && n > 0)
+    {
+        const uint32_t head_key = record_key(c.rec[0]);
+        if (head_key < kKeyPosInf && head_key > kKeyNegInf)
+        {
+            const uint32_t considered = (p.top_k > 0 && p.top_k <= n) ? p.top_k : n;
+            const float peak = __fdiv_rn(key_to_float(head_key), p.temperature);
+            for (uint32_t i = tid; i < considered; i += kThreads)
+            {
+                const uint32_t key = record_key(c.rec[i]);
+                if (key > kKeyNegInf)
+                    c.work[i] = exact_expf(scaled_offset(key_to_float(key), p.temperature, peak));
+            }
+            numerators_ready = true;
+        }
+        if (tid == kThreads - 32)
+            s.uniform = philox_uniform(p.seed, p.row_id, p.step + a.step_offset);
+        __syncthreads();
+    }
+    MOE_SUB(5);
 
     if (tid < 32)
     {
@@ -1167,8 +1341,9 @@ __device__ __forceinline__ void finish_row_block(const SampleArgs& a, RowShared&
         }
         else
         {
-            const float uniform = philox_uniform(p.seed, p.row_id, p.step + a.step_offset);
-            out = finish_row_warp(c.rec, n, c.work, p.temperature, p.top_k, p.top_p, p.min_p, uniform, c.mode == kLive, kept_list);
+            const float uniform = n > 0 ? s.uniform : 0.0f;
+            out = finish_row_warp(c.rec, n, c.work, numerators_ready, p.temperature, p.top_k, p.top_p, p.min_p, uniform, c.mode == kLive, kept_list);
+            MOE_SUB(8);
         }
         if (tid == 0)
         {
@@ -1223,6 +1398,49 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(const SampleAr
     if (a.overlap_previous)
         grid_dependency_release();
 
+    // ---- the slice of this CTA, and its first bytes on request at once -----------
+    const T* row_pointer = static_cast<const T*>(a.logits) + static_cast<size_t>(row) * a.row_stride;
+    const uint32_t vocab = a.vocab;
+    // the row body is walked in 16-byte vectors from the first 32-byte boundary;
+    // `groups` of kThreads vectors (or of one ring chunk of every lane's size if
+    // that is more) are dealt to the row's CTAs in contiguous runs
+    const uint32_t misaligned = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(row_pointer) & 31u);
+    uint32_t head = ((32u - misaligned) & 31u) / static_cast<uint32_t>(sizeof(T));
+    head = min(head, vocab);
+    const uint32_t vectors = (vocab - head) / Unpack<T>::kWidth;
+    const uint32_t tail_begin = head + vectors * Unpack<T>::kWidth;
+    constexpr uint32_t kGroupVectors = (kChunkVectors > kThreads) ? kChunkVectors : static_cast<uint32_t>(kThreads);
+    const uint32_t groups = (vectors + kGroupVectors - 1) / kGroupVectors;
+    const uint32_t group_begin = static_cast<uint32_t>(static_cast<uint64_t>(rank) * groups / splits);
+    const uint32_t group_end = static_cast<uint32_t>(static_cast<uint64_t>(rank + 1) * groups / splits);
+    const uint32_t chunks = (vectors + kChunkVectors - 1) / kChunkVectors;
+    SliceFeed feed;
+    feed.body = reinterpret_cast<const unsigned char*>(row_pointer + head);
+    feed.vectors = vectors;
+    feed.chunk_begin = group_begin * (kGroupVectors / kChunkVectors);
+    feed.chunk_end = min(group_end * (kGroupVectors / kChunkVectors), chunks);
+    const uint32_t slice_chunks = feed.chunk_end - feed.chunk_begin;
+    feed.my_chunks = (slice_chunks + kWarps - 1u - static_cast<uint32_t>(tid >> 5)) / kWarps;
+    if (slice_chunks <= static_cast<uint32_t>(tid >> 5))
+        feed.my_chunks = 0;
+
+    Ring ring;
+    ring.data = shared_address(ring_base) + static_cast<uint32_t>(tid >> 5) * stages * kChunkBytes;
+    ring.full = shared_address(&s.ring_full[tid >> 5][0]);
+    ring.stages = stages;
+    ring.issue_slot = ring.wait_slot = ring.wait_parity = ring.outstanding = 0u;
+    ring.policy = evict_first_policy();
+    if ((tid & 31) == 0)
+    {
+        for (uint32_t slot = 0; slot < stages; ++slot)
+            barrier_init(ring.full + 8u * slot, 1u);
+        // make the initialised barriers visible to the copy engine
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncwarp();
+    feed.prefetch(ring); // a warp only ever uses its own barriers: no block barrier needed first
+
     moe_row_params p;
     if (candidates_only)
     {
@@ -1241,6 +1459,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(const SampleAr
     const int invalid = validate_row(p);
     if (invalid != MOE_ROW_OK)
     {
+        ring_drain(ring);
         // every CTA of the row takes this branch, so the arrival counter stays untouched
         if (a.overlap_previous)
             grid_dependency_wait();
@@ -1288,45 +1507,16 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(const SampleAr
         s.maxkey = 0;
         s.abort_flag = 0;
         s.overflow = 0;
+        s.tighten_claimed = 0;
+        s.tighten_key = 0;
     }
-    Ring ring;
-    ring.data = ring_base + static_cast<size_t>(tid >> 5) * stages * kChunkBytes;
-    ring.full = s.ring_full[tid >> 5];
-    ring.stages = stages;
-    ring.issue_slot = ring.wait_slot = ring.wait_parity = ring.outstanding = 0u;
-    ring.policy = evict_first_policy();
-    if ((tid & 31) == 0)
-    {
-        for (uint32_t slot = 0; slot < stages; ++slot)
-            barrier_init(ring.full + slot, 1u);
-        // make the initialised barriers visible to the copy engine
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
+    for (uint32_t i = tid; i < kTightenWindow; i += kThreads)
+        records[i] = 0ull; // an unwritten slot must read as "no record" to the threshold tightening
     __syncthreads();
 
-    // ---- the slice of this CTA -------------------------------------------------
-    const T* row_pointer = static_cast<const T*>(a.logits) + static_cast<size_t>(row) * a.row_stride;
-    const uint32_t vocab = a.vocab;
-    // the row body is walked in 16-byte vectors from the first 32-byte boundary;
-    // `groups` of kThreads vectors (two ring chunks of every warp's size) are
-    // dealt to the row's CTAs in contiguous runs
-    const uint32_t misaligned = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(row_pointer) & 31u);
-    uint32_t head = ((32u - misaligned) & 31u) / static_cast<uint32_t>(sizeof(T));
-    head = min(head, vocab);
-    const uint32_t vectors = (vocab - head) / Unpack<T>::kWidth;
-    const uint32_t tail_begin = head + vectors * Unpack<T>::kWidth;
-    constexpr uint32_t kGroupVectors = (kChunkVectors > kThreads) ? kChunkVectors : static_cast<uint32_t>(kThreads);
-    const uint32_t groups = (vectors + kGroupVectors - 1) / kGroupVectors;
-    const uint32_t group_begin = static_cast<uint32_t>(static_cast<uint64_t>(rank) * groups / splits);
-    const uint32_t group_end = static_cast<uint32_t>(static_cast<uint64_t>(rank + 1) * groups / splits);
-    const uint32_t chunks = (vectors + kChunkVectors - 1) / kChunkVectors;
-    const uint32_t chunk_begin = group_begin * (kGroupVectors / kChunkVectors);
-    const uint32_t chunk_end = min(group_end * (kGroupVectors / kChunkVectors), chunks);
-
     MOE_PHASE_MARK(0);
-    const int streamed = stream_slice_ring<T>(s, ring, c.rec, c.cap, c.mode, c.k, p.temperature, row_pointer, vocab, head, vectors, tail_begin, chunk_begin,
-                                              chunk_end, rank == 0, rank == splits - 1);
+    const int streamed = stream_slice_ring<T>(s, ring, feed, c.rec, c.cap, c.mode, c.k, p.temperature, row_pointer, vocab, head, tail_begin, rank == 0,
+                                              rank == splits - 1);
     MOE_PHASE_MARK(1);
     MOE_TRACE(1);
 #ifdef MOE_PHASE_TIMERS
