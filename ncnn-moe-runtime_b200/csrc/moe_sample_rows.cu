@@ -120,13 +120,19 @@ __device__ __forceinline__ void grid_dependency_release()
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
-constexpr int kThreads = 256;
+#ifndef MOE_ROW_MIN_CTAS
+#define MOE_ROW_MIN_CTAS 2 // CTAs per SM the register allocation leaves room for
+#endif
+#ifndef MOE_ROW_THREADS
+#define MOE_ROW_THREADS 256
+#endif
+constexpr int kThreads = MOE_ROW_THREADS;
 constexpr int kWarps = kThreads / 32;
 constexpr int kCapSmall = 2048;           // records a CTA can hold: batches whose Top-K sizes are small
 constexpr int kCapLarge = 4096;           // ... and batches with top_k up to MOE_SAMPLER_TOPK_FAST_MAX
 constexpr int kItems = kCapLarge / kThreads; // most records per thread in block-wide passes
 constexpr int kMaxStages = 8;             // ring slots per warp, at most
-constexpr uint32_t kHitQueue = 64;        // queued hit vectors per warp (a vote adds at most 32)
+constexpr uint32_t kHitQueue = 64;        // queued hit vectors per warp
 // A Top-K slice lets about 200 logits through its sampled threshold, spread
 // like a Gamma variate, and ordering more than kThreads survivors costs two
 // sorts instead of one.  When the buffer holds kTightenAt records, the k-th
@@ -169,8 +175,8 @@ struct __align__(16) RowShared
     // divergence, unpacked one vector per lane when the queue runs full
     uint4 hit_vector[kWarps][kHitQueue];
     uint32_t hit_index[kWarps][kHitQueue];
-    uint32_t hit_count[kWarps];
     float uniform; // the row's Philox uniform, computed off the critical path
+    uint32_t sample_keys[kThreads]; // per-thread maxima of the threshold sample, one sorted run per warp
     // Top-K streams: once enough records are in the buffer, one warp finds their
     // k-th best key and every warp raises its threshold to it
     uint32_t tighten_claimed;
@@ -230,6 +236,20 @@ struct Unpack<float>
     {
         return fmaxf(fmaxf(__uint_as_float(v.x), __uint_as_float(v.y)), fmaxf(__uint_as_float(v.z), __uint_as_float(v.w)));
     }
+    // maxima are combined in the logits' own format and widened once
+    using Packed = float;
+    __device__ static __forceinline__ Packed packed_maximum(const uint4& v)
+    {
+        return maximum(v);
+    }
+    __device__ static __forceinline__ Packed combine(Packed a, Packed b)
+    {
+        return fmaxf(a, b);
+    }
+    __device__ static __forceinline__ float widen(Packed p)
+    {
+        return p;
+    }
     __device__ static __forceinline__ uint4 nan_vector()
     {
         return make_uint4(0x7FC00000u, 0x7FC00000u, 0x7FC00000u, 0x7FC00000u);
@@ -253,8 +273,21 @@ struct Unpack<__nv_bfloat16>
     }
     __device__ static __forceinline__ float maximum(const uint4& v)
     {
-        const uint32_t bits = max_bf16x2(max_bf16x2(v.x, v.y), max_bf16x2(v.z, v.w));
-        return fmaxf(__uint_as_float(bits << 16), __uint_as_float(bits & 0xFFFF0000u));
+        return widen(packed_maximum(v));
+    }
+    // maxima are combined as bf16 pairs (a NaN operand is ignored, like fmaxf) and widened once
+    using Packed = uint32_t;
+    __device__ static __forceinline__ Packed packed_maximum(const uint4& v)
+    {
+        return max_bf16x2(max_bf16x2(v.x, v.y), max_bf16x2(v.z, v.w));
+    }
+    __device__ static __forceinline__ Packed combine(Packed a, Packed b)
+    {
+        return max_bf16x2(a, b);
+    }
+    __device__ static __forceinline__ float widen(Packed p)
+    {
+        return fmaxf(__uint_as_float(p << 16), __uint_as_float(p & 0xFFFF0000u));
     }
     __device__ static __forceinline__ uint4 nan_vector()
     {
@@ -790,7 +823,8 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, const
     // the sample: the chunks every warp has on request when the stream starts, all of them complete
     const uint32_t rounds_available = (chunk_end - chunk_begin) / kWarps;
     const uint32_t complete_chunks = vectors / kChunkVectors;
-    uint32_t sample_rounds = min(ring.stages, rounds_available);
+    // (all but one of the ring's slots: the last one keeps bytes arriving while the threshold is worked out)
+    uint32_t sample_rounds = min(max(ring.stages, 2u) - 1u, rounds_available);
     if (chunk_begin + kWarps * sample_rounds > complete_chunks)
         sample_rounds = (complete_chunks > chunk_begin) ? (complete_chunks - chunk_begin) / kWarps : 0u;
     if (sample_rounds == 0u)
@@ -814,8 +848,7 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, const
     }
 
     MOE_LAP_DECLARE();
-    uint32_t* lists = s.sel.hist; // kThreads entries, untouched while streaming
-    const uint32_t hit_count = shared_address(&s.hit_count[warp]);
+    uint32_t* lists = s.sample_keys;
     const uint32_t hit_vectors = shared_address(&s.hit_vector[warp][0]);
     const uint32_t hit_indices = shared_address(&s.hit_index[warp][0]);
     const uint32_t overflow_flag = shared_address(&s.overflow);
@@ -868,8 +901,6 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, const
         // Threshold = the r-th largest thread maximum: at least r logits of the sample reach it.
         if (tid == 0)
             s.sel.bucket = 0;
-        if (lane == 0)
-            store_shared_32(hit_count, 0u);
         __syncthreads();
         if (static_cast<uint32_t>(lane) < r)
         {
@@ -939,6 +970,41 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, const
         bool maximum_only = false;
         // only the first attempt finds the record buffer zeroed beyond what has been written
         const bool tightening = mode == kTopK && attempt == 0 && k <= kTightenTopKMax;
+        uint32_t queued = 0; // hit vectors on this warp's queue
+        const unsigned lanes_below = (1u << lane) - 1u;
+        // Unpacks the queue; true when the stream of this warp is over (the buffer overflowed).
+        const auto flush_queue = [&]() -> bool {
+            if (mode == kLive)
+                tau = fmaxf(tau, live_threshold(load_shared_32_volatile(maximum_key), temperature));
+            drain_hit_queue<T>(s, rec, cap, mode, tau, queued);
+            queued = 0;
+            if (tightening)
+            {
+                // the first warp to see kTightenAt records in the buffer raises everybody's threshold
+                uint32_t present = 0;
+                if (lane == 0)
+                {
+                    present = load_shared_32_volatile(record_count);
+                    if (present < kTightenAt || atomic_add_shared(tighten_claimed, 1u) != 0u)
+                        present = 0;
+                }
+                present = __shfl_sync(kFullMask, present, 0);
+                if (present != 0u)
+                {
+                    const uint32_t kth = warp_kth_key(rec, min(present, kTightenWindow), k);
+                    if (kth > kKeyNegInf && lane == 0)
+                        store_shared_32(tighten_key, kth);
+                }
+            }
+            if (load_shared_32_volatile(overflow_flag) != 0u)
+            {
+                if (mode == kLive && live_maximum == 0u)
+                    maximum_only = true; // keep looking for the row's maximum
+                else
+                    return true;
+            }
+            return false;
+        };
         for (uint32_t i = 0; usable && !fault && i < my_chunks; ++i)
         {
             if (!ring_acquire(ring))
@@ -967,14 +1033,15 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, const
                     if (first_vector + j * 32 + lane >= vectors)
                         v[j] = U::nan_vector();
             }
-            float top[kVectorsPerLane];
+            typename U::Packed top[kVectorsPerLane];
 #pragma unroll
             for (int j = 0; j < kVectorsPerLane; ++j)
-                top[j] = U::maximum(v[j]);
-            float best = top[0];
+                top[j] = U::packed_maximum(v[j]);
+            typename U::Packed best_packed = top[0];
 #pragma unroll
             for (int j = 1; j < kVectorsPerLane; ++j)
-                best = fmaxf(best, top[j]);
+                best_packed = U::combine(best_packed, top[j]);
+            const float best = U::widen(best_packed);
             const bool hit = best >= tau;
             // the vote needs every lane's values, so all reads of the slot are complete behind it
             const unsigned voters = __ballot_sync(kFullMask, hit);
@@ -991,68 +1058,54 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, const
                 }
                 else
                 {
-                    if (hit)
-                    {
-                        // only the few lanes that have something to queue come here
+                    // Queue the vectors that reached the threshold.  A lane's first slot is the queue
+                    // length plus the vectors of the lanes below it: a popcount of the vote when no lane
+                    // has more than one (nearly always), a prefix sum over the lanes otherwise.
+                    uint32_t mine = 0;
 #pragma unroll
-                        for (int j = 0; j < kVectorsPerLane; ++j)
-                        {
-                            if (!(top[j] >= tau))
-                                continue;
-                            const uint32_t first_index = head + (first_vector + j * 32 + lane) * U::kWidth;
-                            const uint32_t slot = atomic_add_shared(hit_count, 1u);
-                            if (slot < kHitQueue)
-                            {
-                                store_shared_16(hit_vectors + 16u * slot, v[j]);
-                                store_shared_32(hit_indices + 4u * slot, first_index);
-                            }
-                            else
-                            {
-                                // the queue is full (a chunk in which nearly everything passes): unpack in place
-                                float x[U::kWidth];
-                                U::values(v[j], x);
-                                offer_values<U::kWidth>(s, rec, cap, mode, tau, x, first_index);
-                            }
-                            if (mode == kLive && ordered_key(top[j]) > seen_max)
-                                atomic_max_shared(maximum_key, ordered_key(top[j]));
-                        }
-                    }
-                    __syncwarp();
-                    const uint32_t queued = min(load_shared_32_volatile(hit_count), kHitQueue);
-                    if (queued >= kHitQueue / 2u)
+                    for (int j = 0; j < kVectorsPerLane; ++j)
+                        mine |= (U::widen(top[j]) >= tau ? 1u : 0u) << j;
+                    const uint32_t count = __popc(mine);
+                    uint32_t before = __popc(voters & lanes_below);
+                    uint32_t total = __popc(voters);
+                    if (__ballot_sync(kFullMask, count > 1u) != 0u)
                     {
-                        if (mode == kLive)
-                            tau = fmaxf(tau, live_threshold(load_shared_32_volatile(maximum_key), temperature));
-                        drain_hit_queue<T>(s, rec, cap, mode, tau, queued);
-                        if (lane == 0)
-                            store_shared_32(hit_count, 0u);
-                        __syncwarp();
-                        if (tightening)
+                        uint32_t inclusive = count;
+#pragma unroll
+                        for (int offset = 1; offset < 32; offset <<= 1)
                         {
-                            // the first warp to see kTightenAt records in the buffer raises everybody's threshold
-                            uint32_t present = 0;
-                            if (lane == 0)
-                            {
-                                present = load_shared_32_volatile(record_count);
-                                if (present < kTightenAt || atomic_add_shared(tighten_claimed, 1u) != 0u)
-                                    present = 0;
-                            }
-                            present = __shfl_sync(kFullMask, present, 0);
-                            if (present != 0u)
-                            {
-                                const uint32_t kth = warp_kth_key(rec, min(present, kTightenWindow), k);
-                                if (kth > kKeyNegInf && lane == 0)
-                                    store_shared_32(tighten_key, kth);
-                            }
+                            const uint32_t other = __shfl_up_sync(kFullMask, inclusive, offset);
+                            if (lane >= offset)
+                                inclusive += other;
                         }
-                        if (load_shared_32_volatile(overflow_flag) != 0u)
+                        before = inclusive - count;
+                        total = __shfl_sync(kFullMask, inclusive, 31);
+                    }
+                    if (queued + total > kHitQueue && flush_queue())
+                        break;
+                    if (total > kHitQueue)
+                    {
+                        // nearly everything in this chunk passes: the sampled threshold is useless for this slice
+                        if (lane == 0)
+                            store_shared_32(overflow_flag, 1u);
+                        break;
+                    }
+                    uint32_t slot = queued + before;
+#pragma unroll
+                    for (int j = 0; j < kVectorsPerLane; ++j)
+                    {
+                        if ((mine >> j) & 1u)
                         {
-                            if (mode == kLive && live_maximum == 0u)
-                                maximum_only = true; // keep looking for the row's maximum
-                            else
-                                break;
+                            store_shared_16(hit_vectors + 16u * slot, v[j]);
+                            store_shared_32(hit_indices + 4u * slot, head + (first_vector + j * 32 + lane) * U::kWidth);
+                            ++slot;
                         }
                     }
+                    if (mode == kLive && hit && ordered_key(best) > seen_max)
+                        atomic_max_shared(maximum_key, ordered_key(best));
+                    queued += total;
+                    if (queued >= kHitQueue / 2u && flush_queue())
+                        break;
                 }
             }
             if (mode == kLive)
@@ -1071,7 +1124,7 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, const
                 tau = fmaxf(tau, key_to_float(tighter));
         }
         __syncwarp();
-        drain_hit_queue<T>(s, rec, cap, mode, tau, min(load_shared_32_volatile(hit_count), kHitQueue));
+        drain_hit_queue<T>(s, rec, cap, mode, tau, queued);
         MOE_LAP(3);
         MOE_LAP_FLUSH();
         if (!ring_drain(ring))
@@ -1377,7 +1430,7 @@ __host__ __device__ constexpr size_t shared_bytes_for(uint32_t cap, uint32_t sta
 }
 
 template<typename T, bool kLargeBuffer>
-__global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(const SampleArgs a, const Workspace ws, const uint32_t splits, const uint32_t stages)
+__global__ void __launch_bounds__(kThreads, MOE_ROW_MIN_CTAS) sample_rows_kernel(const SampleArgs a, const Workspace ws, const uint32_t splits, const uint32_t stages)
 {
     extern __shared__ __align__(128) unsigned char shared_raw[];
     constexpr uint32_t kCapacity = kLargeBuffer ? kCapLarge : kCapSmall;
@@ -1625,7 +1678,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(const SampleAr
 // ids).  The k best of their union are the row's global Top-K
 // (session.cpp:80-87); the reference normalises over exactly those, so no
 // partial softmax sums cross GPUs.  One CTA per row.
-__global__ void __launch_bounds__(kThreads, 4) merge_candidates_kernel(const uint64_t* gathered, uint32_t shards, uint32_t rows, uint32_t top_k,
+__global__ void __launch_bounds__(kThreads, 2) merge_candidates_kernel(const uint64_t* gathered, uint32_t shards, uint32_t rows, uint32_t top_k,
                                                                         const SampleArgs a)
 {
     extern __shared__ __align__(128) unsigned char shared_raw[];
@@ -1755,7 +1808,8 @@ uint32_t resident_per_sm(bool large_top_k, uint32_t stages)
     // 227 KiB per SM, 1 KiB reserved per CTA
     const size_t per_cta = shared_bytes_for(large_top_k ? kCapLarge : kCapSmall, stages) + 1024u;
     const uint32_t fit = static_cast<uint32_t>((227u * 1024u) / per_cta);
-    return fit < 1u ? 1u : (fit > 8u ? 8u : fit); // 8 CTAs of 256 threads fill an SM's 2048 thread slots
+    const uint32_t by_registers = MOE_ROW_MIN_CTAS; // the launch bounds promise registers for this many
+    return fit < 1u ? 1u : (fit > by_registers ? by_registers : fit);
 }
 
 } // namespace
