@@ -173,6 +173,29 @@ int moe_sample_batch_ex(moe_sampler* sampler, void* stream, const void* logits, 
                         size_t row_stride, const moe_row_params* params, uint64_t step_offset, const int32_t* stop_offsets,
                         const int32_t* stop_tokens, const moe_sample_outputs* outputs);
 
+/* Sampling with the logits already on the device and only the sampled tokens
+ * returned to the host: the LogitsOutputMode::SampledToken the reference
+ * reserves but still rejects (include/ncnn/moe/types.h:304-309,
+ * src/engine/runtime.cpp:579-580).  The staged [sessions x vocab] logit matrix
+ * of the LM head (src/engine/cpu_executor.cpp:2978-2995) stays where it was
+ * produced; what crosses to the host is one 16-byte record per row.
+ *
+ * Same arguments as moe_sample_batch up to stop_tokens.  `stream` is the stream
+ * the logits were produced on: the kernel is ordered behind the producer there.
+ * results   HOST (page-locked for speed: moe_host_alloc), rows records; valid when
+ *           the call returns (it synchronises `stream`). */
+typedef struct moe_sampled_row
+{
+    int32_t token_id;    /* SampledToken::token_id, -1 for a rejected row */
+    float probability;   /* SampledToken::probability */
+    uint32_t row_flags;  /* MOE_ROW_FLAG_* */
+    int32_t row_status;  /* MOE_ROW_* */
+} moe_sampled_row;
+
+int moe_sample_tokens(moe_sampler* sampler, void* stream, const void* logits, int dtype, uint32_t rows, uint32_t vocab,
+                      size_t row_stride, const moe_row_params* params, uint64_t step_offset, const int32_t* stop_offsets,
+                      const int32_t* stop_tokens, moe_sampled_row* results);
+
 /* The verification step of speculative decoding for one Session
  * (the loop of Session::generate, src/engine/session.cpp:776-880): the
  * `draft_count` proposed tokens are walked in order, each accepted with
@@ -330,9 +353,16 @@ int moe_router_dispatch_static(void* stream, const float* router_logits, uint32_
                                size_t error_capacity);
 
 /* Replaces gather_tokens (src/engine/cpu_executor.cpp:635-642): copies
- * hidden[route_token[i], :] to gathered[i, :] for every route.  All device. */
+ * hidden[route_token[i], :] to gathered[i, :] for every route.  All device.
+ * A route_token entry >= token_count is never dereferenced: its row of
+ * `gathered` is zero-filled and the handle remembers that it happened. */
 int moe_regroup_gather(moe_sampler* sampler, void* stream, const float* hidden, uint32_t token_count, uint32_t columns,
                        const uint32_t* route_token, uint32_t route_count, float* gathered);
+/* Synchronises `stream`, reports in *out_of_range whether any moe_regroup_gather
+ * call on this handle since the last check met a token index >= token_count
+ * (1) or not (0), and clears the mark.  No reference counterpart: the
+ * reference indexes its host vector unchecked. */
+int moe_regroup_gather_check(moe_sampler* sampler, void* stream, int32_t* out_of_range);
 
 #ifdef __cplusplus
 }

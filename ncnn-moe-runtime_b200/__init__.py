@@ -23,6 +23,8 @@ LIBRARY_PATH = HERE / "libmoe_b200_sampler.so"
 SPECULATIVE_RESULT_DTYPE = np.dtype([("accepted", np.uint32), ("next_token", np.int32), ("next_probability", np.float32),
                                      ("uniforms_used", np.uint32), ("status", np.int32), ("flags", np.uint32)])
 SPECULATIVE_MAX_DRAFT = 16
+# numpy view of moe_sampled_row (16 bytes): what moe_sample_tokens returns per row
+SAMPLED_ROW_DTYPE = np.dtype([("token", np.int32), ("probability", np.float32), ("flags", np.uint32), ("status", np.int32)])
 
 
 class SampleOutputs(C.Structure):
@@ -56,7 +58,7 @@ EXPORTED_SYMBOLS = [
     "moe_philox_uniform", "moe_host_alloc", "moe_host_free", "moe_sample_batch", "moe_sample_batch_ex", "moe_speculative_verify", "moe_speculative_verify_host", "moe_sample_batch_host",
     "moe_sample_local_candidates", "moe_sample_merge_candidates", "moe_router_dispatch", "moe_router_status_message",
     "moe_router_status_error_code", "moe_router_check_options", "moe_router_dispatch_host", "moe_regroup_gather",
-    "moe_router_dispatch_static", "moe_sampler_set_overlap",
+    "moe_router_dispatch_static", "moe_sampler_set_overlap", "moe_sample_tokens", "moe_regroup_gather_check",
 ]
 
 _library = None
@@ -106,6 +108,8 @@ def library() -> C.CDLL:
     lib.moe_router_status_error_code.argtypes = [C.c_int]
     lib.moe_router_check_options.argtypes = [u32, C.POINTER(RouterOptions)]
     lib.moe_regroup_gather.argtypes = [vp, vp, vp, u32, u32, vp, u32, vp]
+    lib.moe_sample_tokens.argtypes = [vp, vp, vp, C.c_int, u32, u32, sz, vp, u64, vp, vp, vp]
+    lib.moe_regroup_gather_check.argtypes = [vp, vp, C.POINTER(i32)]
     lib.moe_router_dispatch_static.argtypes = [vp, vp, u32, C.POINTER(RouterOptions), vp, vp, vp, vp, vp, C.c_char_p, sz]
     _library = lib
     return lib
@@ -238,6 +242,25 @@ class Sampler:
                                                _dev_ptr(out.get("topk")), int(topk_stride)))
         return out
 
+    def sample_tokens(self, logits, params=None, step_offset=0, stop_lists=None, stream=None, vocab=None, results=None):
+        """moe_sample_tokens: CUDA logits in, one 16-byte record per row out on the host (synchronous).
+        results: optional numpy array of SAMPLED_ROW_DTYPE (e.g. a view of page-locked memory) to fill."""
+        import torch
+        rows, row_stride = logits.shape
+        vocab = row_stride if vocab is None else vocab
+        dtype = DTYPE_F32 if logits.dtype == torch.float32 else DTYPE_BF16
+        if results is None:
+            results = np.empty(rows, dtype=SAMPLED_ROW_DTYPE)
+        offsets = tokens = None
+        if stop_lists is not None:
+            offsets, tokens = stop_lists_to_csr(stop_lists)
+        if params is not None:
+            params = np.ascontiguousarray(params, dtype=ROW_PARAMS_DTYPE)
+        stream_handle = torch.cuda.current_stream(logits.device).cuda_stream if stream is None else stream
+        self._check(self._lib.moe_sample_tokens(self._handle, C.c_void_p(stream_handle), _dev_ptr(logits), dtype, rows, vocab, logits.stride(0),
+                                                _np_ptr(params), int(step_offset), _np_ptr(offsets), _np_ptr(tokens), _np_ptr(results)))
+        return results
+
     def speculative_verify(self, target_logits, draft_logits, proposed, params, stream=None, out=None, sync=True):
         """Verification step of speculative decoding for one Session (moe_speculative_verify).
         target_logits: CUDA [draft_count + 1, row_stride]; draft_logits: CUDA [draft_count, row_stride];
@@ -321,23 +344,24 @@ class Sampler:
                                                     _np_ptr(out["status"]), None, 0))
 
     # ---- vocabulary-sharded -------------------------------------------------------
-    def local_candidates(self, logits, vocab_begin, top_k, stream=None):
+    def local_candidates(self, logits, vocab_begin, top_k, stream=None, out=None):
+        """moe_sample_local_candidates: [rows, top_k] int64 records of this vocabulary slice (written to `out` when given)."""
         import torch
         rows, row_stride = logits.shape
         dtype = DTYPE_F32 if logits.dtype == torch.float32 else DTYPE_BF16
-        candidates = torch.empty((rows, top_k), dtype=torch.int64, device=logits.device)
+        candidates = torch.empty((rows, top_k), dtype=torch.int64, device=logits.device) if out is None else out
         stream_handle = torch.cuda.current_stream(logits.device).cuda_stream if stream is None else stream
         self._check(self._lib.moe_sample_local_candidates(self._handle, C.c_void_p(stream_handle), _dev_ptr(logits), dtype, rows, row_stride,
                                                           logits.stride(0), int(vocab_begin), int(top_k), _dev_ptr(candidates)))
         return candidates
 
-    def merge_candidates(self, gathered, params, top_k, step_offset=0, topk_stride=0, stream=None):
+    def merge_candidates(self, gathered, params, top_k, step_offset=0, topk_stride=0, stream=None, out=None):
         """gathered: CUDA int64 tensor [shards, rows, top_k]."""
         import torch
         shards, rows, k = gathered.shape
         assert k == top_k
         device = gathered.device
-        out = {
+        out = out if out is not None else {
             "token": torch.empty(rows, dtype=torch.int32, device=device),
             "probability": torch.empty(rows, dtype=torch.float32, device=device),
             "flags": torch.empty(rows, dtype=torch.int32, device=device),
@@ -404,3 +428,11 @@ class Sampler:
         self._check(self._lib.moe_regroup_gather(self._handle, C.c_void_p(stream_handle), _dev_ptr(hidden), token_count, columns,
                                                  _dev_ptr(route_token), routes, _dev_ptr(gathered)))
         return gathered
+
+    def regroup_gather_check(self, stream=None) -> bool:
+        """True when a regroup_gather since the last check met a token index outside the hidden matrix (synchronises)."""
+        import torch
+        stream_handle = torch.cuda.current_stream(self.device).cuda_stream if stream is None else stream
+        flag = C.c_int32(0)
+        self._check(self._lib.moe_regroup_gather_check(self._handle, C.c_void_p(stream_handle), C.byref(flag)))
+        return flag.value != 0

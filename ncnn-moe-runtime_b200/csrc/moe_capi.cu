@@ -33,6 +33,9 @@ struct moe_sampler
     bool overlap_launches = false;
     bool resident_has_stops = false;
 
+    // packed per-row results of moe_sample_tokens
+    moe_sampled_row* sampled_dev = nullptr;
+
     // staging for the host-buffer entry points
     void* logits_dev = nullptr;
     size_t logits_dev_bytes = 0;
@@ -278,6 +281,7 @@ int moe_sampler_create(int device, uint32_t max_rows, uint32_t max_vocab, moe_sa
     allocate(reinterpret_cast<void**>(&sampler->probability_dev), sizeof(float) * max_rows);
     allocate(reinterpret_cast<void**>(&sampler->flags_dev), sizeof(uint32_t) * max_rows);
     allocate(reinterpret_cast<void**>(&sampler->status_dev), sizeof(int32_t) * max_rows);
+    allocate(reinterpret_cast<void**>(&sampler->sampled_dev), sizeof(moe_sampled_row) * max_rows);
     allocate(reinterpret_cast<void**>(&sampler->router_error), sizeof(unsigned long long));
     allocate(reinterpret_cast<void**>(&sampler->router_scan_done), sizeof(uint32_t));
     allocate(reinterpret_cast<void**>(&sampler->gather_status), sizeof(int32_t));
@@ -317,7 +321,7 @@ void moe_sampler_destroy(moe_sampler* sampler)
                         sampler->ws.slice_header, sampler->ws.row_arrivals, sampler->params_dev, sampler->stop_offsets_dev,
                         sampler->stop_tokens_dev, sampler->logits_dev, sampler->token_dev, sampler->probability_dev, sampler->flags_dev,
                         sampler->status_dev, sampler->topk_dev, sampler->selected_expert, sampler->selected_weight, sampler->expert_counts,
-                        sampler->router_error, sampler->router_scan_done, sampler->router_block_counts, sampler->gather_status,
+                        sampler->sampled_dev, sampler->router_error, sampler->router_scan_done, sampler->router_block_counts, sampler->gather_status,
                         sampler->router_logits_dev, sampler->router_bias_dev, sampler->router_explicit_dev,
                         sampler->router_offsets_dev, sampler->router_token_dev, sampler->router_rank_dev, sampler->router_weight_dev,
                         sampler->router_status_dev, sampler->spec_kept_token, sampler->spec_kept_probability, sampler->spec_kept_count,
@@ -603,6 +607,29 @@ int moe_sample_batch_host(moe_sampler* sampler, const void* logits, int dtype, u
     return MOE_STATUS_OK;
 }
 
+int moe_sample_tokens(moe_sampler* sampler, void* stream_handle, const void* logits, int dtype, uint32_t rows, uint32_t vocab, size_t row_stride,
+                      const moe_row_params* params, uint64_t step_offset, const int32_t* stop_offsets, const int32_t* stop_tokens,
+                      moe_sampled_row* results)
+{
+    if (int status = check_shape(sampler, dtype, rows, vocab, row_stride))
+        return status;
+    if (rows == 0)
+        return MOE_STATUS_OK;
+    if (logits == nullptr || results == nullptr)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "logits and results must not be null");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+    const int status = moe_sample_batch(sampler, stream, logits, dtype, rows, vocab, row_stride, params, step_offset, stop_offsets, stop_tokens,
+                                        sampler->token_dev, sampler->probability_dev, sampler->flags_dev, sampler->status_dev, nullptr, 0);
+    if (status != MOE_STATUS_OK)
+        return status;
+    DeviceGuard guard(sampler->device);
+    MOE_CUDA_CHECK(sampler, launch_pack_sampled_rows(sampler->token_dev, sampler->probability_dev, sampler->flags_dev, sampler->status_dev, rows,
+                                                     sampler->sampled_dev, stream));
+    MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(results, sampler->sampled_dev, sizeof(moe_sampled_row) * rows, cudaMemcpyDeviceToHost, stream));
+    MOE_CUDA_CHECK(sampler, cudaStreamSynchronize(stream));
+    return MOE_STATUS_OK;
+}
+
 int moe_speculative_verify_host(moe_sampler* sampler, const void* target_logits, const void* draft_logits, int dtype, uint32_t draft_count,
                                 uint32_t vocab, size_t row_stride, const int32_t* proposed_tokens, const moe_row_params* params,
                                 float* accepted_probability, moe_speculative_result* result)
@@ -876,6 +903,18 @@ int moe_regroup_gather(moe_sampler* sampler, void* stream_handle, const float* h
     DeviceGuard guard(sampler->device);
     MOE_CUDA_CHECK(sampler, launch_regroup_gather(hidden, token_count, columns, route_token, route_count, gathered, sampler->gather_status,
                                                   static_cast<cudaStream_t>(stream_handle)));
+    return MOE_STATUS_OK;
+}
+
+int moe_regroup_gather_check(moe_sampler* sampler, void* stream_handle, int32_t* out_of_range)
+{
+    if (sampler == nullptr || out_of_range == nullptr)
+        return MOE_STATUS_INVALID_ARGUMENT;
+    DeviceGuard guard(sampler->device);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+    MOE_CUDA_CHECK(sampler, cudaMemcpyAsync(out_of_range, sampler->gather_status, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+    MOE_CUDA_CHECK(sampler, cudaMemsetAsync(sampler->gather_status, 0, sizeof(int32_t), stream));
+    MOE_CUDA_CHECK(sampler, cudaStreamSynchronize(stream));
     return MOE_STATUS_OK;
 }
 

@@ -77,6 +77,9 @@ struct SampleArgs
 
 cudaError_t launch_sample_rows(const SampleArgs& args, const Workspace& ws, uint32_t splits, cudaStream_t stream);
 cudaError_t launch_sample_exact(const SampleArgs& args, const Workspace& ws, cudaStream_t stream);
+// token_id / probability / row_flags / row_status arrays -> one 16-byte record per row
+cudaError_t launch_pack_sampled_rows(const int32_t* token_id, const float* probability, const uint32_t* row_flags, const int32_t* row_status,
+                                     uint32_t rows, moe_sampled_row* packed, cudaStream_t stream);
 cudaError_t launch_merge_candidates(const uint64_t* gathered, uint32_t shards, uint32_t rows, uint32_t top_k, const moe_row_params* params,
                                     uint64_t step_offset, int32_t* token_id, float* probability, uint32_t* row_flags, int32_t* row_status,
                                     int32_t* topk_index, uint32_t topk_stride, cudaStream_t stream);
@@ -127,7 +130,25 @@ struct RouterPartition
     uint32_t tokens_per_block;
     uint32_t blocks;
 };
-RouterPartition router_partition(uint32_t token_count, uint32_t experts);
+// blocks of the select kernel: about four per SM (148 SMs, four warps of one token each per block), fewer when
+// the [expert][block] table would outgrow MOE_ROUTER_BLOCK_TABLE_ENTRIES
+inline RouterPartition router_partition_host(uint32_t token_count, uint32_t experts)
+{
+    constexpr uint32_t kWarpsPerBlock = 4;
+    RouterPartition part;
+    part.tokens_per_block = kWarpsPerBlock * ((token_count + kWarpsPerBlock * 592u - 1u) / (kWarpsPerBlock * 592u));
+    if (part.tokens_per_block == 0)
+        part.tokens_per_block = kWarpsPerBlock;
+    part.blocks = (token_count + part.tokens_per_block - 1u) / part.tokens_per_block;
+    while (static_cast<uint64_t>(part.blocks) * experts > MOE_ROUTER_BLOCK_TABLE_ENTRIES)
+    {
+        part.tokens_per_block *= 2u;
+        part.blocks = (token_count + part.tokens_per_block - 1u) / part.tokens_per_block;
+    }
+    if (part.blocks == 0)
+        part.blocks = 1;
+    return part;
+}
 // expert_counts: [expert_count] scratch; scan_done: one word that is 0 between calls; error_word: ~0 between calls
 cudaError_t launch_router_dispatch_kernels(const RouterArgs& args, uint32_t* expert_counts, uint32_t* scan_done, unsigned long long* error_word,
                                            cudaStream_t stream);

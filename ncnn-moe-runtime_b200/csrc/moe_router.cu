@@ -484,27 +484,13 @@ __global__ void __launch_bounds__(256) regroup_gather_kernel(const float* hidden
 
 } // namespace
 
-RouterPartition router_partition(uint32_t token_count, uint32_t experts)
-{
-    // blocks of the select kernel: about four per SM, fewer when the
-    // [expert][block] table would outgrow MOE_ROUTER_BLOCK_TABLE_ENTRIES
-    RouterPartition part;
-    part.tokens_per_block = kRouteWarps * ((token_count + kRouteWarps * 592u - 1u) / (kRouteWarps * 592u));
-    part.blocks = (token_count + part.tokens_per_block - 1u) / part.tokens_per_block;
-    while (static_cast<uint64_t>(part.blocks) * experts > MOE_ROUTER_BLOCK_TABLE_ENTRIES)
-    {
-        part.tokens_per_block *= 2u;
-        part.blocks = (token_count + part.tokens_per_block - 1u) / part.tokens_per_block;
-    }
-    return part;
-}
-
 cudaError_t launch_router_dispatch_kernels(const RouterArgs& caller_args, uint32_t* expert_counts, uint32_t* scan_done, unsigned long long* error_word,
                                            cudaStream_t stream)
 {
     RouterArgs args = caller_args;
     const uint32_t experts = args.options.expert_count;
-    const RouterPartition part = router_partition(args.token_count, experts);
+    static_assert(kRouteWarps == 4, "router_partition_host assumes four warps per block");
+    const RouterPartition part = router_partition_host(args.token_count, experts);
     args.tokens_per_block = part.tokens_per_block;
     const size_t shared_bytes = static_cast<size_t>(kRouteWarps) * experts * (sizeof(float) + sizeof(uint64_t)) + sizeof(uint32_t) * experts +
                                 sizeof(uint32_t) * 256u * kRouteWarps;

@@ -1830,6 +1830,25 @@ cudaError_t launch_sample_rows(const SampleArgs& args, const Workspace& ws, uint
     return launch_typed<__nv_bfloat16, false>(args, ws, splits, stages, stream);
 }
 
+namespace {
+__global__ void pack_sampled_rows_kernel(const int32_t* token_id, const float* probability, const uint32_t* row_flags, const int32_t* row_status,
+                                         uint32_t rows, moe_sampled_row* packed)
+{
+    const uint32_t row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row < rows)
+        packed[row] = moe_sampled_row{token_id[row], probability[row], row_flags[row], row_status[row]};
+}
+} // namespace
+
+cudaError_t launch_pack_sampled_rows(const int32_t* token_id, const float* probability, const uint32_t* row_flags, const int32_t* row_status,
+                                     uint32_t rows, moe_sampled_row* packed, cudaStream_t stream)
+{
+    if (rows == 0)
+        return cudaSuccess;
+    pack_sampled_rows_kernel<<<(rows + 255u) / 256u, 256, 0, stream>>>(token_id, probability, row_flags, row_status, rows, packed);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_merge_candidates(const uint64_t* gathered, uint32_t shards, uint32_t rows, uint32_t top_k, const moe_row_params* params,
                                     uint64_t step_offset, int32_t* token_id, float* probability, uint32_t* row_flags, int32_t* row_status,
                                     int32_t* topk_index, uint32_t topk_stride, cudaStream_t stream)

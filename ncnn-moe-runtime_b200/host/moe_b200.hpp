@@ -169,6 +169,29 @@ inline Result<Handle> make_handle(int device, uint32_t max_rows, uint32_t max_vo
 
 } // namespace detail
 
+// What a decode step hands back to the host, after LogitsOutputMode of the
+// reference (include/ncnn/moe/types.h:304-309).  The reference accepts only
+// FullLogits today (src/engine/runtime.cpp:579-580); SampledToken is the mode a
+// device-side sampler makes possible: the [sessions x vocab] logits stay on the
+// GPU that produced them and only {token, probability} per Session returns.
+enum class LogitsOutputMode : uint32_t
+{
+    FullLogits = 0,  // host logits in, DeviceSampler::sample / sample_batch(std::span<const float>, ...)
+    SampledToken = 2 // device logits in, DeviceSampler::sample_batch(DeviceLogits, ...)
+};
+
+// A [rows x row_stride] logit matrix that lives on the device, e.g. the staged
+// LM-head output of src/engine/cpu_executor.cpp:2978-2995 kept on the GPU.
+struct DeviceLogits
+{
+    const void* data = nullptr; // device pointer
+    int dtype = MOE_DTYPE_F32;  // MOE_DTYPE_F32 or MOE_DTYPE_BF16
+    uint32_t rows = 0;
+    uint32_t vocab = 0;
+    size_t row_stride = 0;      // elements between rows, >= vocab
+    void* stream = nullptr;     // cudaStream_t the producer wrote the logits on
+};
+
 // One sampling stream: what a Session is to the reference sampler.  `seed`
 // plays the role of SessionOptions::sampling_seed (session.h:283); `session_id`
 // distinguishes the streams of one batch; every sample() call advances `step`.
@@ -252,6 +275,68 @@ public:
         return results;
     }
 
+    // LogitsOutputMode::SampledToken: the cross-Session step on logits that never
+    // leave the device.  The sampling kernel is ordered behind the producer on
+    // logits.stream; one 16-byte record per row comes back.
+    [[nodiscard]] std::vector<Result<SampledToken>> sample_batch(const DeviceLogits& logits, std::span<const SamplingOptions> options,
+                                                                 std::span<const int32_t> stop_tokens = {})
+    {
+        const uint32_t rows = static_cast<uint32_t>(options.size());
+        std::vector<Result<SampledToken>> results;
+        results.reserve(rows);
+        if (logits.data == nullptr || logits.vocab == 0 || logits.rows != rows || rows > max_rows_)
+        {
+            const char* text = (logits.data == nullptr || logits.vocab == 0) ? "cannot sample empty logits"
+                                                                             : "logits do not match the number of options or exceed the sampler's row capacity";
+            for (uint32_t r = 0; r < rows; ++r)
+                results.emplace_back(Error{ErrorCode::InvalidArgument, text});
+            return results;
+        }
+        std::vector<moe_row_params> params(rows);
+        std::vector<int32_t> offsets(rows + 1);
+        std::vector<int32_t> stops;
+        for (uint32_t r = 0; r < rows; ++r)
+        {
+            params[r] = moe_row_params{options[r].temperature, options[r].top_k, options[r].top_p, options[r].min_p, seed_, session_id_ + r, step_};
+            offsets[r] = static_cast<int32_t>(stops.size());
+            stops.insert(stops.end(), stop_tokens.begin(), stop_tokens.end());
+        }
+        offsets[rows] = static_cast<int32_t>(stops.size());
+        if (sampled_rows_ == nullptr)
+        {
+            void* pinned = nullptr;
+            if (moe_host_alloc(sizeof(moe_sampled_row) * max_rows_, &pinned) != MOE_STATUS_OK)
+            {
+                for (uint32_t r = 0; r < rows; ++r)
+                    results.emplace_back(Error{ErrorCode::InternalError, "page-locked result buffer could not be allocated"});
+                return results;
+            }
+            sampled_rows_ = static_cast<moe_sampled_row*>(pinned);
+        }
+        const int status = moe_sample_tokens(handle_.get(), logits.stream, logits.data, logits.dtype, rows, logits.vocab, logits.row_stride, params.data(), 0,
+                                             stops.empty() ? nullptr : offsets.data(), stops.empty() ? nullptr : stops.data(), sampled_rows_);
+        ++step_;
+        for (uint32_t r = 0; r < rows; ++r)
+        {
+            const moe_sampled_row& row = sampled_rows_[r];
+            if (status != MOE_STATUS_OK)
+                results.emplace_back(Error{detail::to_error_code(status), moe_sampler_last_error(handle_.get())});
+            else if (row.row_status != MOE_ROW_OK)
+                results.emplace_back(Error{detail::to_error_code(moe_row_status_error_code(row.row_status)), moe_row_status_message(row.row_status)});
+            else
+                results.emplace_back(SampledToken{row.token_id, row.probability, (row.row_flags & MOE_ROW_FLAG_STOP_TOKEN) != 0});
+        }
+        return results;
+    }
+
+    ~DeviceSampler()
+    {
+        if (sampled_rows_ != nullptr)
+            moe_host_free(sampled_rows_);
+    }
+    DeviceSampler(const DeviceSampler&) = delete;
+    DeviceSampler& operator=(const DeviceSampler&) = delete;
+
     // The verification step of Session::generate's speculative branch
     // (src/engine/session.cpp:776-880): `proposed` tokens of the draft model
     // against target_logits [(proposed.size() + 1) x vocab] and draft_logits
@@ -300,6 +385,7 @@ private:
     uint64_t session_id_ = 0;
     uint64_t step_ = 0;
     uint32_t max_rows_ = 0;
+    moe_sampled_row* sampled_rows_ = nullptr; // page-locked, max_rows_ records, allocated by the first SampledToken call
 };
 
 // ExpertDispatcher on the GPU.  Input is token-major; output is ordered by

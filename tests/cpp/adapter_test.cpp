@@ -14,6 +14,15 @@
 
 using namespace moe_b200;
 
+// The CUDA runtime calls this test needs to put logits on the device (the
+// adapter itself needs no CUDA header): declared here, resolved from libcudart.
+extern "C" {
+int cudaMalloc(void** pointer, size_t bytes);
+int cudaFree(void* pointer);
+int cudaMemcpy(void* destination, const void* source, size_t bytes, int kind);
+}
+constexpr int kCudaMemcpyHostToDevice = 1;
+
 static void check(bool condition, const std::source_location where = std::source_location::current())
 {
     if (!condition)
@@ -163,6 +172,68 @@ static void test_expert_dispatcher()
     check(routed.value().batches[1].expert_id == 3);
 }
 
+// LogitsOutputMode::SampledToken: the same rows sampled from logits that stay on
+// the device must give what the host-logits path (FullLogits) gives, stop flags
+// and per-row errors included.
+static void test_device_resident_logits()
+{
+    constexpr uint32_t rows = 6, vocab = 5000;
+    std::vector<float> logits(static_cast<size_t>(rows) * vocab);
+    uint32_t state = 12345u;
+    for (float& value : logits)
+    {
+        state = state * 1664525u + 1013904223u;
+        value = static_cast<float>(state >> 8) * (12.0f / 16777216.0f) - 6.0f;
+    }
+    logits[3 * vocab + 77] = 40.0f; // row 3 collapses to one candidate
+    std::vector<SamplingOptions> options(rows);
+    options[0].temperature = 0.0f;
+    options[1].top_k = 40;
+    options[1].top_p = 0.9f;
+    options[2].top_k = 5;
+    options[2].temperature = 0.7f;
+    options[3].top_p = 0.95f;
+    options[4].top_p = 0.0f; // invalid: reported per row
+    options[5].top_k = 300;
+    options[5].min_p = 0.01f;
+    const std::array<int32_t, 1> stops = {77};
+
+    auto host_side = DeviceSampler::create(99, 7, vocab, rows);
+    auto device_side = DeviceSampler::create(99, 7, vocab, rows);
+    check(static_cast<bool>(host_side) && static_cast<bool>(device_side));
+    const auto expected = host_side.value()->sample_batch(logits, vocab, options, stops);
+
+    void* device_logits = nullptr;
+    check(cudaMalloc(&device_logits, logits.size() * sizeof(float)) == 0);
+    check(cudaMemcpy(device_logits, logits.data(), logits.size() * sizeof(float), kCudaMemcpyHostToDevice) == 0);
+    DeviceLogits view;
+    view.data = device_logits;
+    view.dtype = MOE_DTYPE_F32;
+    view.rows = rows;
+    view.vocab = vocab;
+    view.row_stride = vocab;
+    view.stream = nullptr; // the legacy default stream: the copy above has completed
+    const auto sampled = device_side.value()->sample_batch(view, options, stops);
+    check(sampled.size() == rows && expected.size() == rows);
+    for (uint32_t r = 0; r < rows; ++r)
+    {
+        check(static_cast<bool>(sampled[r]) == static_cast<bool>(expected[r]));
+        if (!sampled[r])
+        {
+            check(sampled[r].error().code == expected[r].error().code);
+            check(sampled[r].error().message == expected[r].error().message);
+            continue;
+        }
+        check(sampled[r].value().token_id == expected[r].value().token_id);
+        check(sampled[r].value().probability == expected[r].value().probability);
+        check(sampled[r].value().is_stop_token == expected[r].value().is_stop_token);
+    }
+    check(!sampled[4] && sampled[4].error().message == "top_p must be in the range (0, 1]");
+    check(sampled[3].value().token_id == 77 && sampled[3].value().is_stop_token);
+    check(device_side.value()->step() == 1);
+    check(cudaFree(device_logits) == 0);
+}
+
 // The verification step of speculative decoding (src/engine/session.cpp:776-880
 // of the reference) on cases small enough to follow by hand.
 static void test_speculative_verification()
@@ -240,6 +311,7 @@ int main()
         test_sampling();
         test_expert_dispatcher();
         test_speculative_verification();
+        test_device_resident_logits();
     }
     catch (const std::exception& error)
     {

@@ -85,3 +85,20 @@ def test_shard_ranges(pkg):
             assert vocab_ranges[0][0] == 0 and vocab_ranges[-1][1] == total
             assert all(vocab_ranges[i][1] == vocab_ranges[i + 1][0] for i in range(world - 1))
             assert all(b % 16 == 0 or b == total for b, _ in vocab_ranges)
+
+
+def test_shared_memory_opt_in_bookkeeping(tmp_path):
+    """tests/cpp/opt_in_test.cpp: host-only logic of csrc/moe_internal.h, compiled with the CUDA headers but run without a GPU."""
+    import shutil
+    import subprocess
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    compiler = shutil.which("g++")
+    include = Path("/usr/local/cuda/include")
+    if compiler is None or not (include / "cuda_runtime.h").exists():
+        import pytest
+        pytest.skip("needs g++ and the CUDA headers")
+    target = tmp_path / "opt_in_test"
+    subprocess.run([compiler, "-std=c++17", "-O1", f"-I{include}", str(root / "tests" / "cpp" / "opt_in_test.cpp"), "-o", str(target)], check=True)
+    result = subprocess.run([str(target)], capture_output=True, text=True, timeout=60)
+    assert result.returncode == 0, result.stdout + result.stderr

@@ -15,8 +15,11 @@ def build(pkg, target: Path) -> None:
     compiler = shutil.which("g++")
     if compiler is None:
         pytest.skip("no g++ on this machine")
+    cuda_lib = Path("/usr/local/cuda/lib64")
+    if not (cuda_lib / "libcudart.so").exists():
+        pytest.skip("no CUDA runtime library to link the test's device allocations against")
     subprocess.run([compiler, "-std=c++20", "-O1", "-Wall", "-Wextra", str(SOURCE), "-o", str(target), f"-L{library_dir}",
-                    "-lmoe_b200_sampler", f"-Wl,-rpath,{library_dir}"], check=True)
+                    "-lmoe_b200_sampler", f"-L{cuda_lib}", "-lcudart", f"-Wl,-rpath,{library_dir}", f"-Wl,-rpath,{cuda_lib}"], check=True)
 
 
 def test_adapter_compiles_and_links(pkg, tmp_path):

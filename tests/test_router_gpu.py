@@ -117,6 +117,61 @@ def test_router_shapes_and_ties(sampler, checker, port):
     compare(sampler.router_dispatch_host(logits, 40, 16, 4, score_function=2, explicit_ids=explicit), want, 16, exact["weight"])
 
 
+def test_wide_routers(sampler, checker, port, pkg):
+    """More than 1024 experts or top_k above 16: the k survivors are radix-selected before the rank order is
+    established, the select kernel needs more than 48 KiB of shared memory, and the offsets scan walks several chunks."""
+    rng = np.random.default_rng(21)
+    for tokens, experts, top_k in ((3, 1025, 8), (8, 4096, 8), (5, 2048, 64), (4, 600, 40), (2, 4096, 300)):
+        logits = (rng.standard_normal((tokens, experts)) * 2).astype(np.float32)
+        logits[:, ::7] = logits[:, 3:4]                      # exact ties across experts
+        bias = (0.1 * rng.standard_normal(experts)).astype(np.float32)
+        for score_function in (0, 1, 2):
+            kwargs = dict(score_function=score_function, selection_bias=bias)
+            want, exact = both_oracles(checker, port, logits, tokens, experts, top_k, **kwargs)
+            compare(sampler.router_dispatch_host(logits, tokens, experts, top_k, **kwargs), want, experts, exact["weight"])
+    assert sampler.router_dispatch_host(np.zeros((1, 4097), dtype=np.float32), 1, 4097, 2).status == 110
+
+
+def test_cross_session_coalescing(sampler, checker, torch_cuda):
+    """src/engine/cpu_executor.cpp:3217-3264 of the reference: every Session of a decode step is dispatched on its
+    own (one token each), then the routes that name the same expert are merged into one batch with token_index
+    rewritten to the Session's position in the step.  One dispatch of the stacked [sessions x experts] router
+    logits yields exactly those batches: same expert sets, and inside an expert the Sessions in ascending order
+    with the ranks and weights of their own plans."""
+    rng = np.random.default_rng(33)
+    sessions, experts, top_k = 48, 64, 6
+    logits = rng.standard_normal((sessions, experts)).astype(np.float32)
+    bias = (0.1 * rng.standard_normal(experts)).astype(np.float32)
+    merged = {}
+    for session in range(sessions):
+        plan = checker.expert_dispatch(logits[session], 1, experts, top_k, score_function=1, selection_bias=bias)
+        for b, expert in enumerate(plan["batch_expert"]):
+            for i in range(plan["batch_offset"][b], plan["batch_offset"][b + 1]):
+                assert plan["token"][i] == 0
+                merged.setdefault(int(expert), []).append((session, int(plan["rank"][i]), np.float32(plan["weight"][i])))
+    stacked = sampler.router_dispatch_host(logits, sessions, experts, top_k, score_function=1, selection_bias=bias)
+    assert stacked.status == 0
+    offsets = stacked.expert_offsets.astype(np.int64)
+    assert sorted(merged) == [e for e in range(experts) if offsets[e + 1] > offsets[e]]
+    for expert, routes in merged.items():
+        rows = slice(offsets[expert], offsets[expert + 1])
+        assert stacked.route_token[rows].tolist() == [r[0] for r in routes]      # Session order = the order the executor appends in
+        assert stacked.route_rank[rows].tolist() == [r[1] for r in routes]
+        np.testing.assert_allclose(stacked.route_weight[rows], np.array([r[2] for r in routes]), rtol=1e-5, atol=0)
+
+
+def test_regroup_gather_refuses_tokens_outside_the_matrix(sampler, torch_cuda):
+    torch = torch_cuda
+    hidden = torch.randn(10, 64, device="cuda")
+    route_token = torch.tensor([3, 9, 10, 0, 4000000000 - 2**32, 7], dtype=torch.int32, device="cuda")   # 10 and 4e9 are out of range
+    assert sampler.regroup_gather_check() is False
+    gathered = sampler.regroup_gather(hidden, route_token)
+    assert sampler.regroup_gather_check() is True
+    assert sampler.regroup_gather_check() is False                      # the mark is cleared by the check
+    assert torch.equal(gathered[[0, 1, 3, 5]], hidden[[3, 9, 0, 7]])
+    assert torch.count_nonzero(gathered[[2, 4]]).item() == 0            # zero-filled, nothing dereferenced
+
+
 def test_router_errors(sampler, pkg):
     logits = np.zeros((4, 8), dtype=np.float32)
     assert sampler.router_dispatch_host(logits, 0, 8, 2).status == 104

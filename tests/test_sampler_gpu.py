@@ -297,3 +297,54 @@ def test_kept_candidate_lists_without_top_k(pkg, workloads, parity, torch_cuda):
     logits, params = workloads.config2_greedy_temperature(pkg.ROW_PARAMS_DTYPE, rows=12, vocab=20011, seed=4)
     params["top_p"][1::2] = np.linspace(0.3, 1.0, params["top_p"][1::2].size)
     _check_kept_lists(pkg, parity, torch_cuda, logits, params, kept_stride=20011)
+
+
+def test_sampled_tokens_from_device_logits(pkg, workloads, parity, torch_cuda):
+    """moe_sample_tokens (LogitsOutputMode::SampledToken): logits stay on the device, one 16-byte record per row
+    returns; the records equal what moe_sample_batch writes, and the tokens equal the oracle's."""
+    torch = torch_cuda
+    logits, params = workloads.config3_mixed(pkg.ROW_PARAMS_DTYPE, rows=40, vocab=30011)
+    params["top_p"][5] = 0.0                                      # one rejected row
+    device = torch.from_numpy(logits).cuda()
+    stops = [[int(t)] for t in np.argmax(logits, axis=1)]          # every row's stop list: its arg-max
+    want = parity.sampler.sample_batch(device, params, stop_lists=stops)
+    torch.cuda.synchronize()
+    records = parity.sampler.sample_tokens(device, params, stop_lists=stops)
+    assert records.dtype.itemsize == 16
+    np.testing.assert_array_equal(records["token"], want["token"].cpu().numpy())
+    np.testing.assert_array_equal(records["probability"].view(np.uint32), want["probability"].cpu().numpy().view(np.uint32))
+    np.testing.assert_array_equal(records["flags"], want["flags"].cpu().numpy().view(np.uint32))
+    np.testing.assert_array_equal(records["status"], want["status"].cpu().numpy())
+    assert records["status"][5] == 3 and records["token"][5] == -1
+    uniforms = parity.uniforms(params)
+    oracle = parity.checker.sample_batch(logits, params["temperature"], params["top_k"], params["top_p"], params["min_p"], uniforms)
+    np.testing.assert_array_equal(records["token"], oracle["token"])
+    # resident parameters and a step offset, into page-locked memory
+    pinned = torch.empty(40 * 16, dtype=torch.uint8).pin_memory()
+    view = pinned.numpy().view(pkg.SAMPLED_ROW_DTYPE)
+    parity.sampler.sample_tokens(device, None, step_offset=3, results=view)
+    oracle = parity.checker.sample_batch(logits, params["temperature"], params["top_k"], params["top_p"], params["min_p"], parity.uniforms(params, 3))
+    np.testing.assert_array_equal(view["token"], oracle["token"])
+
+
+def test_handles_on_two_devices_in_one_process(pkg, workloads, checker, torch_cuda):
+    """Kernels that need more than 48 KiB of shared memory opt in per device; a second handle on another GPU of
+    the same process must work like the first."""
+    torch = torch_cuda
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two visible GPUs")
+    logits, params = workloads.config1_row(pkg.ROW_PARAMS_DTYPE, rows=8, vocab=60000, seed=3)
+    params["top_k"][:] = 600                                      # the large-buffer instantiation
+    uniforms = np.array([pkg.philox_uniform(p["seed"], p["row_id"], p["step"]) for p in params], dtype=np.float32)
+    want = checker.sample_batch(logits, params["temperature"], params["top_k"], params["top_p"], params["min_p"], uniforms)
+    for device in (0, 1):
+        with torch.cuda.device(device):
+            handle = pkg.Sampler(max_rows=8, max_vocab=60000, device=device)
+            out = handle.sample_batch(torch.from_numpy(logits).cuda(device), params)
+            torch.cuda.synchronize(device)
+            np.testing.assert_array_equal(out["token"].cpu().numpy(), want["token"])
+            wide = np.random.default_rng(device).standard_normal((4, 2048)).astype(np.float32)
+            plan = handle.router_dispatch_host(wide, 4, 2048, 8)
+            oracle = checker.expert_dispatch(wide, 4, 2048, 8)
+            np.testing.assert_array_equal(plan.route_token[:32], oracle["token"])
+            handle.close()

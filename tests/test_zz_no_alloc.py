@@ -38,10 +38,12 @@ def call_static(pkg, torch, logits, top_k, score_function, bias, normalization=1
     return code, message.value.decode(), out
 
 
-def test_static_router_matches_the_allocating_entry_point(pkg, workloads, sampler, torch_cuda):
+def test_static_router_matches_the_allocating_entry_point(pkg, workloads, sampler, checker, torch_cuda):
     torch = torch_cuda
-    # two calls in a row: a large sigmoid case, then a smaller softmax case with fewer experts
-    cases = [(4096, 256, 8, pkg.ROUTER_SIGMOID, 11), (300, 40, 6, pkg.ROUTER_SOFTMAX, 12)]
+    # calls in a row: a large sigmoid case, a smaller softmax case with fewer experts, the widest router the
+    # fixed array serves, and a call that fills it to the last route
+    cases = [(4096, 256, 8, pkg.ROUTER_SIGMOID, 11), (300, 40, 6, pkg.ROUTER_SOFTMAX, 12), (8, MAX_EXPERTS, 8, pkg.ROUTER_SIGMOID, 13),
+             (MAX_ROUTES // 16, 64, 16, pkg.ROUTER_SQRT_SOFTPLUS, 14)]
     for tokens, experts, top_k, score_function, seed in cases:
         logits_host, bias_host = workloads.config5b_router(tokens, experts, seed=seed)
         logits = torch.from_numpy(logits_host).cuda()
@@ -57,7 +59,15 @@ def test_static_router_matches_the_allocating_entry_point(pkg, workloads, sample
         assert torch.equal(got.expert_offsets, want.expert_offsets)
         assert torch.equal(got.route_token, want.route_token)
         assert torch.equal(got.route_rank, want.route_rank)
-        np.testing.assert_allclose(got.route_weight.cpu().numpy(), want.route_weight.cpu().numpy(), rtol=1e-5, atol=0)
+        # the same kernels ran on both paths: the weights agree to the bit
+        assert torch.equal(got.route_weight.view(torch.int32), want.route_weight.view(torch.int32))
+        # ... and with the CPU oracle directly
+        oracle = checker.expert_dispatch(logits_host, tokens, experts, top_k, score_function=score_function, selection_bias=bias_host)
+        total = int(oracle["batch_offset"][-1])
+        assert total == tokens * top_k == int(got.expert_offsets[experts].item())
+        np.testing.assert_array_equal(got.route_token.cpu().numpy().view(np.uint32)[:total], oracle["token"])
+        np.testing.assert_array_equal(got.route_rank.cpu().numpy().view(np.uint32)[:total], oracle["rank"])
+        np.testing.assert_allclose(got.route_weight.cpu().numpy()[:total], oracle["weight"], rtol=1e-5, atol=0)
 
 
 def test_static_router_reports_data_errors_and_recovers(pkg, torch_cuda):
