@@ -364,6 +364,25 @@ int moe_regroup_gather(moe_sampler* sampler, void* stream, const float* hidden, 
  * reference indexes its host vector unchecked. */
 int moe_regroup_gather_check(moe_sampler* sampler, void* stream, int32_t* out_of_range);
 
+/* ---- latent-attention indexer ------------------------------------------- */
+
+/* Replaces the selection at the end of select_compressed_indices
+ * (src/kernels/cpu_latent_attention.cpp:414-423): std::partial_sort of the
+ * {index, score} pairs with scored_index_precedes (:257-262: score descending,
+ * index ascending on equal scores) and the first min(top_k, count) indices in
+ * that order.  The scores themselves (:399-413) are the attention kernels'
+ * business and are taken as input.
+ *
+ * scores      device, [rows x row_stride] fp32, count <= row_stride entries used per row
+ * out_index   device, [rows x top_k]: the selected indices in rank order,
+ *             0xFFFFFFFF in the slots beyond min(top_k, count)
+ * out_score   device, [rows x top_k] or NULL: the scores of those indices
+ * top_k <= MOE_INDEXER_TOPK_MAX.  NaN scores, for which the reference's order
+ * is unspecified, rank last.  Asynchronous on `stream`; allocates nothing. */
+#define MOE_INDEXER_TOPK_MAX 8192u
+int moe_indexer_topk(moe_sampler* sampler, void* stream, const float* scores, uint32_t rows, uint32_t count, size_t row_stride,
+                     uint32_t top_k, uint32_t* out_index, float* out_score);
+
 #ifdef __cplusplus
 }
 #endif

@@ -59,6 +59,7 @@ EXPORTED_SYMBOLS = [
     "moe_sample_local_candidates", "moe_sample_merge_candidates", "moe_router_dispatch", "moe_router_status_message",
     "moe_router_status_error_code", "moe_router_check_options", "moe_router_dispatch_host", "moe_regroup_gather",
     "moe_router_dispatch_static", "moe_sampler_set_overlap", "moe_sample_tokens", "moe_regroup_gather_check",
+    "moe_indexer_topk",
 ]
 
 _library = None
@@ -110,6 +111,7 @@ def library() -> C.CDLL:
     lib.moe_regroup_gather.argtypes = [vp, vp, vp, u32, u32, vp, u32, vp]
     lib.moe_sample_tokens.argtypes = [vp, vp, vp, C.c_int, u32, u32, sz, vp, u64, vp, vp, vp]
     lib.moe_regroup_gather_check.argtypes = [vp, vp, C.POINTER(i32)]
+    lib.moe_indexer_topk.argtypes = [vp, vp, vp, u32, u32, sz, u32, vp, vp]
     lib.moe_router_dispatch_static.argtypes = [vp, vp, u32, C.POINTER(RouterOptions), vp, vp, vp, vp, vp, C.c_char_p, sz]
     _library = lib
     return lib
@@ -428,6 +430,19 @@ class Sampler:
         self._check(self._lib.moe_regroup_gather(self._handle, C.c_void_p(stream_handle), _dev_ptr(hidden), token_count, columns,
                                                  _dev_ptr(route_token), routes, _dev_ptr(gathered)))
         return gathered
+
+    def indexer_topk(self, scores, top_k, count=None, with_scores=False, stream=None):
+        """moe_indexer_topk: scores CUDA float32 [rows, row_stride] -> int32 tensor [rows, top_k] of indices in rank order
+        (score descending, index ascending on ties; -1 beyond min(top_k, count)), and their scores when asked."""
+        import torch
+        rows, row_stride = scores.shape
+        count = row_stride if count is None else count
+        indices = torch.empty((rows, top_k), dtype=torch.int32, device=scores.device)
+        values = torch.empty((rows, top_k), dtype=torch.float32, device=scores.device) if with_scores else None
+        stream_handle = torch.cuda.current_stream(scores.device).cuda_stream if stream is None else stream
+        self._check(self._lib.moe_indexer_topk(self._handle, C.c_void_p(stream_handle), _dev_ptr(scores), rows, int(count), scores.stride(0), int(top_k),
+                                               _dev_ptr(indices), _dev_ptr(values)))
+        return (indices, values) if with_scores else indices
 
     def regroup_gather_check(self, stream=None) -> bool:
         """True when a regroup_gather since the last check met a token index outside the hidden matrix (synchronises)."""

@@ -906,6 +906,24 @@ int moe_regroup_gather(moe_sampler* sampler, void* stream_handle, const float* h
     return MOE_STATUS_OK;
 }
 
+int moe_indexer_topk(moe_sampler* sampler, void* stream_handle, const float* scores, uint32_t rows, uint32_t count, size_t row_stride, uint32_t top_k,
+                     uint32_t* out_index, float* out_score)
+{
+    if (sampler == nullptr)
+        return MOE_STATUS_INVALID_ARGUMENT;
+    if (top_k == 0 || top_k > MOE_INDEXER_TOPK_MAX)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "indexer Top-K needs 0 < top_k <= MOE_INDEXER_TOPK_MAX");
+    if (row_stride < count)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "row_stride is smaller than count");
+    if (rows == 0)
+        return MOE_STATUS_OK;
+    if (scores == nullptr || out_index == nullptr)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "scores and out_index must not be null");
+    DeviceGuard guard(sampler->device);
+    MOE_CUDA_CHECK(sampler, launch_indexer_topk(scores, rows, count, row_stride, top_k, out_index, out_score, static_cast<cudaStream_t>(stream_handle)));
+    return MOE_STATUS_OK;
+}
+
 int moe_regroup_gather_check(moe_sampler* sampler, void* stream_handle, int32_t* out_of_range)
 {
     if (sampler == nullptr || out_of_range == nullptr)

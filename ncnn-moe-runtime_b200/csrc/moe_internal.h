@@ -189,6 +189,11 @@ cudaError_t opt_in_shared(SharedOptIn& state, Kernel kernel, size_t shared_bytes
     return status;
 }
 
+// Stable Top-K of every row of `scores` (score descending, index ascending): out_index [rows x top_k] in that
+// order, 0xFFFFFFFF beyond min(top_k, count); out_score may be null.  top_k <= MOE_INDEXER_TOPK_MAX.
+cudaError_t launch_indexer_topk(const float* scores, uint32_t rows, uint32_t count, size_t row_stride, uint32_t top_k, uint32_t* out_index,
+                                float* out_score, cudaStream_t stream);
+
 uint32_t choose_splits(uint32_t rows, uint32_t vocab, int dtype, int sm_count, uint32_t slice_slots, bool large_top_k, bool overlapped);
 
 } // namespace moe

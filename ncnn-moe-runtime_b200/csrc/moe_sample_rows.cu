@@ -1744,7 +1744,6 @@ __global__ void __launch_bounds__(kThreads, 2) merge_candidates_kernel(const uin
             s.count = local_count + s.sel.out_count;
         __syncthreads();
     }
-    flush_buffer(c);
     if (p.temperature == 0.0f)
     {
         // greedy over the merged candidates: best finite record (session.cpp:404-424)
@@ -1758,8 +1757,8 @@ __global__ void __launch_bounds__(kThreads, 2) merge_candidates_kernel(const uin
         __syncthreads();
         c.mode = kGreedy;
         c.k = 1;
-        flush_buffer(c);
     }
+    reduce_buffer(c, true); // the k best of the union, in rank order (one block-wide sort for up to 512 candidates)
     finish_row_block(a, s, c, p, row, nullptr, nullptr);
 }
 

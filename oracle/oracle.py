@@ -127,6 +127,18 @@ class Oracle:
         self.lib.oracle_topk_order(_ptr(logits, C.c_float), logits.size, count, _ptr(ids, C.c_int32))
         return ids
 
+    def indexer_topk(self, scores, top_k):
+        """Latent-attention indexer selection (cpu_latent_attention.cpp:414-423): indices of the top_k scores, score
+        descending, index ascending on ties.  The reference's own function is a file-static that cannot be linked
+        from outside its translation unit, so both oracles answer this with the port's restatement."""
+        lib = port().lib
+        lib.oracle_indexer_topk.argtypes = [C.POINTER(C.c_float), C.c_size_t, C.c_size_t, C.POINTER(C.c_uint32)]
+        lib.oracle_indexer_topk.restype = None
+        scores = np.ascontiguousarray(scores, dtype=np.float32)
+        selected = np.empty(min(int(top_k), scores.size), dtype=np.uint32)
+        lib.oracle_indexer_topk(_ptr(scores, C.c_float), scores.size, int(top_k), _ptr(selected, C.c_uint32))
+        return selected
+
     def sample_batch(self, logits, temperature, top_k, top_p, min_p, uniforms, threads=None):
         """logits: [rows, vocab] float32, or uint16 holding bf16 bit patterns.
 

@@ -644,4 +644,26 @@ int oracle_expert_dispatch(int /*use_dispatch_into*/, const float* router_logits
     return kOk;
 }
 
+// The selection of src/kernels/cpu_latent_attention.cpp:414-423: {index, score}
+// pairs ordered by scored_index_precedes (:257-262) with std::partial_sort, the
+// first min(top_k, count) indices returned.  (The reference function is a
+// file-static of that translation unit; the statement here is line for line.)
+void oracle_indexer_topk(const float* scores, size_t count, size_t top_k, uint32_t* selected_indices)
+{
+    struct ScoredIndex
+    {
+        uint32_t index;
+        float score;
+    };
+    std::vector<ScoredIndex> scored(count);
+    for (uint32_t index = 0; index < count; ++index)
+        scored[index] = {index, scores[index]};
+    const size_t selected_count = std::min(top_k, count);
+    std::partial_sort(scored.begin(), scored.begin() + selected_count, scored.end(), [](const ScoredIndex& left, const ScoredIndex& right) {
+        return left.score > right.score || (left.score == right.score && left.index < right.index);
+    });
+    for (size_t index = 0; index < selected_count; ++index)
+        selected_indices[index] = scored[index].index;
+}
+
 } // extern "C"

@@ -211,3 +211,15 @@ def test_port_speculative_matches_compiled_reference(port, oracle_module):
                (b["status"], b["message"], b["accepted"], b["next_token"], b["uniforms_used"])
         np.testing.assert_array_equal(bits(a["accepted_probability"]), bits(b["accepted_probability"]))
         assert bits(np.array([a["next_probability"]], np.float32))[0] == bits(np.array([b["next_probability"]], np.float32))[0]
+
+
+def test_indexer_selection_orders_by_score_then_index(checker):
+    # scored_index_precedes (cpu_latent_attention.cpp:257-262): score descending, index ascending on equality
+    scores = np.array([1, 3, 3, 2, 5, 3, -0.0, 0.0], dtype=np.float32)
+    assert checker.indexer_topk(scores, 4).tolist() == [4, 1, 2, 5]
+    assert checker.indexer_topk(scores, 8).tolist() == [4, 1, 2, 5, 3, 0, 6, 7]
+    assert checker.indexer_topk(scores, 100).tolist() == [4, 1, 2, 5, 3, 0, 6, 7]
+    rng = np.random.default_rng(0)
+    values = rng.standard_normal(5000).astype(np.float32)
+    want = np.lexsort((np.arange(values.size), -values))[:300]
+    np.testing.assert_array_equal(checker.indexer_topk(values, 300), want.astype(np.uint32))
