@@ -17,6 +17,7 @@
 #include "moe_epilogue.cuh"
 #include "moe_internal.h"
 #include "moe_seqscan.cuh"
+#include "moe_seqruns.cuh"
 
 #ifdef MOE_PHASE_TIMERS
 // Debug builds only: cycles per phase of the exact kernel, summed over rows.
@@ -57,6 +58,11 @@ constexpr int kSeqItems = 8; // elements per thread and scan step of the sequent
 struct ExactShared
 {
     SeqShared<1024> seq;
+    SeqRunsShared<1024> seq_runs;
+    uint32_t run_total;     // value-histogram path: distinct live values of the row
+    uint32_t window_total;  // ... and finite logits inside the live window
+    uint32_t chosen_warp;   // ... warp whose segment holds the drawn occurrence
+    uint32_t chosen_index;
     uint32_t first_fail; // Min-P: first rank whose probability is below the floor
     uint32_t warp_hist[kExactWarps][256];
     uint32_t digit_total[256];
@@ -537,6 +543,357 @@ __device__ RowOutcome finish_row_exact_block(const uint64_t* records, uint32_t p
     return out;
 }
 
+// ---- bf16 rows: a value histogram instead of a sort ---------------------------------
+//
+// A bf16 row holds at most 65536 distinct logits, a few thousand inside the
+// window that can matter, so its rank order is a short list of (value, count)
+// runs: candidates of equal value are adjacent, in index order.  The sums are
+// replayed over the runs (moe_seqruns.cuh), and the drawn rank (run r, copy j)
+// is the j-th lowest index that carries value r, found by one more pass.
+// Everything below the window of the row maximum is numerically dead
+// (live_window_floor); where the outcome would reach into it, or the caller
+// wants per-candidate lists, the sort path takes the row.
+
+constexpr uint32_t kHistogramBins = 40960;        // 160 KiB of dynamic shared memory
+constexpr uint32_t kRunsPerThread = 6;            // runs a thread handles in the sums
+constexpr uint32_t kMaxRuns = kExactThreads * kRunsPerThread;
+
+// Lowest logit that can still change one of the running sums: exp((v - peak) / T)
+// below 2^-26 is absorbed by every accumulator (each starts at the head
+// candidate's addend).  0.1 T of slack plus 2^-20 of the peak's magnitude cover
+// the roundings of the reference's own v / T - peak / T.
+__device__ __forceinline__ float live_window_floor(float peak_logit, float temperature)
+{
+    return __fsub_rn(__fsub_rn(peak_logit, __fmul_rn(18.2f, temperature)), __fmul_rn(9.5367431640625e-07f, fabsf(peak_logit)));
+}
+
+// Calls visit(pattern) for every bf16 logit of the row, in no particular order:
+// 16-byte loads (eight logits) while the row is 16-byte aligned, two in flight per thread.
+template<typename Visit>
+__device__ __forceinline__ void for_each_bf16(const uint16_t* bits, uint32_t vocab, Visit visit)
+{
+    const uint32_t tid = threadIdx.x;
+    if ((reinterpret_cast<uintptr_t>(bits) & 15u) != 0u)
+    {
+        for (uint32_t i = tid; i < vocab; i += kExactThreads)
+            visit(bits[i]);
+        return;
+    }
+    const uint4* vectors = reinterpret_cast<const uint4*>(bits);
+    const uint32_t vector_count = vocab / 8u;
+    const auto visit_vector = [&](const uint4& v) {
+        visit(static_cast<uint16_t>(v.x)); visit(static_cast<uint16_t>(v.x >> 16));
+        visit(static_cast<uint16_t>(v.y)); visit(static_cast<uint16_t>(v.y >> 16));
+        visit(static_cast<uint16_t>(v.z)); visit(static_cast<uint16_t>(v.z >> 16));
+        visit(static_cast<uint16_t>(v.w)); visit(static_cast<uint16_t>(v.w >> 16));
+    };
+    uint32_t index = tid;
+    for (; index + kExactThreads < vector_count; index += 2u * kExactThreads)
+    {
+        const uint4 first = vectors[index];
+        const uint4 second = vectors[index + kExactThreads];
+        visit_vector(first);
+        visit_vector(second);
+    }
+    if (index < vector_count)
+        visit_vector(vectors[index]);
+    for (uint32_t i = vector_count * 8u + tid; i < vocab; i += kExactThreads)
+        visit(bits[i]);
+}
+
+// Returns false when the row has to go through the sort path; `out` is only valid on true.
+__device__ bool exact_row_bf16_runs(const SampleArgs& a, uint32_t row, const moe_row_params& p, uint32_t* hist, uint32_t* scratch, uint32_t scratch_words,
+                                    ExactShared& sh, RowOutcome& out)
+{
+    const uint32_t tid = threadIdx.x;
+    const uint32_t lane = tid & 31u;
+    const uint32_t warp = tid >> 5;
+    const uint16_t* bits = reinterpret_cast<const uint16_t*>(a.logits) + static_cast<size_t>(row) * a.row_stride;
+    const uint32_t vocab = a.vocab;
+    out = RowOutcome{MOE_ROW_OK, -1, 0.0f, 0u, false};
+    if (a.kept_count != nullptr || (a.topk_index != nullptr && p.top_k > 0 && p.top_k <= MOE_SAMPLER_TOPK_FAST_MAX))
+        return false; // per-candidate lists need the materialised order
+    if (scratch_words < 4u * kMaxRuns)
+        return false;
+
+    // ---- pass 1: maximum, finite count, +inf --------------------------------------------
+    if (tid == 0)
+    {
+        sh.flag_pos_inf = 0;
+        sh.finite_total = 0;
+        sh.max_key = 0;
+        sh.run_total = 0;
+        sh.window_total = 0;
+    }
+    __syncthreads();
+    uint32_t finite = 0, max_key = 0;
+    bool saw_pos_inf = false;
+    for_each_bf16(bits, vocab, [&](uint16_t pattern) {
+        const float v = __uint_as_float(static_cast<uint32_t>(pattern) << 16);
+        saw_pos_inf |= (v == INFINITY);
+        if (fabsf(v) < INFINITY)
+        {
+            max_key = max(max_key, ordered_key(v));
+            ++finite;
+        }
+    });
+    finite = __reduce_add_sync(kFullMask, finite);
+    max_key = __reduce_max_sync(kFullMask, max_key);
+    const bool warp_saw_pos_inf = __any_sync(kFullMask, saw_pos_inf);
+    if (lane == 0)
+    {
+        atomicAdd(&sh.finite_total, finite);
+        atomicMax(&sh.max_key, max_key);
+        if (warp_saw_pos_inf)
+            sh.flag_pos_inf = 1;
+    }
+    __syncthreads();
+    const uint32_t finite_total = sh.finite_total;
+    if (sh.flag_pos_inf != 0 || finite_total == 0)
+    {
+        out.status = MOE_ROW_NO_FINITE_LOGIT; // session.cpp:84-85,399
+        return true;
+    }
+    const uint32_t top_bin_key = sh.max_key >> 16; // bf16 values: the low half of the ordered key is constant per sign
+    const float peak_logit = key_to_float(sh.max_key);
+    const float floor_value = live_window_floor(peak_logit, p.temperature);
+    // the bin of the floor itself is kept whole: a superset of the live window
+    const uint32_t floor_bin_key = (floor_value == floor_value && floor_value > -INFINITY) ? (ordered_key(floor_value) >> 16) : (kKeyNegInf >> 16) + 1u;
+    if (floor_bin_key > top_bin_key)
+        return false;
+    const uint32_t bins = top_bin_key - floor_bin_key + 1u;
+    if (bins > kHistogramBins)
+        return false;
+
+    // ---- pass 2: histogram over the values of the window, bin 0 = the maximum ------------------
+    for (uint32_t b = tid; b < bins; b += kExactThreads)
+        hist[b] = 0;
+    __syncthreads();
+    uint32_t inside = 0;
+    for_each_bf16(bits, vocab, [&](uint16_t pattern) {
+        const float v = __uint_as_float(static_cast<uint32_t>(pattern) << 16);
+        if (fabsf(v) < INFINITY)
+        {
+            const uint32_t bin_key = ordered_key(v) >> 16;
+            if (bin_key >= floor_bin_key)
+            {
+                atomicAdd(&hist[top_bin_key - bin_key], 1u);
+                ++inside;
+            }
+        }
+    });
+    inside = __reduce_add_sync(kFullMask, inside);
+    if (lane == 0 && inside != 0)
+        atomicAdd(&sh.window_total, inside);
+    __syncthreads();
+    const uint32_t window_total = sh.window_total;
+
+    // ---- runs: the non-empty bins in rank order, with the number of candidates before each -------
+    float* run_value = reinterpret_cast<float*>(scratch);       // addend of the run (numerator, probability, ...)
+    uint32_t* run_count = scratch + kMaxRuns;
+    uint32_t* run_cum = scratch + 2u * kMaxRuns;
+    uint32_t* run_key = scratch + 3u * kMaxRuns;                 // ordered key of the run's logit
+    const uint32_t bins_per_thread = (bins + kExactThreads - 1u) / kExactThreads;
+    const uint32_t my_first_bin = min(bins, tid * bins_per_thread);
+    const uint32_t my_last_bin = min(bins, my_first_bin + bins_per_thread);
+    uint32_t my_runs = 0, my_elements = 0;
+    for (uint32_t b = my_first_bin; b < my_last_bin; ++b)
+    {
+        const uint32_t c = hist[b];
+        my_runs += c != 0 ? 1u : 0u;
+        my_elements += c;
+    }
+    // block-wide exclusive scan of (runs, elements)
+    uint32_t scan_runs = my_runs, scan_elements = my_elements;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1)
+    {
+        const uint32_t r = __shfl_up_sync(kFullMask, scan_runs, offset);
+        const uint32_t e = __shfl_up_sync(kFullMask, scan_elements, offset);
+        if (lane >= static_cast<uint32_t>(offset))
+        {
+            scan_runs += r;
+            scan_elements += e;
+        }
+    }
+    if (lane == 31)
+    {
+        sh.warp_count[warp] = scan_runs;
+        sh.warp_or[warp] = scan_elements;
+    }
+    __syncthreads();
+    uint32_t runs_before = scan_runs - my_runs, elements_before = scan_elements - my_elements;
+    for (uint32_t w = 0; w < warp; ++w)
+    {
+        runs_before += sh.warp_count[w];
+        elements_before += sh.warp_or[w];
+    }
+    if (tid == kExactThreads - 1)
+        sh.run_total = runs_before + my_runs;
+    __syncthreads();
+    const uint32_t runs = sh.run_total;
+    if (runs > kMaxRuns)
+        return false;
+    for (uint32_t b = my_first_bin; b < my_last_bin; ++b)
+    {
+        const uint32_t c = hist[b];
+        if (c != 0)
+        {
+            run_count[runs_before] = c;
+            run_cum[runs_before] = elements_before;
+            // ordered key of the bf16 value of this bin: its low half is all zeros for a
+            // non-negative value and all ones for a negative one (the complemented zero bits)
+            const uint32_t bin_key = top_bin_key - b;
+            run_key[runs_before] = (bin_key << 16) | ((bin_key & 0x8000u) ? 0u : 0xFFFFu);
+            ++runs_before;
+            elements_before += c;
+        }
+    }
+    __syncthreads();
+
+    // ---- the arithmetic of session.cpp:89-136,429-442 over the runs --------------------------
+    // Top-K (only top_k > MOE_SAMPLER_TOPK_FAST_MAX reaches this kernel) shortens the list
+    const uint32_t listed = (p.top_k > 0 && p.top_k < finite_total) ? p.top_k : finite_total;
+    const uint32_t have = min(window_total, listed); // candidates whose runs exist
+    const float peak = __fdiv_rn(peak_logit, p.temperature);
+    for (uint32_t r = tid; r < runs; r += kExactThreads)
+        run_value[r] = exact_expf(scaled_offset(key_to_float(run_key[r]), p.temperature, peak));
+    __syncthreads();
+    const SeqRunsResult normaliser = block_sequential_sum_runs<kExactThreads, kRunsPerThread>(run_value, run_count, run_cum, runs, have, kSeqSumOnly, 0.0f, sh.seq_runs);
+    if (normaliser.unsupported)
+        return false;
+    const float total = normaliser.acc;
+    if (!(total - total == 0.0f) || total <= 0.0f)
+    {
+        out.status = MOE_ROW_INVALID_DISTRIBUTION; // session.cpp:102-103
+        return true;
+    }
+    for (uint32_t r = tid; r < runs; r += kExactThreads)
+        run_value[r] = __fdiv_rn(run_value[r], total);
+    if (tid == 0)
+        sh.first_fail = runs;
+    __syncthreads();
+    // Min-P: probabilities do not increase, so the survivors are a prefix of the runs
+    uint32_t allowed = listed;
+    if (p.min_p > 0.0f)
+    {
+        const float floor_probability = __fmul_rn(run_value[0], p.min_p);
+        uint32_t mine = runs;
+        for (uint32_t r = tid; r < runs; r += kExactThreads)
+            if (!(run_value[r] >= floor_probability))
+            {
+                mine = r;
+                break;
+            }
+        if (mine < runs)
+            atomicMin(&sh.first_fail, mine);
+        __syncthreads();
+        const uint32_t first_fail = sh.first_fail;
+        __syncthreads();
+        if (first_fail < runs)
+            allowed = min(allowed, run_cum[first_fail]);
+        else if (have < listed)
+            return false; // the prefix may go on below the window
+    }
+    // Top-P: first prefix whose running sum reaches top_p; never reached: the whole list stays
+    const SeqRunsResult nucleus = block_sequential_sum_runs<kExactThreads, kRunsPerThread>(run_value, run_count, run_cum, runs, min(allowed, have), kSeqReachBound, p.top_p, sh.seq_runs);
+    if (nucleus.unsupported)
+        return false;
+    const uint32_t kept = nucleus.stopped ? nucleus.taken : allowed;
+    // the renormaliser (session.cpp:130-132) repeats the adds of the Top-P loop over the same prefix from the same zero
+    const float kept_total = nucleus.acc;
+    uint32_t chosen_run = 0;
+    uint32_t occurrence = 0; // 0-based among the indices carrying the chosen value
+    if (kept == 1)
+    {
+        // session.cpp:429-430: no uniform drawn; the head candidate is the lowest index of the maximum
+        out.probability = 1.0f;
+    }
+    else
+    {
+        out.flags |= MOE_ROW_FLAG_USED_UNIFORM;
+        const uint32_t kept_have = min(kept, have);
+        for (uint32_t r = tid; r < runs; r += kExactThreads)
+            run_value[r] = __fdiv_rn(run_value[r], kept_total);
+        __syncthreads();
+        const float uniform = philox_uniform(p.seed, p.row_id, p.step + a.step_offset);
+        const SeqRunsResult draw = block_sequential_sum_runs<kExactThreads, kRunsPerThread>(run_value, run_count, run_cum, runs, kept_have, kSeqExceedBound, uniform, sh.seq_runs);
+        if (draw.unsupported)
+            return false;
+        uint32_t chosen_rank;
+        if (draw.stopped)
+            chosen_rank = draw.taken - 1u;
+        else if (kept <= have)
+            chosen_rank = kept - 1u; // session.cpp:441-442: the last candidate if the sum never passes the uniform
+        else
+            return false; // the last candidate of the list lies below the window
+        // run of that rank: the last run that starts at or before it
+        if (tid == 0)
+            sh.first_fail = 0;
+        __syncthreads();
+        {
+            uint32_t mine = 0;
+            for (uint32_t r = tid; r < runs; r += kExactThreads)
+                if (run_cum[r] <= chosen_rank)
+                    mine = max(mine, r);
+            mine = __reduce_max_sync(kFullMask, mine);
+            if (lane == 0)
+                atomicMax(&sh.first_fail, mine);
+        }
+        __syncthreads();
+        chosen_run = sh.first_fail;
+        occurrence = chosen_rank - run_cum[chosen_run];
+        out.probability = run_value[chosen_run];
+    }
+    const float chosen_value = key_to_float(run_key[chosen_run]);
+    const uint16_t wanted = static_cast<uint16_t>(__float_as_uint(chosen_value) >> 16);
+    __syncthreads();
+
+    // ---- the occurrence-th lowest index that carries the chosen value ------------------------
+    // each thread owns a contiguous range of the row, so that "lowest" is a prefix count over threads
+    const uint32_t range = (vocab + kExactThreads - 1u) / kExactThreads;
+    const uint32_t begin = min(vocab, tid * range);
+    const uint32_t end = min(vocab, begin + range);
+    const auto matches = [&](uint16_t pattern) -> bool { return pattern == wanted || (((pattern | wanted) & 0x7FFFu) == 0u); };
+    uint32_t in_range = 0;
+    for (uint32_t i = begin; i < end; ++i)
+        in_range += matches(bits[i]) ? 1u : 0u;
+    uint32_t scan = in_range;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1)
+    {
+        const uint32_t other = __shfl_up_sync(kFullMask, scan, offset);
+        if (lane >= static_cast<uint32_t>(offset))
+            scan += other;
+    }
+    if (lane == 31)
+        sh.warp_count[warp] = scan;
+    if (tid == 0)
+        sh.chosen_index = 0xFFFFFFFFu;
+    __syncthreads();
+    uint32_t before = scan - in_range;
+    for (uint32_t w = 0; w < warp; ++w)
+        before += sh.warp_count[w];
+    if (occurrence >= before && occurrence < before + in_range)
+    {
+        uint32_t seen = before;
+        for (uint32_t i = begin; i < end; ++i)
+            if (matches(bits[i]))
+            {
+                if (seen == occurrence)
+                {
+                    sh.chosen_index = i;
+                    break;
+                }
+                ++seen;
+            }
+    }
+    __syncthreads();
+    out.token = static_cast<int32_t>(sh.chosen_index);
+    __syncthreads();
+    return out.token >= 0;
+}
+
 template<typename T>
 __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys, uint32_t* slot_index, uint32_t slot_stride, ExactShared& sh)
 {
@@ -553,17 +910,37 @@ __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys
     MOE_EXACT_BEGIN();
     // rows that list their Top-K ids need every rank up to top_k: no filter for them
     const bool lists = a.topk_index != nullptr && p.top_k > 0 && p.top_k <= MOE_SAMPLER_TOPK_FAST_MAX;
-    uint32_t floor_key = dead_tail_floor<T>(row_pointer, a.vocab, p.temperature, sh);
-    const bool has_pos_inf = sh.flag_pos_inf != 0;
-    const uint32_t finite_total = sh.finite_total;
-    if (lists)
-        floor_key = 0;
-    MOE_EXACT_MARK(4);
-
     RowOutcome out{MOE_ROW_OK, -1, 0.0f, 0u, false};
     uint64_t* records = items[0];
     uint32_t n = 0;
-    if (has_pos_inf || finite_total == 0)
+    bool handled = false;
+    if constexpr (sizeof(T) == 2)
+    {
+        extern __shared__ __align__(16) uint32_t value_histogram[];
+        handled = exact_row_bf16_runs(a, row, p, value_histogram, slot_keys, 4u * slot_stride, sh, out);
+        __syncthreads();
+        if (handled && a.kept_count != nullptr && tid == 0)
+            a.kept_count[row] = 0; // unreachable today (lists go through the sort path); kept for a consistent contract
+        MOE_EXACT_MARK(6);
+    }
+    uint32_t floor_key = 0;
+    bool has_pos_inf = false;
+    uint32_t finite_total = 0;
+    if (!handled)
+    {
+        floor_key = dead_tail_floor<T>(row_pointer, a.vocab, p.temperature, sh);
+        has_pos_inf = sh.flag_pos_inf != 0;
+        finite_total = sh.finite_total;
+        if (lists)
+            floor_key = 0;
+        MOE_EXACT_MARK(4);
+    }
+
+    if (handled)
+    {
+        // finished by the value-histogram path
+    }
+    else if (has_pos_inf || finite_total == 0)
     {
         out.status = MOE_ROW_NO_FINITE_LOGIT;
         if (a.kept_count != nullptr && tid == 0)
@@ -710,9 +1087,18 @@ cudaError_t launch_sample_exact(const SampleArgs& args, const Workspace& ws, cud
         return cudaSuccess;
     const uint32_t grid = ws.slots < args.rows ? ws.slots : args.rows;
     if (args.dtype == MOE_DTYPE_F32)
+    {
         sample_exact_kernel<float><<<grid, kExactThreads, 0, stream>>>(args, ws);
+    }
     else
-        sample_exact_kernel<__nv_bfloat16><<<grid, kExactThreads, 0, stream>>>(args, ws);
+    {
+        // the value histogram of the bf16 path lives in dynamic shared memory
+        const size_t shared_bytes = sizeof(uint32_t) * kHistogramBins;
+        static SharedOptIn opt_in;
+        if (cudaError_t status = opt_in_shared(opt_in, sample_exact_kernel<__nv_bfloat16>, shared_bytes))
+            return status;
+        sample_exact_kernel<__nv_bfloat16><<<grid, kExactThreads, shared_bytes, stream>>>(args, ws);
+    }
     return cudaGetLastError();
 }
 

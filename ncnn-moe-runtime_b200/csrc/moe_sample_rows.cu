@@ -1,23 +1,25 @@
 // Streaming sampler kernel: one pass over each logit row.
 //
-// A row is cut into `splits` contiguous slices, one CTA each.  A CTA streams its
-// slice through a shared-memory ring that the copy engine fills with bulk
+// A row is cut into `splits` contiguous slices, one CTA each (one slice per row
+// once there are about as many rows as resident CTAs).  A CTA streams its slice
+// through a shared-memory ring that the copy engine fills with bulk
 // asynchronous copies (cp.async.bulk + mbarrier, no cluster forms), reads it
 // back with 128-bit shared loads and keeps only the records that can still
 // matter:
-//   greedy rows      the best finite logit so far              (session.cpp:404-424)
-//   Top-K rows       the k best records so far                 (session.cpp:80-87)
+//   greedy rows      the best finite logit                     (session.cpp:404-424)
+//   Top-K rows       the logits at or above a threshold sampled from the first
+//                    chunks, at least k of them                (session.cpp:80-87)
 //   full-vocab rows  the records whose softmax numerator could be >= 2^-26
 //                    relative to the running maximum ("live" records)
-// A record passes a single float compare against a threshold held in a register;
-// the threshold is tightened by a shared-memory radix select (Top-K) or by
-// re-testing against the running maximum (live) whenever the buffer fills.
-// After the stream a CTA publishes its survivors to a small global scratch slot
-// and counts itself in; nobody waits.  The CTA that arrives last for a row
-// gathers the row's slots, selects the k best (or the live set), sorts them into
-// the reference rank order, and one warp replays the reference's sequential
-// softmax / Min-P / Top-P / renormalise / inverse-CDF arithmetic on them
-// (moe_epilogue.cuh) while the other CTAs of the SM keep streaming other rows.
+// A chunk is filtered with one packed maximum per 16-byte vector, one compare
+// and one warp vote; vectors that reach the threshold are queued per warp and
+// unpacked one per lane.  After the stream the survivors are ordered (shuffle
+// network per warp + rank by binary search), and one warp replays the
+// reference's sequential softmax / Min-P / Top-P / renormalise / inverse-CDF
+// arithmetic on them (moe_epilogue.cuh) after all threads have computed the
+// softmax numerators.  When rows are sliced, a CTA publishes its survivors to a
+// small global scratch slot and counts itself in; nobody waits, and the CTA that
+// arrives last for a row gathers the row's slots and finishes it.
 //
 // Rows whose live set does not fit on chip, and draws that fall through to a
 // numerically dead candidate, are appended to a list that the exact kernel

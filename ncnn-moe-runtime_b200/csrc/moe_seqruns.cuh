@@ -1,0 +1,296 @@
+// Block-parallel, bit-exact replay of a left-to-right fp32 accumulation over a
+// sequence given as RUNS of equal addends:
+//     acc = 0; for every run r in order: repeat count[r] times: acc = acc + x[r]
+// with x non-increasing and non-negative — the sums of the reference sampler
+// (src/engine/session.cpp:92-101,119-134,434-440) over a row of bf16 logits,
+// where equal logits are equal addends and a row holds a few thousand distinct
+// values instead of a hundred thousand candidates.
+//
+// Same arithmetic as moe_seqscan.cuh: inside one binade of the accumulator an
+// addend is an integer step that depends at most on the accumulator's parity
+// (exact ties of the rounding), a step is a pair (even start, odd start) and
+// pairs compose associatively.  A run of c equal addends is again such a pair,
+// in closed form: after a tie step the accumulator's integer is even and the
+// tie step from an even integer is even, so every copy after the first takes
+// the even-start step d0:
+//     steps(c, parity) = (parity ? d1 : d0) + (c - 1) * d0
+// (for an addend that is no tie d0 = d1 and this is c * d0).  The place inside a
+// run where the accumulator leaves its binade or meets the stop condition is
+// found by bisection on the copy count, because the accumulator only grows.
+#pragma once
+
+#include "moe_seqscan.cuh"
+
+namespace moe {
+
+struct SeqRunsResult
+{
+    float acc;       // accumulator after the last addend taken
+    uint32_t taken;  // addends (copies, not runs) taken, the stopping one included
+    bool stopped;    // the stop condition fired
+    bool unsupported; // the accumulator left the range this replay handles: the caller must use another path
+};
+
+template<int kThreads>
+struct SeqRunsShared
+{
+    uint32_t warp_pair[kThreads / 32][2];
+    uint32_t first_event; // smallest run offset in the chunk with a stop or a carry
+    uint32_t event_copies; // copies of that run consumed, the event's copy included
+    float acc;
+    uint32_t stopped;
+};
+
+// integer steps of `copies` equal addends (pair d0 / d1) from an accumulator integer of the given parity
+__device__ __forceinline__ unsigned long long seq_run_steps(uint32_t d0, uint32_t d1, uint32_t copies, uint32_t parity)
+{
+    if (copies == 0)
+        return 0ull;
+    return static_cast<unsigned long long>(parity ? d1 : d0) + static_cast<unsigned long long>(copies - 1u) * d0;
+}
+
+__device__ __forceinline__ uint32_t seq_clamp64(unsigned long long v)
+{
+    return v < kSeqSaturate ? static_cast<uint32_t>(v) : kSeqSaturate;
+}
+
+// x[r], count[r], cum[r] (= addends before run r) for r < runs, readable by every
+// thread.  Only the first `limit` addends of the sequence take part.  All
+// threads of the block call this with the same arguments; ends with a barrier.
+template<int kThreads, int kItems>
+__device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, const uint32_t* count, const uint32_t* cum, uint32_t runs, uint32_t limit,
+                                                                SeqStop stop, float bound, SeqRunsShared<kThreads>& sh)
+{
+    const uint32_t tid = threadIdx.x;
+    const uint32_t lane = tid & 31u;
+    const uint32_t warp = tid >> 5;
+    SeqRunsResult result{0.0f, 0u, false, false};
+    if (runs == 0 || limit == 0)
+        return result;
+    // copies of run r that take part
+    const auto copies_of = [&](uint32_t r) -> uint32_t {
+        const uint32_t before = cum[r];
+        if (before >= limit)
+            return 0u;
+        return min(count[r], limit - before);
+    };
+    // 0 + x[0] is exact
+    float acc = x[0];
+    uint32_t run = 0;     // current run
+    uint32_t done = 1;    // copies of it already added
+    if ((stop == kSeqReachBound && acc >= bound) || (stop == kSeqExceedBound && bound < acc))
+        return SeqRunsResult{acc, 1u, true, false};
+    for (;;)
+    {
+        while (run < runs && done >= copies_of(run))
+        {
+            ++run;
+            done = 0;
+        }
+        if (run >= runs || cum[run] >= limit)
+            break;
+        const uint32_t acc_bits = __float_as_uint(acc);
+        const int acc_biased = static_cast<int>((acc_bits >> 23) & 0xFFu);
+        if (acc_biased <= 23 || acc_biased == 0xFF)
+        {
+            result.unsupported = true; // never on the sampler's sums (first addend >= 1 / vocab)
+            return result;
+        }
+        const uint32_t start_integer = (acc_bits & 0x7FFFFFu) | 0x800000u;
+        const float unit = __uint_as_float(static_cast<uint32_t>(acc_biased - 23) << 23);
+        const float inverse_unit = __uint_as_float(static_cast<uint32_t>(277 - acc_biased) << 23);
+        // the sequence does not increase and the accumulator does not decrease: once the next
+        // addend is below half a unit nothing changes any more and no stop can fire
+        if (x[run] < 0.5f * unit)
+            break;
+        const uint32_t chunk = min(static_cast<uint32_t>(kThreads * kItems), runs - run);
+
+        // my kItems consecutive runs of the chunk
+        float mine[kItems];
+        uint32_t copies[kItems];
+        uint32_t t0 = 0, t1 = 0;
+        const uint32_t first = tid * kItems;
+#pragma unroll
+        for (int j = 0; j < kItems; ++j)
+        {
+            const uint32_t offset = first + j;
+            mine[j] = 0.0f;
+            copies[j] = 0;
+            if (offset < chunk)
+            {
+                mine[j] = x[run + offset];
+                copies[j] = copies_of(run + offset) - (offset == 0 ? done : 0u);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kItems; ++j)
+        {
+            uint32_t d0, d1;
+            seq_element(mine[j], inverse_unit, d0, d1);
+            const uint32_t e0 = seq_clamp64(seq_run_steps(d0, d1, copies[j], 0u));
+            const uint32_t e1 = seq_clamp64(seq_run_steps(d0, d1, copies[j], 1u));
+            if (j == 0)
+            {
+                t0 = e0;
+                t1 = e1;
+            }
+            else
+            {
+                seq_compose(t0, t1, e0, e1, t0, t1);
+            }
+        }
+        uint32_t s0 = t0, s1 = t1;
+#pragma unroll
+        for (int offset = 1; offset < 32; offset <<= 1)
+        {
+            const uint32_t p0 = __shfl_up_sync(kFullMask, s0, offset);
+            const uint32_t p1 = __shfl_up_sync(kFullMask, s1, offset);
+            if (lane >= static_cast<uint32_t>(offset))
+                seq_compose(p0, p1, s0, s1, s0, s1);
+        }
+        if (lane == 31)
+        {
+            sh.warp_pair[warp][0] = s0;
+            sh.warp_pair[warp][1] = s1;
+        }
+        if (tid == 0)
+        {
+            sh.first_event = 0xFFFFFFFFu;
+            sh.stopped = 0;
+        }
+        __syncthreads();
+        const uint32_t start_parity = start_integer & 1u;
+        uint32_t before = 0; // integer steps taken before my first run
+        {
+            constexpr uint32_t kWarps = kThreads / 32;
+            uint32_t w0 = lane < kWarps ? sh.warp_pair[lane][0] : 0u;
+            uint32_t w1 = lane < kWarps ? sh.warp_pair[lane][1] : 0u;
+#pragma unroll
+            for (int offset = 1; offset < 32; offset <<= 1)
+            {
+                const uint32_t p0 = __shfl_up_sync(kFullMask, w0, offset);
+                const uint32_t p1 = __shfl_up_sync(kFullMask, w1, offset);
+                if (lane >= static_cast<uint32_t>(offset))
+                    seq_compose(p0, p1, w0, w1, w0, w1);
+            }
+            const uint32_t prior0 = __shfl_sync(kFullMask, w0, warp == 0 ? 0 : warp - 1);
+            const uint32_t prior1 = __shfl_sync(kFullMask, w1, warp == 0 ? 0 : warp - 1);
+            uint32_t parity = start_parity;
+            if (warp > 0)
+            {
+                before = start_parity ? prior1 : prior0;
+                parity = (start_parity + before) & 1u;
+            }
+            const uint32_t x0 = __shfl_up_sync(kFullMask, s0, 1);
+            const uint32_t x1 = __shfl_up_sync(kFullMask, s1, 1);
+            if (lane > 0)
+                before = seq_clamp(before + (parity ? x1 : x0));
+        }
+        // walk my runs with the true running integer
+        uint32_t running = seq_clamp(start_integer + before);
+        uint32_t event = 0xFFFFFFFFu; // first offset of mine inside which the scan stops or leaves the binade
+#pragma unroll
+        for (int j = 0; j < kItems; ++j)
+        {
+            const uint32_t offset = first + j;
+            if (offset < chunk && event == 0xFFFFFFFFu && copies[j] != 0u)
+            {
+                uint32_t d0, d1;
+                seq_element(mine[j], inverse_unit, d0, d1);
+                const uint32_t next = seq_clamp64(running + seq_run_steps(d0, d1, copies[j], running & 1u));
+                if (running >= (1u << 24) || next >= (1u << 24))
+                {
+                    event = offset;
+                }
+                else
+                {
+                    const float value = __uint2float_rn(next) * unit; // exact
+                    if ((stop == kSeqReachBound && value >= bound) || (stop == kSeqExceedBound && bound < value))
+                        event = offset; // the accumulator only grows: the first copy that satisfies the bound is inside this run
+                    else
+                        running = next;
+                }
+            }
+        }
+        if (event != 0xFFFFFFFFu)
+            atomicMin(&sh.first_event, event);
+        __syncthreads();
+        const uint32_t first_event = sh.first_event;
+        if (first_event == 0xFFFFFFFFu)
+        {
+            // the whole chunk inside the binade, no stop: the thread that owns the last run holds the final integer
+            const uint32_t last_offset = chunk - 1;
+            if (last_offset / kItems == tid)
+                sh.acc = __uint2float_rn(running) * unit;
+            __syncthreads();
+            acc = sh.acc;
+            run += chunk;
+            done = 0;
+            __syncthreads();
+            continue;
+        }
+        if (first_event / kItems == tid)
+        {
+            // `running` is the exact integer before the event run.  Find the first copy m (1-based)
+            // after which the integer has left the binade or the bound is met.
+            const int j = static_cast<int>(first_event - first);
+            float addend = 0.0f;
+            uint32_t available = 0;
+#pragma unroll
+            for (int k = 0; k < kItems; ++k)
+                if (k == j)
+                {
+                    addend = mine[k];
+                    available = copies[k];
+                }
+            uint32_t d0, d1;
+            seq_element(addend, inverse_unit, d0, d1);
+            const uint32_t parity = running & 1u;
+            const auto is_event = [&](uint32_t m) -> bool {
+                const unsigned long long integer = running + seq_run_steps(d0, d1, m, parity);
+                if (integer >= (1ull << 24))
+                    return true;
+                const float value = __uint2float_rn(static_cast<uint32_t>(integer)) * unit;
+                return (stop == kSeqReachBound && value >= bound) || (stop == kSeqExceedBound && bound < value);
+            };
+            uint32_t lo = 1, hi = available; // is_event(available) holds
+            while (lo < hi)
+            {
+                const uint32_t mid = lo + (hi - lo) / 2u;
+                if (is_event(mid))
+                    hi = mid;
+                else
+                    lo = mid + 1u;
+            }
+            const uint32_t m = lo;
+            const unsigned long long integer_before = running + seq_run_steps(d0, d1, m - 1u, parity);
+            const unsigned long long integer_after = running + seq_run_steps(d0, d1, m, parity);
+            float value;
+            if (integer_after >= (1ull << 24))
+            {
+                // the m-th copy carries out of the binade: a real fp32 add from the exact value before it
+                const float value_before = __uint2float_rn(static_cast<uint32_t>(integer_before)) * unit;
+                value = __fadd_rn(value_before, addend);
+            }
+            else
+            {
+                value = __uint2float_rn(static_cast<uint32_t>(integer_after)) * unit;
+            }
+            sh.acc = value;
+            sh.event_copies = m;
+            sh.stopped = ((stop == kSeqReachBound && value >= bound) || (stop == kSeqExceedBound && bound < value)) ? 1u : 0u;
+        }
+        __syncthreads();
+        acc = sh.acc;
+        const bool stopped = sh.stopped != 0;
+        const uint32_t consumed = sh.event_copies;
+        done = (first_event == 0 ? done : 0u) + consumed;
+        run += first_event;
+        __syncthreads();
+        if (stopped)
+            return SeqRunsResult{acc, cum[run] + done, true, false};
+    }
+    return SeqRunsResult{acc, limit, false, false};
+}
+
+} // namespace moe

@@ -77,7 +77,11 @@ __device__ __forceinline__ void seq_element(float x, float inverse_unit, uint32_
 
 // All threads of the block call this with the same arguments; x[0..n) is
 // readable by every thread (global or shared).  Ends with a barrier.
-template<int kThreads, int kItems>
+// kSorted = false lifts the requirement that x does not increase (addends are
+// still non-negative): an addend larger than the accumulator saturates its step
+// and is handled like a binade carry, with a real add; only the early exit on
+// an absorbed tail is lost.
+template<int kThreads, int kItems, bool kSorted = true>
 __device__ __noinline__ SeqResult block_sequential_sum(const float* x, uint32_t n, SeqStop stop, float bound, SeqShared<kThreads>& sh)
 {
     const uint32_t tid = threadIdx.x;
@@ -140,7 +144,7 @@ __device__ __noinline__ SeqResult block_sequential_sum(const float* x, uint32_t 
         // The sequence does not increase and the accumulator does not decrease:
         // once the next addend is below half a unit, no later add changes the
         // accumulator (and no stop condition can fire any more).
-        if (x[position] < 0.5f * unit)
+        if (kSorted && x[position] < 0.5f * unit)
             break;
 
         // my kItems consecutive elements

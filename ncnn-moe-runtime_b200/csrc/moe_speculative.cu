@@ -15,6 +15,7 @@
 
 #include "moe_common.cuh"
 #include "moe_internal.h"
+#include "moe_seqscan.cuh"
 
 namespace moe {
 
@@ -25,6 +26,7 @@ constexpr int kVerifyWarps = kVerifyThreads / 32;
 
 struct VerifyShared
 {
+    SeqShared<kVerifyThreads> seq;
     float found[2];
     uint32_t warp_count[kVerifyWarps];
     uint32_t cursor;
@@ -164,32 +166,28 @@ __global__ void __launch_bounds__(kVerifyThreads, 1) speculative_verify_kernel(c
             __syncthreads();
         }
         const uint32_t positives = sh.cursor;
-        if (tid == 0)
+        __syncthreads();
+        // std::accumulate over the dense vector (session.cpp:171-176) = the positive entries added in token-id
+        // order; replayed bit-exactly by the whole block (the entries are not sorted by value)
+        const float normalizer = block_sequential_sum<kVerifyThreads, 8, false>(s.residual_value, positives, kSeqSumOnly, 0.0f, sh.seq).acc;
+        if (positives == 0 || !(normalizer - normalizer == 0.0f) || normalizer <= 0.0f)
         {
-            float normalizer = 0.0f;
-            for (uint32_t i = 0; i < positives; ++i)
-                normalizer = __fadd_rn(normalizer, s.residual_value[i]);
-            if (!(normalizer - normalizer == 0.0f) || normalizer <= 0.0f)
+            if (tid == 0)
             {
                 sh.decision = 2;
                 sh.found[0] = 0.0f;
                 sh.cursor = 0;
             }
-            else
+        }
+        else
+        {
+            const float uniform = philox_uniform(p.seed, p.row_id, p.step + used);
+            const float sample_value = __fmul_rn(uniform, normalizer); // uniform_real_distribution<float>(0, normalizer)
+            const SeqResult draw = block_sequential_sum<kVerifyThreads, 8, false>(s.residual_value, positives, kSeqExceedBound, sample_value, sh.seq);
+            // session.cpp:189-197: the last positive entry if the sum never passes the draw
+            const uint32_t chosen = draw.stopped ? draw.taken - 1u : positives - 1u;
+            if (tid == 0)
             {
-                const float uniform = philox_uniform(p.seed, p.row_id, p.step + used);
-                const float sample_value = __fmul_rn(uniform, normalizer); // uniform_real_distribution<float>(0, normalizer)
-                float cumulative = 0.0f;
-                uint32_t chosen = positives - 1; // session.cpp:189-197: the last positive entry if the sum never passes the draw
-                for (uint32_t i = 0; i < positives; ++i)
-                {
-                    cumulative = __fadd_rn(cumulative, s.residual_value[i]);
-                    if (sample_value < cumulative)
-                    {
-                        chosen = i;
-                        break;
-                    }
-                }
                 sh.decision = 0;
                 sh.cursor = static_cast<uint32_t>(s.residual_token[chosen]);
                 sh.found[0] = __fdiv_rn(s.residual_value[chosen], normalizer);

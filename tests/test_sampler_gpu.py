@@ -348,3 +348,30 @@ def test_handles_on_two_devices_in_one_process(pkg, workloads, checker, torch_cu
             oracle = checker.expert_dispatch(wide, 4, 2048, 8)
             np.testing.assert_array_equal(plan.route_token[:32], oracle["token"])
             handle.close()
+
+
+def test_bf16_rows_without_topk_are_replayed_over_value_runs(pkg, workloads, parity):
+    """bf16 rows without Top-K skip the sort: their candidates are (value, count) runs of a histogram, and the
+    reference's sequential sums are replayed over the runs.  Long runs (few distinct values) put the binade
+    crossings and the Top-P / draw stops in the middle of runs."""
+    rng = np.random.default_rng(77)
+    rows, vocab = 28, 40000
+    values = (2.0 * rng.standard_normal((rows, vocab))).astype(np.float32)
+    values[4:8] = np.round(values[4:8] * 2) / 2                 # about 40 distinct values: runs of a thousand candidates
+    values[8:10] = np.round(values[8:10])                       # about 15 distinct values
+    values[10] = 1.25                                           # one value only
+    values[11] = np.where(rng.random(vocab) < 0.5, 3.0, 2.5)    # two values
+    values[12, rng.integers(0, vocab, 9)] = values[12].max()    # ties at the head
+    values[13, rng.integers(0, vocab, 3000)] = -np.inf          # masked logits
+    values[14] = -np.abs(values[14]) - 3.0                      # everything negative
+    values[15] = values[15] * 8.0                               # a peaked row: one or two candidates kept
+    values[16, ::2] = 0.0
+    values[16, 1::2] = -0.0                                     # zeros of both signs are one value
+    logits = workloads.to_bf16_bits(values)
+    params = pkg.make_row_params(rows, temperature=rng.choice([0.5, 1.0, 1.7], rows).astype(np.float32), top_k=0,
+                                 top_p=rng.choice([0.3, 0.9, 0.999, 1.0], rows).astype(np.float32),
+                                 min_p=rng.choice([0.0, 0.0, 1e-4, 0.02], rows).astype(np.float32), seed=77)
+    params["top_k"][20:24] = 5000                               # above the on-chip limit: same path, shortened list
+    for step in (0, 1, 2):
+        params["step"] = step
+        parity.check(logits, params)
