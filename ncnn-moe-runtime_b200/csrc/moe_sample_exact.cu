@@ -616,6 +616,7 @@ __device__ bool exact_row_bf16_runs(const SampleArgs& a, uint32_t row, const moe
     if (scratch_words < 4u * kMaxRuns)
         return false;
 
+    MOE_EXACT_BEGIN();
     // ---- pass 1: maximum, finite count, +inf --------------------------------------------
     if (tid == 0)
     {
@@ -649,6 +650,7 @@ __device__ bool exact_row_bf16_runs(const SampleArgs& a, uint32_t row, const moe
     }
     __syncthreads();
     const uint32_t finite_total = sh.finite_total;
+    MOE_EXACT_MARK(8);
     if (sh.flag_pos_inf != 0 || finite_total == 0)
     {
         out.status = MOE_ROW_NO_FINITE_LOGIT; // session.cpp:84-85,399
@@ -687,8 +689,10 @@ __device__ bool exact_row_bf16_runs(const SampleArgs& a, uint32_t row, const moe
         atomicAdd(&sh.window_total, inside);
     __syncthreads();
     const uint32_t window_total = sh.window_total;
+    MOE_EXACT_MARK(9);
 
     // ---- runs: the non-empty bins in rank order, with the number of candidates before each -------
+    // built in the global scratch slot, then moved into shared memory
     float* run_value = reinterpret_cast<float*>(scratch);       // addend of the run (numerator, probability, ...)
     uint32_t* run_count = scratch + kMaxRuns;
     uint32_t* run_cum = scratch + 2u * kMaxRuns;
@@ -750,7 +754,28 @@ __device__ bool exact_row_bf16_runs(const SampleArgs& a, uint32_t row, const moe
         }
     }
     __syncthreads();
+    // The histogram has served its purpose: its shared memory now holds the run arrays, which the
+    // sums below walk many times (4 * runs <= 4 * kMaxRuns words fit the kHistogramBins words).
+    static_assert(4u * kMaxRuns <= kHistogramBins, "the run arrays reuse the histogram's shared memory");
+    {
+        float* shared_value = reinterpret_cast<float*>(hist);
+        uint32_t* shared_count = hist + kMaxRuns;
+        uint32_t* shared_cum = hist + 2u * kMaxRuns;
+        uint32_t* shared_key = hist + 3u * kMaxRuns;
+        for (uint32_t r = tid; r < runs; r += kExactThreads)
+        {
+            shared_count[r] = run_count[r];
+            shared_cum[r] = run_cum[r];
+            shared_key[r] = run_key[r];
+        }
+        __syncthreads();
+        run_value = shared_value;
+        run_count = shared_count;
+        run_cum = shared_cum;
+        run_key = shared_key;
+    }
 
+    MOE_EXACT_MARK(10);
     // ---- the arithmetic of session.cpp:89-136,429-442 over the runs --------------------------
     // Top-K (only top_k > MOE_SAMPLER_TOPK_FAST_MAX reaches this kernel) shortens the list
     const uint32_t listed = (p.top_k > 0 && p.top_k < finite_total) ? p.top_k : finite_total;
@@ -762,6 +787,7 @@ __device__ bool exact_row_bf16_runs(const SampleArgs& a, uint32_t row, const moe
     const SeqRunsResult normaliser = block_sequential_sum_runs<kExactThreads, kRunsPerThread>(run_value, run_count, run_cum, runs, have, kSeqSumOnly, 0.0f, sh.seq_runs);
     if (normaliser.unsupported)
         return false;
+    MOE_EXACT_MARK(11);
     const float total = normaliser.acc;
     if (!(total - total == 0.0f) || total <= 0.0f)
     {
@@ -799,6 +825,7 @@ __device__ bool exact_row_bf16_runs(const SampleArgs& a, uint32_t row, const moe
     const SeqRunsResult nucleus = block_sequential_sum_runs<kExactThreads, kRunsPerThread>(run_value, run_count, run_cum, runs, min(allowed, have), kSeqReachBound, p.top_p, sh.seq_runs);
     if (nucleus.unsupported)
         return false;
+    MOE_EXACT_MARK(12);
     const uint32_t kept = nucleus.stopped ? nucleus.taken : allowed;
     // the renormaliser (session.cpp:130-132) repeats the adds of the Top-P loop over the same prefix from the same zero
     const float kept_total = nucleus.acc;
@@ -848,15 +875,28 @@ __device__ bool exact_row_bf16_runs(const SampleArgs& a, uint32_t row, const moe
     const float chosen_value = key_to_float(run_key[chosen_run]);
     const uint16_t wanted = static_cast<uint16_t>(__float_as_uint(chosen_value) >> 16);
     __syncthreads();
+    MOE_EXACT_MARK(13);
 
     // ---- the occurrence-th lowest index that carries the chosen value ------------------------
-    // each thread owns a contiguous range of the row, so that "lowest" is a prefix count over threads
-    const uint32_t range = (vocab + kExactThreads - 1u) / kExactThreads;
+    // each thread owns a contiguous range of the row (whole 16-byte vectors), so that "lowest" is a
+    // prefix count over threads
+    const uint32_t range = ((vocab + kExactThreads - 1u) / kExactThreads + 7u) & ~7u;
     const uint32_t begin = min(vocab, tid * range);
     const uint32_t end = min(vocab, begin + range);
     const auto matches = [&](uint16_t pattern) -> bool { return pattern == wanted || (((pattern | wanted) & 0x7FFFu) == 0u); };
+    const bool aligned = (reinterpret_cast<uintptr_t>(bits) & 15u) == 0u;
+    // bit i of the mask = the i-th logit of the vector carries the value
+    const auto vector_mask = [&](const uint4& v) -> uint32_t {
+        return (matches(static_cast<uint16_t>(v.x)) ? 1u : 0u) | (matches(static_cast<uint16_t>(v.x >> 16)) ? 2u : 0u) |
+               (matches(static_cast<uint16_t>(v.y)) ? 4u : 0u) | (matches(static_cast<uint16_t>(v.y >> 16)) ? 8u : 0u) |
+               (matches(static_cast<uint16_t>(v.z)) ? 16u : 0u) | (matches(static_cast<uint16_t>(v.z >> 16)) ? 32u : 0u) |
+               (matches(static_cast<uint16_t>(v.w)) ? 64u : 0u) | (matches(static_cast<uint16_t>(v.w >> 16)) ? 128u : 0u);
+    };
+    const uint32_t whole_end = aligned ? begin + ((end - begin) & ~7u) : begin; // vectors first, the ragged rest one by one
     uint32_t in_range = 0;
-    for (uint32_t i = begin; i < end; ++i)
+    for (uint32_t i = begin; i < whole_end; i += 8)
+        in_range += __popc(vector_mask(*reinterpret_cast<const uint4*>(bits + i)));
+    for (uint32_t i = whole_end; i < end; ++i)
         in_range += matches(bits[i]) ? 1u : 0u;
     uint32_t scan = in_range;
 #pragma unroll
@@ -877,20 +917,32 @@ __device__ bool exact_row_bf16_runs(const SampleArgs& a, uint32_t row, const moe
     if (occurrence >= before && occurrence < before + in_range)
     {
         uint32_t seen = before;
-        for (uint32_t i = begin; i < end; ++i)
+        uint32_t found = 0xFFFFFFFFu;
+        for (uint32_t i = begin; i < whole_end && found == 0xFFFFFFFFu; i += 8)
+        {
+            uint32_t mask = vector_mask(*reinterpret_cast<const uint4*>(bits + i));
+            const uint32_t here = __popc(mask);
+            if (seen + here > occurrence)
+            {
+                for (uint32_t skip = occurrence - seen; skip > 0; --skip)
+                    mask &= mask - 1u; // drop the lowest set bits
+                found = i + static_cast<uint32_t>(__ffs(mask) - 1);
+            }
+            seen += here;
+        }
+        for (uint32_t i = whole_end; i < end && found == 0xFFFFFFFFu; ++i)
             if (matches(bits[i]))
             {
                 if (seen == occurrence)
-                {
-                    sh.chosen_index = i;
-                    break;
-                }
+                    found = i;
                 ++seen;
             }
+        sh.chosen_index = found;
     }
     __syncthreads();
     out.token = static_cast<int32_t>(sh.chosen_index);
     __syncthreads();
+    MOE_EXACT_MARK(0);
     return out.token >= 0;
 }
 
