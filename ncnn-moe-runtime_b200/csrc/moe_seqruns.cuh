@@ -122,21 +122,25 @@ __device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, 
                 copies[j] = copies_of(run + offset) - (offset == 0 ? done : 0u);
             }
         }
-#pragma unroll
-        for (int j = 0; j < kItems; ++j)
+        // threads beyond the chunk keep the identity pair (0, 0): a row has a few thousand runs at most
+        if (first < chunk)
         {
-            uint32_t d0, d1;
-            seq_element(mine[j], inverse_unit, d0, d1);
-            const uint32_t e0 = seq_clamp64(seq_run_steps(d0, d1, copies[j], 0u));
-            const uint32_t e1 = seq_clamp64(seq_run_steps(d0, d1, copies[j], 1u));
-            if (j == 0)
+#pragma unroll
+            for (int j = 0; j < kItems; ++j)
             {
-                t0 = e0;
-                t1 = e1;
-            }
-            else
-            {
-                seq_compose(t0, t1, e0, e1, t0, t1);
+                uint32_t d0, d1;
+                seq_element(mine[j], inverse_unit, d0, d1);
+                const uint32_t e0 = seq_clamp64(seq_run_steps(d0, d1, copies[j], 0u));
+                const uint32_t e1 = seq_clamp64(seq_run_steps(d0, d1, copies[j], 1u));
+                if (j == 0)
+                {
+                    t0 = e0;
+                    t1 = e1;
+                }
+                else
+                {
+                    seq_compose(t0, t1, e0, e1, t0, t1);
+                }
             }
         }
         uint32_t s0 = t0, s1 = t1;
@@ -193,7 +197,7 @@ __device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, 
         for (int j = 0; j < kItems; ++j)
         {
             const uint32_t offset = first + j;
-            if (offset < chunk && event == 0xFFFFFFFFu && copies[j] != 0u)
+            if (first < chunk && offset < chunk && event == 0xFFFFFFFFu && copies[j] != 0u)
             {
                 uint32_t d0, d1;
                 seq_element(mine[j], inverse_unit, d0, d1);
