@@ -143,14 +143,19 @@ __device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, 
                 }
             }
         }
+        // warps whose runs all lie beyond the chunk only keep the barriers company
+        const bool warp_active = warp * 32u * kItems < chunk;
         uint32_t s0 = t0, s1 = t1;
-#pragma unroll
-        for (int offset = 1; offset < 32; offset <<= 1)
+        if (warp_active)
         {
-            const uint32_t p0 = __shfl_up_sync(kFullMask, s0, offset);
-            const uint32_t p1 = __shfl_up_sync(kFullMask, s1, offset);
-            if (lane >= static_cast<uint32_t>(offset))
-                seq_compose(p0, p1, s0, s1, s0, s1);
+#pragma unroll
+            for (int offset = 1; offset < 32; offset <<= 1)
+            {
+                const uint32_t p0 = __shfl_up_sync(kFullMask, s0, offset);
+                const uint32_t p1 = __shfl_up_sync(kFullMask, s1, offset);
+                if (lane >= static_cast<uint32_t>(offset))
+                    seq_compose(p0, p1, s0, s1, s0, s1);
+            }
         }
         if (lane == 31)
         {
@@ -165,6 +170,7 @@ __device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, 
         __syncthreads();
         const uint32_t start_parity = start_integer & 1u;
         uint32_t before = 0; // integer steps taken before my first run
+        if (warp_active)
         {
             constexpr uint32_t kWarps = kThreads / 32;
             uint32_t w0 = lane < kWarps ? sh.warp_pair[lane][0] : 0u;
