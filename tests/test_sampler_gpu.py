@@ -375,3 +375,20 @@ def test_bf16_rows_without_topk_are_replayed_over_value_runs(pkg, workloads, par
     for step in (0, 1, 2):
         params["step"] = step
         parity.check(logits, params)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_more_rows_than_resident_ctas(pkg, workloads, parity, dtype):
+    """With more rows than CTAs that fit the GPU at once, a CTA takes several rows in turn and asks for the next
+    row's first bytes while it finishes the current one: every kind of row in every position, invalid rows included."""
+    rng = np.random.default_rng(91)
+    rows, vocab = 1000, 9000 + (0 if dtype == "f32" else 11)
+    values = (3.0 * rng.standard_normal((rows, vocab))).astype(np.float32)
+    values[rng.integers(0, rows, 40), rng.integers(0, vocab, 40)] += 9.0
+    params = pkg.make_row_params(rows, temperature=rng.choice([0.0, 0.6, 1.0, 1.4], rows).astype(np.float32),
+                                 top_k=rng.choice([0, 1, 8, 50, 300, 700], rows).astype(np.uint32),
+                                 top_p=rng.uniform(0.4, 1.0, rows).astype(np.float32),
+                                 min_p=rng.choice([0.0, 0.03], rows).astype(np.float32), seed=91)
+    params["top_p"][::97] = 0.0                                   # rejected rows in between
+    logits = values if dtype == "f32" else workloads.to_bf16_bits(values)
+    parity.check(logits, params, topk_stride=8)
