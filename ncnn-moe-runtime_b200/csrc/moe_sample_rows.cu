@@ -1232,30 +1232,35 @@ __device__ __forceinline__ void reduce_buffer(Ctx& c, bool sort)
         }
         else if (c.mode != kLive && c.k <= kThreads / 2u)
         {
-            // A little over one record per thread: sort the first kThreads, and
-            // let only the spare records that beat their k-th join a second,
-            // much smaller sort of the k best so far.
-            const uint32_t tid = threadIdx.x;
-            const uint64_t spare = kThreads + tid < n ? c.rec[kThreads + tid] : 0ull;
-            if (tid == 0)
-                s.sel.out_count = 0;
-            block_rank_sort_descending<kThreads>(c.rec, kThreads); // ends with a barrier
-            const uint64_t pivot = c.rec[c.k - 1u];
-            const bool joins = spare > pivot;
-            const unsigned voters = __ballot_sync(kFullMask, joins);
-            uint32_t base = 0;
-            if ((tid & 31u) == 0u && voters != 0u)
-                base = atomicAdd(&s.sel.out_count, static_cast<uint32_t>(__popc(voters)));
-            base = __shfl_sync(kFullMask, base, 0);
-            __syncthreads(); // every thread has read the pivot
-            if (joins)
-                c.rec[c.k + base + __popc(voters & ((1u << (tid & 31u)) - 1u))] = spare;
+            // A little over one record per thread: the k-th best key of the first kThreads records
+            // is a lower bound of the row's k-th best, so everything below it can go before the sort.
+            static_assert(kTightenWindow == kThreads, "warp_kth_key looks at one record per thread of the block");
+            if (threadIdx.x < 32)
+            {
+                const uint32_t kth = warp_kth_key(c.rec, kThreads, c.k);
+                if (threadIdx.x == 0)
+                    s.tighten_key = kth;
+            }
             __syncthreads();
-            const uint32_t merged = c.k + s.sel.out_count; // at most k + kThreads
-            if (merged <= kThreads)
-                block_rank_sort_descending<kThreads>(c.rec, merged);
+            const uint32_t kth = s.tighten_key;
+            const uint32_t survivors = block_compact<kThreads, kItems>(c.rec, n, s.sel, [=](uint64_t record) { return record_key(record) >= kth; });
+            if (threadIdx.x == 0)
+                s.count = survivors;
+            __syncthreads();
+            if (survivors <= kThreads)
+                block_rank_sort_descending<kThreads>(c.rec, survivors);
             else
-                block_rank_sort_descending2<kThreads>(c.rec, merged);
+                block_rank_sort_descending2<kThreads>(c.rec, survivors);
+            MOE_SUB(3);
+            kept = min(survivors, c.k);
+            if (kept != survivors)
+            {
+                if (threadIdx.x == 0)
+                    s.count = kept;
+                __syncthreads();
+            }
+            c.sorted = true;
+            return;
         }
         else
         {
