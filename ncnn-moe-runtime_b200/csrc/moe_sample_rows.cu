@@ -34,13 +34,13 @@
 
 #ifdef MOE_PHASE_TIMERS
 // Debug builds only: cycles spent per kernel phase, summed over CTAs.
-__device__ unsigned long long g_phase_cycles[16];
+__device__ unsigned long long g_phase_cycles[24];
 extern "C" void moe_debug_phase_cycles(unsigned long long* out, int reset)
 {
-    cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(unsigned long long) * 16);
+    cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(unsigned long long) * 24);
     if (reset)
     {
-        unsigned long long zeros[16] = {};
+        unsigned long long zeros[24] = {};
         cudaMemcpyToSymbol(g_phase_cycles, zeros, sizeof(zeros));
     }
 }
@@ -200,6 +200,21 @@ struct Ctx
     bool aborted;
     bool sorted; // the buffer is already in rank order
 };
+
+// The out-of-line helpers of the careful paths take the context by reference,
+// which would pin it to local memory — reached through L2 once the shared-memory
+// carve-out has left no L1 — for the whole kernel.  The hot path therefore keeps
+// its context in registers and hands those helpers a copy.
+__device__ __forceinline__ void copy_back_context(Ctx& to, const Ctx& from)
+{
+    to.mode = from.mode;
+    to.k = from.k;
+    to.flush_level = from.flush_level;
+    to.tau = from.tau;
+    to.primed = from.primed;
+    to.aborted = from.aborted;
+    to.sorted = from.sorted;
+}
 
 __device__ __forceinline__ float live_threshold(uint32_t maxkey, float temperature)
 {
@@ -1192,6 +1207,7 @@ __device__ __forceinline__ int stream_slice_ring(RowShared& s, Ring& ring, const
 __device__ __forceinline__ void reduce_buffer(Ctx& c, bool sort)
 {
     RowShared& s = c.s;
+    MOE_SUB_BEGIN();
     c.sorted = false;
     if (c.aborted)
         return;
@@ -1225,7 +1241,7 @@ __device__ __forceinline__ void reduce_buffer(Ctx& c, bool sort)
             __syncthreads();
             kept = s.sel.out_count;
         }
-        MOE_SUB_BEGIN();
+        MOE_SUB(16);
         if (n <= kThreads)
         {
             block_rank_sort_descending<kThreads>(c.rec, n);
@@ -1276,9 +1292,14 @@ __device__ __forceinline__ void reduce_buffer(Ctx& c, bool sort)
             __syncthreads();
         }
         c.sorted = true;
+        MOE_SUB(17);
         return;
     }
-    flush_buffer(c);
+    {
+        Ctx careful = c;
+        flush_buffer(careful);
+        copy_back_context(c, careful);
+    }
     if (sort && !c.aborted && s.count <= 2u * kThreads)
     {
         if (s.count <= kThreads)
@@ -1589,8 +1610,12 @@ __global__ void __launch_bounds__(kThreads, MOE_ROW_MIN_CTAS) sample_rows_kernel
     if (streamed == kStreamTooLarge)
         c.aborted = true;
     else if (streamed == kStreamCareful)
-        stream_slice_safe<T>(c, row_pointer, vocab, head, vectors, tail_begin, group_begin * (kGroupVectors / kThreads),
+    {
+        Ctx careful = c;
+        stream_slice_safe<T>(careful, row_pointer, vocab, head, vectors, tail_begin, group_begin * (kGroupVectors / kThreads),
                              min(group_end * (kGroupVectors / kThreads), (vectors + kThreads - 1) / kThreads), rank, splits);
+        copy_back_context(c, careful);
+    }
     MOE_PHASE_MARK(2);
     if (a.overlap_previous)
     {
@@ -1652,7 +1677,11 @@ __global__ void __launch_bounds__(kThreads, MOE_ROW_MIN_CTAS) sample_rows_kernel
                 continue;
             if (s.count + remote_count > c.cap)
             {
-                flush_buffer(c);
+                {
+                    Ctx careful = c;
+                    flush_buffer(careful);
+                    copy_back_context(c, careful);
+                }
                 if (c.aborted || s.count + remote_count > c.cap)
                 {
                     c.aborted = true;
@@ -1725,7 +1754,11 @@ __global__ void __launch_bounds__(kThreads, 2) merge_candidates_kernel(const uin
     for (uint32_t shard = 0; shard < shards; ++shard)
     {
         if (s.count + top_k > c.cap)
-            flush_buffer(c);
+        {
+            Ctx careful = c;
+            flush_buffer(careful);
+            copy_back_context(c, careful);
+        }
         const uint32_t local_count = s.count;
         const uint64_t* list = gathered + (static_cast<size_t>(shard) * rows + row) * top_k;
         // a shard's list is dense from the front; empty slots hold 0
