@@ -121,6 +121,12 @@ __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, u
                                                        const KeptList& kept_list)
 {
     const int lane = threadIdx.x & 31;
+    // records and work are shared memory: read through their window addresses
+    const uint32_t record_base = shared_address(records);
+    const uint32_t work_base = shared_address(work);
+    const auto record_at = [&](uint32_t i) -> uint64_t { return load_shared_64(record_base + 8u * i); };
+    const auto work_at = [&](uint32_t i) -> float { return load_shared_f32(work_base + 4u * i); };
+    const auto set_work = [&](uint32_t i, float value) { store_shared_32(work_base + 4u * i, __float_as_uint(value)); };
     RowOutcome out{MOE_ROW_OK, -1, 0.0f, 0u, false};
     if (kept_list.count != nullptr && lane == 0)
         *kept_list.count = 0; // stays 0 on every error return
@@ -129,7 +135,7 @@ __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, u
         out.status = MOE_ROW_NO_FINITE_LOGIT;
         return out;
     }
-    const uint32_t head_key = record_key(records[0]);
+    const uint32_t head_key = record_key(record_at(0));
     if (head_key >= kKeyPosInf || head_key <= kKeyNegInf)
     {
         out.status = MOE_ROW_NO_FINITE_LOGIT; // session.cpp:84-85
@@ -147,7 +153,7 @@ __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, u
     for (uint32_t base = 0; base < considered; base += 32)
     {
         const uint32_t i = base + lane;
-        const bool is_finite = (i < considered) && (record_key(records[i]) > kKeyNegInf);
+        const bool is_finite = (i < considered) && (record_key(record_at(i)) > kKeyNegInf);
         finite += __popc(__ballot_sync(kFullMask, is_finite));
     }
 
@@ -156,7 +162,7 @@ __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, u
     {
         const float peak = __fdiv_rn(key_to_float(head_key), temperature);
         for (uint32_t i = lane; i < finite; i += 32)
-            work[i] = exact_expf(scaled_offset(key_to_float(record_key(records[i])), temperature, peak));
+            set_work(i, exact_expf(scaled_offset(key_to_float(record_key(record_at(i))), temperature, peak)));
     }
     __syncwarp();
     const float total = warp_sequential_sum<kSeqWarpAll>(work, finite, 0.0f).acc;
@@ -174,16 +180,16 @@ __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, u
     // sequential sum over that prefix only.
     __syncwarp();
     for (uint32_t i = lane; i < finite; i += 32)
-        work[i] = __fdiv_rn(work[i], total);
+        set_work(i, __fdiv_rn(work_at(i), total));
     __syncwarp();
     uint32_t allowed = finite;
     if (min_p > 0.0f)
     {
-        const float floor_probability = __fmul_rn(work[0], min_p);
+        const float floor_probability = __fmul_rn(work_at(0), min_p);
         for (uint32_t base = 0; base < finite; base += 32)
         {
             const uint32_t i = base + lane;
-            const bool below = (i < finite) && !(work[i] >= floor_probability);
+            const bool below = (i < finite) && !(work_at(i) >= floor_probability);
             const unsigned voters = __ballot_sync(kFullMask, below);
             if (voters != 0u)
             {
@@ -207,7 +213,7 @@ __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, u
     }
     if (kept == 1)
     {
-        out.token = static_cast<int32_t>(record_index(records[0])); // session.cpp:429-430: no uniform drawn
+        out.token = static_cast<int32_t>(record_index(record_at(0))); // session.cpp:429-430: no uniform drawn
         out.probability = 1.0f;
         if (kept_list.count != nullptr && lane == 0)
         {
@@ -227,7 +233,7 @@ __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, u
     // inverse CDF (session.cpp:432-442)
     __syncwarp();
     for (uint32_t i = lane; i < kept; i += 32)
-        work[i] = __fdiv_rn(work[i], kept_total);
+        set_work(i, __fdiv_rn(work_at(i), kept_total));
     __syncwarp();
     if (kept_list.count != nullptr)
     {
@@ -236,16 +242,16 @@ __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, u
         for (uint32_t i = lane; i < min(kept, kept_list.stride); i += 32)
         {
             if (kept_list.token != nullptr)
-                kept_list.token[i] = static_cast<int32_t>(record_index(records[i]));
+                kept_list.token[i] = static_cast<int32_t>(record_index(record_at(i)));
             if (kept_list.probability != nullptr)
-                kept_list.probability[i] = work[i];
+                kept_list.probability[i] = work_at(i);
         }
     }
     const SeqWarpResult draw = warp_sequential_sum<kSeqWarpExceed>(work, kept, uniform);
     if (draw.index < kept)
     {
-        out.token = static_cast<int32_t>(record_index(records[draw.index]));
-        out.probability = work[draw.index];
+        out.token = static_cast<int32_t>(record_index(record_at(draw.index)));
+        out.probability = work_at(draw.index);
         return out;
     }
     if (!list_is_complete && !cut)
@@ -253,8 +259,8 @@ __device__ __forceinline__ RowOutcome finish_row_warp(const uint64_t* records, u
         out.defer = true;
         return out;
     }
-    out.token = static_cast<int32_t>(record_index(records[kept - 1]));
-    out.probability = work[kept - 1];
+    out.token = static_cast<int32_t>(record_index(record_at(kept - 1)));
+    out.probability = work_at(kept - 1);
     return out;
 }
 

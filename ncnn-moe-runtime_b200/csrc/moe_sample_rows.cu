@@ -1211,7 +1211,7 @@ __device__ __forceinline__ void reduce_buffer(Ctx& c, bool sort)
     c.sorted = false;
     if (c.aborted)
         return;
-    const uint32_t n = s.count;
+    const uint32_t n = load_shared_32(shared_address(&s.count));
     if (n <= 2u * kThreads)
     {
         // At most two records per thread.  Live mode first blanks the records that
@@ -1324,7 +1324,9 @@ __device__ __forceinline__ void finish_row_block(const SampleArgs& a, RowShared&
             exact_rows[atomicAdd(exact_count, 1u)] = row;
         return;
     }
-    const uint32_t n = s.count;
+    const uint32_t n = load_shared_32(shared_address(&s.count));
+    const uint32_t record_base = shared_address(c.rec);
+    const uint32_t work_base = shared_address(c.work);
     if (!c.sorted)
     {
         if (n <= kThreads)
@@ -1362,7 +1364,7 @@ __device__ __forceinline__ void finish_row_block(const SampleArgs& a, RowShared&
     {
         const uint32_t listed = (c.mode == kTopK) ? min(n, c.k) : 0u;
         for (uint32_t i = tid; i < a.topk_stride; i += kThreads)
-            a.topk_index[static_cast<size_t>(row) * a.topk_stride + i] = (i < listed) ? static_cast<int32_t>(record_index(c.rec[i])) : -1;
+            a.topk_index[static_cast<size_t>(row) * a.topk_stride + i] = (i < listed) ? static_cast<int32_t>(record_index(load_shared_64(record_base + 8u * i))) : -1;
     }
     MOE_SUB(4);
 
@@ -1373,16 +1375,16 @@ __device__ __forceinline__ void finish_row_block(const SampleArgs& a, RowShared&
     bool numerators_ready = false;
     if (c.mode != kGreedy && n > 0)
     {
-        const uint32_t head_key = record_key(c.rec[0]);
+        const uint32_t head_key = record_key(load_shared_64(record_base));
         if (head_key < kKeyPosInf && head_key > kKeyNegInf)
         {
             const uint32_t considered = (p.top_k > 0 && p.top_k <= n) ? p.top_k : n;
             const float peak = __fdiv_rn(key_to_float(head_key), p.temperature);
             for (uint32_t i = tid; i < considered; i += kThreads)
             {
-                const uint32_t key = record_key(c.rec[i]);
+                const uint32_t key = record_key(load_shared_64(record_base + 8u * i));
                 if (key > kKeyNegInf)
-                    c.work[i] = exact_expf(scaled_offset(key_to_float(key), p.temperature, peak));
+                    store_shared_32(work_base + 4u * i, __float_as_uint(exact_expf(scaled_offset(key_to_float(key), p.temperature, peak))));
             }
             numerators_ready = true;
         }

@@ -289,32 +289,33 @@ __device__ __noinline__ void block_sort_descending(uint64_t* records, uint32_t p
 }
 
 // Position of `mine` among the records of a descending run of 32 (zeros pad
-// the tail): the number of entries larger than it.
-__device__ __forceinline__ uint32_t count_larger_in_run(const uint64_t* run, uint64_t mine)
+// the tail): the number of entries larger than it.  `run` is the shared-window
+// address of the run.
+__device__ __forceinline__ uint32_t count_larger_in_run(uint32_t run, uint64_t mine)
 {
     uint32_t lo = 0, hi = 32;
 #pragma unroll
     for (int step = 0; step < 5; ++step)
     {
         const uint32_t mid = (lo + hi) >> 1;
-        if (run[mid] > mine)
+        if (load_shared_64(run + 8u * mid) > mine)
             lo = mid + 1;
         else
             hi = mid;
     }
-    if (lo < 32 && run[lo] > mine)
+    if (lo < 32 && load_shared_64(run + 8u * lo) > mine)
         ++lo;
     return lo;
 }
 
-// Sorts records[0..n) descending for n <= kItems * kThreads (kItems 1 or 2).
-// Each warp sorts runs of 32 records in registers with a shuffle network; a
-// record's final position is its position in its own run plus, for every other
-// run, the number of larger records found by binary search — the searches of
-// the different runs are independent, so they are unrolled side by side.
-// Records are unique and 0 pads the tail, so positions are unique.  Three
-// barriers, no atomics: the cheapest order for the few hundred survivors a
-// slice or a row usually has.  Ends with a barrier.
+// Sorts records[0..n) (shared memory) descending for n <= kItems * kThreads
+// (kItems 1 or 2).  Each warp sorts runs of 32 records in registers with a
+// shuffle network; a record's final position is its position in its own run
+// plus, for every other run, the number of larger records found by binary
+// search — the searches of the different runs are independent, so they are
+// unrolled side by side.  Records are unique and 0 pads the tail, so positions
+// are unique.  Three barriers, no atomics: the cheapest order for the few
+// hundred survivors a slice or a row usually has.  Ends with a barrier.
 template<int kThreads, int kItems>
 __device__ __forceinline__ void block_rank_sort_items(uint64_t* records, uint32_t n)
 {
@@ -323,10 +324,11 @@ __device__ __forceinline__ void block_rank_sort_items(uint64_t* records, uint32_
     const uint32_t lane = tid & 31u;
     const uint32_t warp = tid >> 5;
     const uint32_t runs = (n + 31u) >> 5;
+    const uint32_t base = shared_address(records);
     uint64_t mine[kItems];
 #pragma unroll
     for (int j = 0; j < kItems; ++j)
-        mine[j] = (tid + j * kThreads < n) ? records[tid + j * kThreads] : 0ull;
+        mine[j] = (tid + j * kThreads < n) ? load_shared_64(base + 8u * (tid + j * kThreads)) : 0ull;
 #pragma unroll
     for (uint32_t size = 2; size <= 32; size <<= 1)
     {
@@ -349,7 +351,7 @@ __device__ __forceinline__ void block_rank_sort_items(uint64_t* records, uint32_
 #pragma unroll
     for (int j = 0; j < kItems; ++j)
         if (warp + j * kRunsPerItem < runs)
-            records[tid + j * kThreads] = mine[j]; // run `warp + j * kRunsPerItem`, descending, zeros last
+            store_shared_64(base + 8u * (tid + j * kThreads), mine[j]); // run `warp + j * kRunsPerItem`, descending, zeros last
     __syncthreads();
     uint32_t position[kItems];
 #pragma unroll
@@ -362,14 +364,14 @@ __device__ __forceinline__ void block_rank_sort_items(uint64_t* records, uint32_
 #pragma unroll
             for (uint32_t w = 0; w < kItems * kRunsPerItem; ++w)
                 if (w < runs && w != own)
-                    position[j] += count_larger_in_run(records + w * 32u, mine[j]);
+                    position[j] += count_larger_in_run(base + 256u * w, mine[j]);
         }
     }
     __syncthreads();
 #pragma unroll
     for (int j = 0; j < kItems; ++j)
         if (mine[j] != 0ull)
-            records[position[j]] = mine[j];
+            store_shared_64(base + 8u * position[j], mine[j]);
     __syncthreads();
 }
 
