@@ -454,6 +454,34 @@ def run_speculative_bench(args, as_dict=False):
     stop.record()
     torch.cuda.synchronize()
     ms = start.elapsed_time(stop) / steps
+    sampler.close()
+    # the scheduler's batch: 32 Sessions verified by one call (the 4 cases repeated, each Session with its own counters)
+    sessions = 32
+    batch_params = np.repeat(params, sessions)
+    batch_params["row_id"] = np.arange(sessions)
+    batch_target = torch.stack([device_cases[b % 4][0] for b in range(sessions)])
+    batch_draft = torch.stack([device_cases[b % 4][1] for b in range(sessions)])
+    batch_proposed = torch.stack([device_cases[b % 4][2] for b in range(sessions)])
+    sampler = package.Sampler(max_rows=sessions * (2 * draft_count + 1), max_vocab=vocab)
+    records, _ = sampler.speculative_verify_batch(batch_target, batch_draft, batch_proposed, batch_params)
+    batch_equal = 0
+    for b in range(sessions):
+        uniforms = np.array([package.philox_uniform(9, b, int(params["step"][0]) + i) for i in range(draft_count + 2)], dtype=np.float32)
+        want = oracle.speculative_verify(*cases[b % 4], uniforms, *options)
+        batch_equal += int(records[b]["status"] == want["status"] == 0 and records[b]["accepted"] == want["accepted"]
+                           and records[b]["next_token"] == want["next_token"] and records[b]["uniforms_used"] == want["uniforms_used"])
+    batch_out = None
+    for i in range(3):
+        batch_out = sampler.speculative_verify_batch(batch_target, batch_draft, batch_proposed, batch_params, out=batch_out, sync=False)
+    torch.cuda.synchronize()
+    batch_steps = min(args.steps, 64)
+    start.record()
+    for i in range(batch_steps):
+        sampler.speculative_verify_batch(batch_target, batch_draft, batch_proposed, batch_params, out=batch_out, sync=False)
+    stop.record()
+    torch.cuda.synchronize()
+    batch_ms = start.elapsed_time(stop) / batch_steps
+    batch_bytes = sessions * 9 * vocab * 4
     line = {"metric": "speculative verifications/s, 4 proposed tokens, vocab 201088", "value": 1e3 / ms, "unit": "verifications/s", "n_gpus": 1,
             "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "5 target + 4 draft rows x 201088 fp32 2.5*N(0,1) (draft = target + noise), T=1 top_k=40 top_p=0.95; direct C-ABI calls, "
@@ -461,7 +489,10 @@ def run_speculative_bench(args, as_dict=False):
             "gpu_launches": 3 * steps,
             "cpu_baseline": {"value": len(cases) / t_cpu, "unit": "verifications/s", "cores": 1, "kind": oracle.kind,
                              "sample": f"{len(cases)} verifications, single thread (a Session verifies on its own thread)"},
-            "results_equal_to_reference": f"{equal}/{len(cases)}"}
+            "results_equal_to_reference": f"{equal}/{len(cases)}",
+            "batched": {"sessions_per_call": sessions, "ms_per_call": batch_ms, "verifications_per_s": sessions * 1e3 / batch_ms,
+                        "logits_GBps": batch_bytes / batch_ms / 1e6, "kernels_per_call": 3, "steps": batch_steps,
+                        "results_equal_to_reference": f"{batch_equal}/{sessions}"}}
     sampler.close()
     if as_dict:
         return line

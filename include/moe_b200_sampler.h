@@ -235,6 +235,23 @@ int moe_speculative_verify(moe_sampler* sampler, void* stream, const void* targe
                            uint32_t draft_count, uint32_t vocab, size_t row_stride, const int32_t* proposed_tokens,
                            const moe_row_params* params, float* accepted_probability, moe_speculative_result* result);
 
+/* moe_speculative_verify for `sessions` Sessions in one call: the scheduler's
+ * batch of Sessions that all verify `draft_count` proposals this step.  One
+ * sampler launch covers every target position, one every draft position, and
+ * one verification kernel walks the Sessions side by side (one CTA each); each
+ * Session's outcome is what moe_speculative_verify gives for it alone.
+ *
+ * target_logits   device, [sessions x (draft_count + 1) x row_stride], Session-major
+ * draft_logits    device, [sessions x draft_count x row_stride]
+ * proposed_tokens device, [sessions x draft_count]
+ * params          HOST, one entry per Session
+ * accepted_probability  device, [sessions x draft_count]
+ * results         device, [sessions]
+ * sessions * (2 * draft_count + 1) <= the handle's max_rows. */
+int moe_speculative_verify_batch(moe_sampler* sampler, void* stream, const void* target_logits, const void* draft_logits, int dtype,
+                                 uint32_t sessions, uint32_t draft_count, uint32_t vocab, size_t row_stride, const int32_t* proposed_tokens,
+                                 const moe_row_params* params, float* accepted_probability, moe_speculative_result* results);
+
 /* moe_speculative_verify with every buffer in HOST memory (the reference holds
  * target and draft logits as std::vector<float>, session.cpp:760-769).  Copies
  * in, verifies, copies out and synchronises before returning. */

@@ -55,7 +55,7 @@ class RouterOptions(C.Structure):
 
 EXPORTED_SYMBOLS = [
     "moe_sampler_create", "moe_sampler_destroy", "moe_sampler_last_error", "moe_row_status_message", "moe_row_status_error_code",
-    "moe_philox_uniform", "moe_host_alloc", "moe_host_free", "moe_sample_batch", "moe_sample_batch_ex", "moe_speculative_verify", "moe_speculative_verify_host", "moe_sample_batch_host",
+    "moe_philox_uniform", "moe_host_alloc", "moe_host_free", "moe_sample_batch", "moe_sample_batch_ex", "moe_speculative_verify", "moe_speculative_verify_batch", "moe_speculative_verify_host", "moe_sample_batch_host",
     "moe_sample_local_candidates", "moe_sample_merge_candidates", "moe_router_dispatch", "moe_router_status_message",
     "moe_router_status_error_code", "moe_router_check_options", "moe_router_dispatch_host", "moe_regroup_gather",
     "moe_router_dispatch_static", "moe_sampler_set_overlap", "moe_sample_tokens", "moe_regroup_gather_check",
@@ -98,6 +98,7 @@ def library() -> C.CDLL:
     lib.moe_sample_batch.argtypes = [vp, vp, vp, C.c_int, u32, u32, sz, vp, u64, vp, vp, vp, vp, vp, vp, vp, u32]
     lib.moe_sample_batch_ex.argtypes = [vp, vp, vp, C.c_int, u32, u32, sz, vp, u64, vp, vp, C.POINTER(SampleOutputs)]
     lib.moe_speculative_verify.argtypes = [vp, vp, vp, vp, C.c_int, u32, u32, sz, vp, vp, vp, vp]
+    lib.moe_speculative_verify_batch.argtypes = [vp, vp, vp, vp, C.c_int, u32, u32, u32, sz, vp, vp, vp, vp]
     lib.moe_speculative_verify_host.argtypes = [vp, vp, vp, C.c_int, u32, u32, sz, vp, vp, vp, vp]
     lib.moe_sample_batch_host.argtypes = [vp, vp, C.c_int, u32, u32, sz, vp, vp, vp, vp, vp, vp, vp, vp, u32]
     lib.moe_sample_local_candidates.argtypes = [vp, vp, vp, C.c_int, u32, u32, sz, u32, u32, vp]
@@ -293,6 +294,35 @@ class Sampler:
         out["next_probability"] = np.float32(record["next_probability"])
         out["accepted_probability"] = accepted_probability.cpu().numpy()[:out["accepted"]]
         return out
+
+    def speculative_verify_batch(self, target_logits, draft_logits, proposed, params, stream=None, out=None, sync=True):
+        """moe_speculative_verify_batch: `sessions` Sessions verified in one call.
+        target_logits: CUDA [sessions, draft_count + 1, vocab]; draft_logits: CUDA [sessions, draft_count, vocab] (None when
+        draft_count is 0); proposed: CUDA int32 [sessions, draft_count]; params: ROW_PARAMS_DTYPE [sessions].
+        Returns (records, accepted_probability): a SPECULATIVE_RESULT_DTYPE array [sessions] and float32 [sessions, draft_count]
+        on the host (sync=False: the device tensors, to be passed back as `out`)."""
+        import torch
+        sessions, positions, vocab = target_logits.shape
+        draft_count = positions - 1
+        assert target_logits.is_contiguous() and (draft_count == 0 or (draft_logits.is_contiguous() and proposed.is_contiguous()))
+        assert draft_count == 0 or (tuple(draft_logits.shape) == (sessions, draft_count, vocab) and tuple(proposed.shape) == (sessions, draft_count))
+        dtype = DTYPE_F32 if target_logits.dtype == torch.float32 else DTYPE_BF16
+        device = target_logits.device
+        params = np.ascontiguousarray(params, dtype=ROW_PARAMS_DTYPE).reshape(sessions)
+        if out is None:
+            out = (torch.zeros(max(sessions * draft_count, 1), dtype=torch.float32, device=device),
+                   torch.zeros(max(sessions, 1) * SPECULATIVE_RESULT_DTYPE.itemsize, dtype=torch.uint8, device=device))
+        accepted_probability, result = out
+        stream_handle = torch.cuda.current_stream(device).cuda_stream if stream is None else stream
+        self._check(self._lib.moe_speculative_verify_batch(self._handle, C.c_void_p(stream_handle), _dev_ptr(target_logits),
+                                                           _dev_ptr(draft_logits) if draft_count else None, dtype, sessions, draft_count, vocab, vocab,
+                                                           _dev_ptr(proposed) if draft_count else None, _np_ptr(params),
+                                                           _dev_ptr(accepted_probability), _dev_ptr(result)))
+        if not sync:
+            return out
+        torch.cuda.synchronize(device)
+        records = result.cpu().numpy().view(SPECULATIVE_RESULT_DTYPE)[:sessions].copy()
+        return records, accepted_probability.cpu().numpy()[:sessions * draft_count].reshape(sessions, draft_count)
 
     def speculative_verify_host(self, target_logits, draft_logits, proposed, params):
         """moe_speculative_verify_host: numpy float32 logits [draft_count + 1, vocab] / [draft_count, vocab], numpy int32 proposals."""

@@ -57,7 +57,9 @@ struct moe_sampler
     float* spec_dense = nullptr;
     int32_t* spec_residual_token = nullptr;
     float* spec_residual_value = nullptr;
-    uint32_t spec_rows = 0;
+    size_t spec_list_capacity = 0;  // entries of each kept-list array
+    size_t spec_row_capacity = 0;   // entries of each per-row array
+    size_t spec_dense_capacity = 0; // entries of each residual array
 
     // router scratch
     uint32_t* selected_expert = nullptr;
@@ -471,62 +473,94 @@ int moe_sample_batch_ex(moe_sampler* sampler, void* stream_handle, const void* l
     return MOE_STATUS_OK;
 }
 
-int moe_speculative_verify(moe_sampler* sampler, void* stream_handle, const void* target_logits, const void* draft_logits, int dtype,
-                           uint32_t draft_count, uint32_t vocab, size_t row_stride, const int32_t* proposed_tokens,
-                           const moe_row_params* params, float* accepted_probability, moe_speculative_result* result)
+int moe_speculative_verify_batch(moe_sampler* sampler, void* stream_handle, const void* target_logits, const void* draft_logits, int dtype,
+                                 uint32_t sessions, uint32_t draft_count, uint32_t vocab, size_t row_stride, const int32_t* proposed_tokens,
+                                 const moe_row_params* params, float* accepted_probability, moe_speculative_result* results)
 {
-    const uint32_t rows = 2u * draft_count + 1u;
-    if (int status = check_shape(sampler, dtype, rows, vocab, row_stride))
-        return status;
+    if (sampler == nullptr)
+        return MOE_STATUS_INVALID_ARGUMENT;
     if (draft_count > MOE_SPECULATIVE_MAX_DRAFT)
         return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "draft_count exceeds MOE_SPECULATIVE_MAX_DRAFT");
-    if (target_logits == nullptr || params == nullptr || result == nullptr ||
+    const uint64_t total_rows = static_cast<uint64_t>(sessions) * (2u * draft_count + 1u);
+    if (total_rows > sampler->max_rows)
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "sessions * (2 * draft_count + 1) exceeds the handle's max_rows");
+    if (int status = check_shape(sampler, dtype, static_cast<uint32_t>(total_rows), vocab, row_stride))
+        return status;
+    if (sessions == 0)
+        return MOE_STATUS_OK;
+    if (target_logits == nullptr || params == nullptr || results == nullptr ||
         (draft_count > 0 && (draft_logits == nullptr || proposed_tokens == nullptr || accepted_probability == nullptr)))
-        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "target_logits, draft_logits, proposed_tokens, params, accepted_probability and result must not be null");
+        return fail(sampler, MOE_STATUS_INVALID_ARGUMENT, "target_logits, draft_logits, proposed_tokens, params, accepted_probability and results must not be null");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
     DeviceGuard guard(sampler->device);
-    const uint32_t capacity_rows = 2u * MOE_SPECULATIVE_MAX_DRAFT + 1u;
-    if (sampler->spec_rows == 0)
+    const uint32_t target_rows = sessions * (draft_count + 1u);
+    const uint32_t draft_rows = sessions * draft_count;
+    const uint32_t rows = target_rows + draft_rows;
+
+    // a kept list is as long as its Session's top_k, or the vocabulary without Top-K
+    uint32_t kept_stride = 1;
+    for (uint32_t b = 0; b < sessions; ++b)
     {
-        const size_t list_entries = static_cast<size_t>(capacity_rows) * sampler->max_vocab;
-        const auto reserve = [](auto*& pointer, size_t entries) {
-            size_t capacity = 0;
-            return grow(pointer, capacity, entries);
-        };
-        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_kept_token, list_entries));
-        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_kept_probability, list_entries));
-        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_kept_count, capacity_rows));
-        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_token, capacity_rows));
-        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_probability, capacity_rows));
-        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_flags, capacity_rows));
-        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_status, capacity_rows));
-        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_dense, sampler->max_vocab));
-        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_residual_token, sampler->max_vocab));
-        MOE_CUDA_CHECK(sampler, reserve(sampler->spec_residual_value, sampler->max_vocab));
-        sampler->spec_rows = capacity_rows;
+        const uint32_t k = params[b].top_k;
+        kept_stride = std::max(kept_stride, k == 0 || k > vocab ? vocab : k);
     }
-    // every position samples under the Session's options; the target rows come first
-    std::vector<moe_row_params> row_params(draft_count + 1u, params[0]);
-    if (int status = upload_rows(sampler, stream, draft_count + 1u, row_params.data(), nullptr, nullptr))
+    kept_stride = (kept_stride + 3u) & ~3u;
+    const size_t list_entries = static_cast<size_t>(rows) * kept_stride;
+    const size_t dense_entries = static_cast<size_t>(sessions) * vocab;
+    if (list_entries > sampler->spec_list_capacity || rows > sampler->spec_row_capacity || dense_entries > sampler->spec_dense_capacity)
+    {
+        // work queued on other streams may still read the old buffers
+        MOE_CUDA_CHECK(sampler, cudaDeviceSynchronize());
+        size_t capacity = sampler->spec_list_capacity;
+        MOE_CUDA_CHECK(sampler, grow(sampler->spec_kept_token, capacity, list_entries));
+        capacity = sampler->spec_list_capacity;
+        MOE_CUDA_CHECK(sampler, grow(sampler->spec_kept_probability, capacity, list_entries));
+        sampler->spec_list_capacity = capacity;
+        const auto grow_rows = [&](auto*& pointer) {
+            size_t row_capacity = sampler->spec_row_capacity;
+            return grow(pointer, row_capacity, static_cast<size_t>(rows));
+        };
+        MOE_CUDA_CHECK(sampler, grow_rows(sampler->spec_kept_count));
+        MOE_CUDA_CHECK(sampler, grow_rows(sampler->spec_token));
+        MOE_CUDA_CHECK(sampler, grow_rows(sampler->spec_probability));
+        MOE_CUDA_CHECK(sampler, grow_rows(sampler->spec_flags));
+        MOE_CUDA_CHECK(sampler, grow_rows(sampler->spec_status));
+        sampler->spec_row_capacity = std::max<size_t>(sampler->spec_row_capacity, rows);
+        const auto grow_dense = [&](auto*& pointer) {
+            size_t dense_capacity = sampler->spec_dense_capacity;
+            return grow(pointer, dense_capacity, dense_entries);
+        };
+        MOE_CUDA_CHECK(sampler, grow_dense(sampler->spec_dense));
+        MOE_CUDA_CHECK(sampler, grow_dense(sampler->spec_residual_token));
+        MOE_CUDA_CHECK(sampler, grow_dense(sampler->spec_residual_value));
+        sampler->spec_dense_capacity = std::max(sampler->spec_dense_capacity, dense_entries);
+    }
+    // every position samples under its Session's options: the target rows first, then the draft rows
+    std::vector<moe_row_params> row_params(rows);
+    for (uint32_t b = 0; b < sessions; ++b)
+    {
+        std::fill_n(row_params.begin() + static_cast<size_t>(b) * (draft_count + 1u), draft_count + 1u, params[b]);
+        std::fill_n(row_params.begin() + target_rows + static_cast<size_t>(b) * draft_count, draft_count, params[b]);
+    }
+    if (int status = upload_rows(sampler, stream, rows, row_params.data(), nullptr, nullptr))
         return status;
 
-    const uint32_t kept_stride = sampler->max_vocab;
     SampleArgs args = {};
     args.dtype = dtype;
     args.vocab = vocab;
     args.row_stride = row_stride;
-    args.params = sampler->params_dev;
     // the one sample that can be used is that of the target row after all proposals,
     // which the Session would draw with its uniform number draft_count of this step
     args.step_offset = draft_count;
     args.large_top_k = sampler->resident_large_top_k;
     for (int side = 0; side < 2; ++side)
     {
-        const uint32_t first = side == 0 ? 0u : draft_count + 1u;
+        const uint32_t first = side == 0 ? 0u : target_rows;
         args.logits = side == 0 ? target_logits : draft_logits;
-        args.rows = side == 0 ? draft_count + 1u : draft_count;
+        args.rows = side == 0 ? target_rows : draft_rows;
         if (args.rows == 0)
             continue;
+        args.params = sampler->params_dev + first;
         args.token_id = sampler->spec_token + first;
         args.probability = sampler->spec_probability + first;
         args.row_flags = sampler->spec_flags + first;
@@ -545,6 +579,7 @@ int moe_speculative_verify(moe_sampler* sampler, void* stream_handle, const void
         }
     }
     SpeculativeArgs verify = {};
+    verify.sessions = sessions;
     verify.draft_count = draft_count;
     verify.vocab = vocab;
     verify.params = sampler->params_dev;
@@ -561,9 +596,17 @@ int moe_speculative_verify(moe_sampler* sampler, void* stream_handle, const void
     verify.residual_token = sampler->spec_residual_token;
     verify.residual_value = sampler->spec_residual_value;
     verify.accepted_probability = accepted_probability;
-    verify.result = result;
+    verify.result = results;
     MOE_CUDA_CHECK(sampler, launch_speculative_verify(verify, stream));
     return MOE_STATUS_OK;
+}
+
+int moe_speculative_verify(moe_sampler* sampler, void* stream_handle, const void* target_logits, const void* draft_logits, int dtype,
+                           uint32_t draft_count, uint32_t vocab, size_t row_stride, const int32_t* proposed_tokens,
+                           const moe_row_params* params, float* accepted_probability, moe_speculative_result* result)
+{
+    return moe_speculative_verify_batch(sampler, stream_handle, target_logits, draft_logits, dtype, 1, draft_count, vocab, row_stride, proposed_tokens,
+                                        params, accepted_probability, result);
 }
 
 int moe_sample_batch_host(moe_sampler* sampler, const void* logits, int dtype, uint32_t rows, uint32_t vocab, size_t row_stride,

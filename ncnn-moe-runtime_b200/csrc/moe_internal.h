@@ -84,14 +84,16 @@ cudaError_t launch_merge_candidates(const uint64_t* gathered, uint32_t shards, u
                                     uint64_t step_offset, int32_t* token_id, float* probability, uint32_t* row_flags, int32_t* row_status,
                                     int32_t* topk_index, uint32_t topk_stride, cudaStream_t stream);
 
-// Speculative verification: rows 0..draft_count of the row outputs and kept
-// lists are the target positions, rows draft_count+1..2*draft_count the draft positions.
+// Speculative verification of `sessions` Sessions with draft_count proposals each.  Rows of the row
+// outputs and kept lists: Session b's target positions are rows b*(draft_count+1) .. +draft_count,
+// its draft positions rows sessions*(draft_count+1) + b*draft_count .. +draft_count-1.
 struct SpeculativeArgs
 {
+    uint32_t sessions;
     uint32_t draft_count;
     uint32_t vocab;
-    const moe_row_params* params; // device, entry 0 = the Session's options and counters
-    const int32_t* proposed;      // device
+    const moe_row_params* params; // device, by row; a Session's options and counters are those of its first target row
+    const int32_t* proposed;      // device, [sessions * draft_count]
     const int32_t* token;         // per-row sampler outputs
     const float* probability;
     const uint32_t* row_flags;
@@ -100,11 +102,11 @@ struct SpeculativeArgs
     const float* kept_probability;
     const uint32_t* kept_count;
     uint32_t kept_stride;
-    float* dense;             // [vocab] scratch: the residual by token id
-    int32_t* residual_token;  // [vocab] scratch: its positive entries in token-id order
+    float* dense;             // [sessions * vocab] scratch: the residual by token id
+    int32_t* residual_token;  // [sessions * vocab] scratch: its positive entries in token-id order
     float* residual_value;
-    float* accepted_probability;
-    moe_speculative_result* result;
+    float* accepted_probability; // [sessions * draft_count]
+    moe_speculative_result* result; // [sessions]
 };
 
 cudaError_t launch_speculative_verify(const SpeculativeArgs& args, cudaStream_t stream);

@@ -1,4 +1,4 @@
-// Verification step of speculative decoding for one Session
+// Verification step of speculative decoding, one CTA per Session
 // (src/engine/session.cpp:776-880): walk the proposed tokens, accept each with
 // probability min(1, p_target / p_draft) (:800-835), and produce the token
 // that follows the accepted prefix — a draw from the residual distribution
@@ -7,7 +7,7 @@
 //
 // The distributions come from the sampler kernels (kept-candidate lists, the
 // vectors sampling_distribution returns); this kernel is the control flow on
-// top of them.  One CTA: the walk is sequential by nature (position j is only
+// top of them.  One CTA per Session: the walk is sequential by nature (position j is only
 // looked at when 0..j-1 were accepted), the look-ups and the residual are
 // spread over the threads.  The residual sums run in token-id order like the
 // reference's std::accumulate over its dense vector; zeros change nothing in
@@ -56,7 +56,16 @@ __global__ void __launch_bounds__(kVerifyThreads, 1) speculative_verify_kernel(c
     const int lane = tid & 31;
     const int warp = tid >> 5;
     const uint32_t n = s.draft_count;
-    const moe_row_params p = s.params[0];
+    const uint32_t session = blockIdx.x;
+    // rows of the sampler outputs: every Session's draft_count + 1 target positions first, then every Session's draft positions
+    const uint32_t target_first = session * (n + 1u);
+    const uint32_t draft_first = s.sessions * (n + 1u) + session * n;
+    const moe_row_params p = s.params[target_first];
+    const int32_t* const proposed_tokens = s.proposed + static_cast<size_t>(session) * n;
+    float* const accepted_probability = s.accepted_probability + static_cast<size_t>(session) * n;
+    float* const dense = s.dense + static_cast<size_t>(session) * s.vocab;
+    int32_t* const residual_token = s.residual_token + static_cast<size_t>(session) * s.vocab;
+    float* const residual_value = s.residual_value + static_cast<size_t>(session) * s.vocab;
     const bool greedy = p.temperature == 0.0f;
 
     uint32_t accepted = 0;
@@ -65,9 +74,9 @@ __global__ void __launch_bounds__(kVerifyThreads, 1) speculative_verify_kernel(c
     bool rejected = false;
     while (accepted < n)
     {
-        const uint32_t target_row = accepted;
-        const uint32_t draft_row = n + 1 + accepted;
-        const int32_t proposed = s.proposed[accepted];
+        const uint32_t target_row = target_first + accepted;
+        const uint32_t draft_row = draft_first + accepted;
+        const int32_t proposed = proposed_tokens[accepted];
         if (s.row_status[target_row] != MOE_ROW_OK)
         {
             status = s.row_status[target_row];
@@ -78,7 +87,7 @@ __global__ void __launch_bounds__(kVerifyThreads, 1) speculative_verify_kernel(c
             if (s.token[target_row] != proposed)
                 break; // session.cpp:790-794
             if (tid == 0)
-                s.accepted_probability[accepted] = 1.0f;
+                accepted_probability[accepted] = 1.0f;
         }
         else
         {
@@ -107,7 +116,7 @@ __global__ void __launch_bounds__(kVerifyThreads, 1) speculative_verify_kernel(c
                 break;
             }
             if (tid == 0)
-                s.accepted_probability[accepted] = target_probability;
+                accepted_probability[accepted] = target_probability;
         }
         ++accepted;
     }
@@ -117,8 +126,8 @@ __global__ void __launch_bounds__(kVerifyThreads, 1) speculative_verify_kernel(c
     if (status == MOE_ROW_OK && rejected)
     {
         // ---- residual distribution of the rejected position (session.cpp:150-202) ----
-        const uint32_t target_row = accepted;
-        const uint32_t draft_row = n + 1 + accepted;
+        const uint32_t target_row = target_first + accepted;
+        const uint32_t draft_row = draft_first + accepted;
         const size_t stride = s.kept_stride;
         const int32_t* target_token = s.kept_token + target_row * stride;
         const float* target_probability = s.kept_probability + target_row * stride;
@@ -127,16 +136,16 @@ __global__ void __launch_bounds__(kVerifyThreads, 1) speculative_verify_kernel(c
         const uint32_t target_count = min(s.kept_count[target_row], s.kept_stride);
         const uint32_t draft_count = min(s.kept_count[draft_row], s.kept_stride);
         for (uint32_t i = tid; i < s.vocab; i += kVerifyThreads)
-            s.dense[i] = 0.0f;
+            dense[i] = 0.0f;
         __syncthreads();
         for (uint32_t i = tid; i < target_count; i += kVerifyThreads)
-            s.dense[target_token[i]] = target_probability[i];
+            dense[target_token[i]] = target_probability[i];
         __syncthreads();
         for (uint32_t i = tid; i < draft_count; i += kVerifyThreads)
         {
             const int32_t id = draft_token[i];
-            const float reduced = __fsub_rn(s.dense[id], draft_probability[i]);
-            s.dense[id] = reduced > 0.0f ? reduced : 0.0f; // std::max(0.0f, ...)
+            const float reduced = __fsub_rn(dense[id], draft_probability[i]);
+            dense[id] = reduced > 0.0f ? reduced : 0.0f; // std::max(0.0f, ...)
         }
         if (tid == 0)
             sh.cursor = 0;
@@ -145,7 +154,7 @@ __global__ void __launch_bounds__(kVerifyThreads, 1) speculative_verify_kernel(c
         for (uint32_t base = 0; base < s.vocab; base += kVerifyThreads)
         {
             const uint32_t id = base + tid;
-            const float value = id < s.vocab ? s.dense[id] : 0.0f;
+            const float value = id < s.vocab ? dense[id] : 0.0f;
             const bool positive = value > 0.0f;
             const unsigned voters = __ballot_sync(kFullMask, positive);
             if (lane == 0)
@@ -157,8 +166,8 @@ __global__ void __launch_bounds__(kVerifyThreads, 1) speculative_verify_kernel(c
             if (positive)
             {
                 const uint32_t slot = before + __popc(voters & ((1u << lane) - 1u));
-                s.residual_token[slot] = static_cast<int32_t>(id);
-                s.residual_value[slot] = value;
+                residual_token[slot] = static_cast<int32_t>(id);
+                residual_value[slot] = value;
             }
             __syncthreads();
             if (tid == kVerifyThreads - 1)
@@ -169,7 +178,7 @@ __global__ void __launch_bounds__(kVerifyThreads, 1) speculative_verify_kernel(c
         __syncthreads();
         // std::accumulate over the dense vector (session.cpp:171-176) = the positive entries added in token-id
         // order; replayed bit-exactly by the whole block (the entries are not sorted by value)
-        const float normalizer = block_sequential_sum<kVerifyThreads, 8, false>(s.residual_value, positives, kSeqSumOnly, 0.0f, sh.seq).acc;
+        const float normalizer = block_sequential_sum<kVerifyThreads, 8, false>(residual_value, positives, kSeqSumOnly, 0.0f, sh.seq).acc;
         if (positives == 0 || !(normalizer - normalizer == 0.0f) || normalizer <= 0.0f)
         {
             if (tid == 0)
@@ -183,14 +192,14 @@ __global__ void __launch_bounds__(kVerifyThreads, 1) speculative_verify_kernel(c
         {
             const float uniform = philox_uniform(p.seed, p.row_id, p.step + used);
             const float sample_value = __fmul_rn(uniform, normalizer); // uniform_real_distribution<float>(0, normalizer)
-            const SeqResult draw = block_sequential_sum<kVerifyThreads, 8, false>(s.residual_value, positives, kSeqExceedBound, sample_value, sh.seq);
+            const SeqResult draw = block_sequential_sum<kVerifyThreads, 8, false>(residual_value, positives, kSeqExceedBound, sample_value, sh.seq);
             // session.cpp:189-197: the last positive entry if the sum never passes the draw
             const uint32_t chosen = draw.stopped ? draw.taken - 1u : positives - 1u;
             if (tid == 0)
             {
                 sh.decision = 0;
-                sh.cursor = static_cast<uint32_t>(s.residual_token[chosen]);
-                sh.found[0] = __fdiv_rn(s.residual_value[chosen], normalizer);
+                sh.cursor = static_cast<uint32_t>(residual_token[chosen]);
+                sh.found[0] = __fdiv_rn(residual_value[chosen], normalizer);
             }
         }
         __syncthreads();
@@ -210,7 +219,7 @@ __global__ void __launch_bounds__(kVerifyThreads, 1) speculative_verify_kernel(c
     {
         // every proposal accepted, or greedy: the sample of the next target row (session.cpp:871-874);
         // its uniform is number `used` of this step, which is draft_count when all were accepted
-        const uint32_t row = accepted;
+        const uint32_t row = target_first + accepted;
         status = s.row_status[row];
         if (status == MOE_ROW_OK)
         {
@@ -229,13 +238,13 @@ __global__ void __launch_bounds__(kVerifyThreads, 1) speculative_verify_kernel(c
         result.uniforms_used = used;
         result.status = status;
         result.flags = 0;
-        *s.result = result;
+        s.result[session] = result;
     }
 }
 
 cudaError_t launch_speculative_verify(const SpeculativeArgs& args, cudaStream_t stream)
 {
-    speculative_verify_kernel<<<1, kVerifyThreads, 0, stream>>>(args);
+    speculative_verify_kernel<<<args.sessions, kVerifyThreads, 0, stream>>>(args);
     return cudaGetLastError();
 }
 

@@ -123,3 +123,48 @@ def test_host_buffer_entry_point_gives_the_same_outcome(pkg, parity, torch_cuda)
             np.testing.assert_array_equal(host["accepted_probability"].view(np.uint32), device["accepted_probability"].view(np.uint32))
     finally:
         sampler.close()
+
+
+def test_batch_of_sessions_equals_each_session_alone(pkg, parity, torch_cuda):
+    """moe_speculative_verify_batch: Sessions with their own options, seeds and steps verified side by side give, each,
+    the outcome of the reference loop for that Session (and the bits of the one-Session call)."""
+    rng = np.random.default_rng(2025)
+    vocab, draft_count = 4099, 4
+    options = [(1.0, 40, 0.95, 0.0), (0.7, 0, 0.9, 0.02), (0.0, 0, 1.0, 0.0), (1.3, 8, 1.0, 0.0), (1.0, 0, 1.0, 0.0), (0.9, 64, 0.8, 0.0),
+               (1.0, 4, 1.0, 0.0)]
+    sessions = len(options)
+    targets, drafts, proposals = [], [], []
+    for b, option in enumerate(options):
+        target, draft, proposed = _case(rng, vocab, draft_count, *option, [0.05, 0.4, 1.5][b % 3], parity.port)
+        if b == sessions - 1:
+            proposed[0] = int(np.argmin(draft[0]))   # outside the draft's kept candidates: this Session fails, the others do not
+        targets.append(target), drafts.append(draft), proposals.append(proposed)
+    params = np.zeros(sessions, dtype=pkg.ROW_PARAMS_DTYPE)
+    for b, option in enumerate(options):
+        params[b]["temperature"], params[b]["top_k"], params[b]["top_p"], params[b]["min_p"] = option
+        params[b]["seed"], params[b]["row_id"], params[b]["step"] = 31 + b, 100 + b, 7 * b
+    sampler = pkg.Sampler(max_rows=sessions * (2 * draft_count + 1), max_vocab=vocab)
+    try:
+        records, accepted_probability = sampler.speculative_verify_batch(torch_cuda.from_numpy(np.stack(targets)).cuda(),
+                                                                         torch_cuda.from_numpy(np.stack(drafts)).cuda(),
+                                                                         torch_cuda.from_numpy(np.stack(proposals)).cuda(), params)
+        failures = 0
+        for b, option in enumerate(options):
+            alone = _compare(pkg, sampler, torch_cuda, parity, targets[b], drafts[b], proposals[b], option, seed=31 + b, row_id=100 + b, step=7 * b)
+            for name in ("accepted", "next_token", "uniforms_used", "status"):
+                assert records[b][name] == alone[name], (b, name, records[b], alone)
+            assert records[b]["next_probability"].view(np.uint32) == np.float32(alone["next_probability"]).view(np.uint32)
+            kept = int(records[b]["accepted"])
+            np.testing.assert_array_equal(accepted_probability[b, :kept].view(np.uint32), alone["accepted_probability"].view(np.uint32))
+            failures += int(alone["status"] != 0)
+        assert failures == 1
+        # no Sessions: nothing to do; too many for the handle: refused
+        assert pkg.library().moe_speculative_verify_batch(sampler._handle, None, None, None, pkg.DTYPE_F32, 0, draft_count, vocab, vocab,
+                                                          None, None, None, None) == 0
+        with pytest.raises(Exception):
+            sampler.speculative_verify_batch(torch_cuda.zeros((sessions + 1, draft_count + 1, vocab), device="cuda"),
+                                             torch_cuda.zeros((sessions + 1, draft_count, vocab), device="cuda"),
+                                             torch_cuda.zeros((sessions + 1, draft_count), dtype=torch_cuda.int32, device="cuda"),
+                                             np.zeros(sessions + 1, dtype=pkg.ROW_PARAMS_DTYPE))
+    finally:
+        sampler.close()
