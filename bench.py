@@ -946,7 +946,7 @@ def main() -> int:
             try:
                 entry = function(argparse.Namespace(steps=128, warmup=3), as_dict=True)
                 table[name] = {k: entry[k] for k in entry if k in ("metric", "value", "unit", "ms_per_step", "regroup_gather", "routes_equal_to_reference",
-                                                                  "results_equal_to_reference", "cpu_baseline")}
+                                                                  "results_equal_to_reference", "cpu_baseline", "batched")}
             except Exception as error:
                 table[name] = {"error": f"{type(error).__name__}: {error}"}
         line["config"]["workloads"] = table

@@ -25,8 +25,12 @@ __device__ unsigned long long g_exact_cycles[16];
 extern "C" void moe_debug_exact_cycles(unsigned long long* out, int reset)
 {
     cudaMemcpyFromSymbol(out, g_exact_cycles, sizeof(unsigned long long) * 16);
+    cudaMemcpyFromSymbol(out + 14, g_seq_debug, sizeof(unsigned long long) * 2);
+    cudaMemcpyFromSymbol(out + 1, g_seq_debug, sizeof(unsigned long long) * 4, sizeof(unsigned long long) * 2);
     if (reset)
     {
+        unsigned long long none[8] = {};
+        cudaMemcpyToSymbol(g_seq_debug, none, sizeof(none));
         unsigned long long zeros[16] = {};
         cudaMemcpyToSymbol(g_exact_cycles, zeros, sizeof(zeros));
     }
@@ -756,7 +760,8 @@ __device__ bool exact_row_bf16_runs(const SampleArgs& a, uint32_t row, const moe
     __syncthreads();
     // The histogram has served its purpose: its shared memory now holds the run arrays, which the
     // sums below walk many times (4 * runs <= 4 * kMaxRuns words fit the kHistogramBins words).
-    static_assert(4u * kMaxRuns <= kHistogramBins, "the run arrays reuse the histogram's shared memory");
+    static_assert(5u * kMaxRuns <= kHistogramBins, "the run arrays and the replay guide reuse the histogram's shared memory");
+    float* const run_guide = reinterpret_cast<float*>(hist + 4u * kMaxRuns); // approximate prefix sums of the numerators
     {
         float* shared_value = reinterpret_cast<float*>(hist);
         uint32_t* shared_count = hist + kMaxRuns;
@@ -784,7 +789,9 @@ __device__ bool exact_row_bf16_runs(const SampleArgs& a, uint32_t row, const moe
     for (uint32_t r = tid; r < runs; r += kExactThreads)
         run_value[r] = exact_expf(scaled_offset(key_to_float(run_key[r]), p.temperature, peak));
     __syncthreads();
-    const SeqRunsResult normaliser = block_sequential_sum_runs<kExactThreads, kRunsPerThread>(run_value, run_count, run_cum, runs, have, kSeqSumOnly, 0.0f, sh.seq_runs);
+    block_runs_prefix_guide<kExactThreads, kRunsPerThread>(run_value, run_count, runs, run_guide, sh.warp_sum);
+    const SeqRunsResult normaliser = block_sequential_sum_runs<kExactThreads, kRunsPerThread>(run_value, run_count, run_cum, runs, have, kSeqSumOnly, 0.0f, sh.seq_runs,
+                                                                                              run_guide, 1.0f);
     if (normaliser.unsupported)
         return false;
     MOE_EXACT_MARK(11);
@@ -822,7 +829,8 @@ __device__ bool exact_row_bf16_runs(const SampleArgs& a, uint32_t row, const moe
             return false; // the prefix may go on below the window
     }
     // Top-P: first prefix whose running sum reaches top_p; never reached: the whole list stays
-    const SeqRunsResult nucleus = block_sequential_sum_runs<kExactThreads, kRunsPerThread>(run_value, run_count, run_cum, runs, min(allowed, have), kSeqReachBound, p.top_p, sh.seq_runs);
+    const SeqRunsResult nucleus = block_sequential_sum_runs<kExactThreads, kRunsPerThread>(run_value, run_count, run_cum, runs, min(allowed, have), kSeqReachBound, p.top_p, sh.seq_runs,
+                                                                                           run_guide, 1.0f / total);
     if (nucleus.unsupported)
         return false;
     MOE_EXACT_MARK(12);
@@ -844,7 +852,8 @@ __device__ bool exact_row_bf16_runs(const SampleArgs& a, uint32_t row, const moe
             run_value[r] = __fdiv_rn(run_value[r], kept_total);
         __syncthreads();
         const float uniform = philox_uniform(p.seed, p.row_id, p.step + a.step_offset);
-        const SeqRunsResult draw = block_sequential_sum_runs<kExactThreads, kRunsPerThread>(run_value, run_count, run_cum, runs, kept_have, kSeqExceedBound, uniform, sh.seq_runs);
+        const SeqRunsResult draw = block_sequential_sum_runs<kExactThreads, kRunsPerThread>(run_value, run_count, run_cum, runs, kept_have, kSeqExceedBound, uniform, sh.seq_runs,
+                                                                                            run_guide, 1.0f / (total * kept_total));
         if (draw.unsupported)
             return false;
         uint32_t chosen_rank;
@@ -894,8 +903,22 @@ __device__ bool exact_row_bf16_runs(const SampleArgs& a, uint32_t row, const moe
     };
     const uint32_t whole_end = aligned ? begin + ((end - begin) & ~7u) : begin; // vectors first, the ragged rest one by one
     uint32_t in_range = 0;
-    for (uint32_t i = begin; i < whole_end; i += 8)
-        in_range += __popc(vector_mask(*reinterpret_cast<const uint4*>(bits + i)));
+    {
+        // four independent 16-byte loads per trip: the pass is bound by their latency
+        uint32_t i = begin;
+        for (; i + 32u <= whole_end; i += 32u)
+        {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                v[u] = *reinterpret_cast<const uint4*>(bits + i + 8u * u);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                in_range += __popc(vector_mask(v[u]));
+        }
+        for (; i < whole_end; i += 8)
+            in_range += __popc(vector_mask(*reinterpret_cast<const uint4*>(bits + i)));
+    }
     for (uint32_t i = whole_end; i < end; ++i)
         in_range += matches(bits[i]) ? 1u : 0u;
     uint32_t scan = in_range;

@@ -21,6 +21,13 @@
 
 #include "moe_seqscan.cuh"
 
+#ifdef MOE_PHASE_TIMERS
+__device__ unsigned long long g_seq_debug[8]; // rounds, runs looked at, cycles: to barrier 1, to barrier 2, rest, search
+#define SEQ_LAP(slot) do { if (tid == 0) { const long long now_ = clock64(); atomicAdd(&g_seq_debug[slot], static_cast<unsigned long long>(now_ - lap_)); lap_ = now_; } } while (0)
+#else
+#define SEQ_LAP(slot) do {} while (0)
+#endif
+
 namespace moe {
 
 struct SeqRunsResult
@@ -31,10 +38,14 @@ struct SeqRunsResult
     bool unsupported; // the accumulator left the range this replay handles: the caller must use another path
 };
 
+constexpr int kSeqRunsHead = 192; // addends at the head of a sequence that are added literally
+
 template<int kThreads>
 struct SeqRunsShared
 {
     uint32_t warp_pair[kThreads / 32][2];
+    float head_addend[kSeqRunsHead];   // the first addends of the sequence, one by one
+    uint32_t head_run[kSeqRunsHead];   // ... and the run each belongs to
     uint32_t first_event; // smallest run offset in the chunk with a stop or a carry
     uint32_t event_copies; // copies of that run consumed, the event's copy included
     float acc;
@@ -54,12 +65,63 @@ __device__ __forceinline__ uint32_t seq_clamp64(unsigned long long v)
     return v < kSeqSaturate ? static_cast<uint32_t>(v) : kSeqSaturate;
 }
 
+// Approximate inclusive prefix sums of count[r] * x[r] over the runs, by the whole block
+// (plain parallel fp32 sums: a guide for the replay below, never a result).
+// warp_scratch: kThreads / 32 floats of shared memory.  Ends with a barrier.
+template<int kThreads, int kItems>
+__device__ void block_runs_prefix_guide(const float* x, const uint32_t* count, uint32_t runs, float* prefix, float* warp_scratch)
+{
+    const uint32_t tid = threadIdx.x;
+    const uint32_t lane = tid & 31u;
+    const uint32_t warp = tid >> 5;
+    const uint32_t first = tid * kItems;
+    float local[kItems];
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kItems; ++j)
+    {
+        const uint32_t r = first + j;
+        if (r < runs)
+            sum += static_cast<float>(count[r]) * x[r];
+        local[j] = sum;
+    }
+    float scan = sum;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1)
+    {
+        const float other = __shfl_up_sync(kFullMask, scan, offset);
+        if (lane >= static_cast<uint32_t>(offset))
+            scan += other;
+    }
+    if (lane == 31)
+        warp_scratch[warp] = scan;
+    __syncthreads();
+    float before = scan - sum;
+    for (uint32_t w = 0; w < warp; ++w)
+        before += warp_scratch[w];
+#pragma unroll
+    for (int j = 0; j < kItems; ++j)
+    {
+        const uint32_t r = first + j;
+        if (r < runs)
+            prefix[r] = before + local[j];
+    }
+    __syncthreads();
+}
+
 // x[r], count[r], cum[r] (= addends before run r) for r < runs, readable by every
 // thread.  Only the first `limit` addends of the sequence take part.  All
 // threads of the block call this with the same arguments; ends with a barrier.
+//
+// `guide` (optional): guide[r] * guide_scale ~ the sum of count * x over the runs 0..r
+// (block_runs_prefix_guide of the same runs, possibly in other units).  A round of the
+// replay covers one binade of the accumulator; with the guide it only looks at the runs
+// expected to fall into that binade (plus a margin) instead of all that remain.  A guide
+// that is off costs an extra round, never a different result.
 template<int kThreads, int kItems>
 __device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, const uint32_t* count, const uint32_t* cum, uint32_t runs, uint32_t limit,
-                                                                SeqStop stop, float bound, SeqRunsShared<kThreads>& sh)
+                                                                SeqStop stop, float bound, SeqRunsShared<kThreads>& sh,
+                                                                const float* guide = nullptr, float guide_scale = 1.0f)
 {
     const uint32_t tid = threadIdx.x;
     const uint32_t lane = tid & 31u;
@@ -80,9 +142,94 @@ __device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, 
     uint32_t done = 1;    // copies of it already added
     if ((stop == kSeqReachBound && acc >= bound) || (stop == kSeqExceedBound && bound < acc))
         return SeqRunsResult{acc, 1u, true, false};
+    // The head of the sequence, literally: the first addends carry the accumulator through several
+    // binades with a handful of addends each, where a round of the block (below) costs far more
+    // than the adds themselves.  The threads lay the first addends out one by one, then one warp
+    // adds them in order while the others wait.
+    {
+        const uint32_t total_addends = min(limit, cum[runs - 1u] + count[runs - 1u]);
+        const uint32_t head = min(static_cast<uint32_t>(kSeqRunsHead), total_addends);
+        if (tid < head)
+        {
+            // the run of addend number tid: the last run that starts at or before it (runs are not empty, so it is <= tid)
+            uint32_t lo = 0, hi = min(runs - 1u, tid);
+            while (lo < hi)
+            {
+                const uint32_t mid = lo + (hi - lo + 1u) / 2u;
+                if (cum[mid] <= tid)
+                    lo = mid;
+                else
+                    hi = mid - 1u;
+            }
+            sh.head_addend[tid] = x[lo];
+            sh.head_run[tid] = lo;
+        }
+        __syncthreads();
+        if (warp == 0)
+        {
+            float a = acc;
+            uint32_t taken = 1;
+            bool stopped = false;
+            // eight adds per trip, then one test: the accumulator does not decrease, so a bound met by
+            // any of the eight is met by the last (adding the +0 padding changes nothing)
+            while (taken < head)
+            {
+                const uint32_t group = min(8u, head - taken);
+                float value[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    value[j] = static_cast<uint32_t>(j) < group ? sh.head_addend[taken + j] : 0.0f;
+                float partial[8];
+                float t = a;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                {
+                    t = __fadd_rn(t, value[j]);
+                    partial[j] = t;
+                }
+                if ((stop == kSeqReachBound && t >= bound) || (stop == kSeqExceedBound && bound < t))
+                {
+                    int first = 7;
+#pragma unroll
+                    for (int j = 6; j >= 0; --j)
+                        if ((stop == kSeqReachBound && partial[j] >= bound) || (stop == kSeqExceedBound && bound < partial[j]))
+                            first = j;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (j == first)
+                            a = partial[j];
+                    taken += static_cast<uint32_t>(first) + 1u;
+                    stopped = true;
+                    break;
+                }
+                a = t;
+                taken += group;
+            }
+            if (lane == 0)
+            {
+                const uint32_t last_run = sh.head_run[taken - 1u];
+                sh.acc = a;
+                sh.first_event = last_run;
+                sh.event_copies = taken - cum[last_run];
+                sh.stopped = stopped ? 1u : 0u;
+            }
+        }
+        __syncthreads();
+        acc = sh.acc;
+        run = sh.first_event;
+        done = sh.event_copies;
+        const bool stopped = sh.stopped != 0;
+        __syncthreads();
+        if (stopped)
+            return SeqRunsResult{acc, cum[run] + done, true, false};
+    }
+#ifdef MOE_PHASE_TIMERS
+    long long lap_ = clock64();
+#endif
     for (;;)
     {
-        while (run < runs && done >= copies_of(run))
+        SEQ_LAP(4);
+        while (run < runs && cum[run] < limit && done >= copies_of(run))
         {
             ++run;
             done = 0;
@@ -103,20 +250,50 @@ __device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, 
         // addend is below half a unit nothing changes any more and no stop can fire
         if (x[run] < 0.5f * unit)
             break;
-        const uint32_t chunk = min(static_cast<uint32_t>(kThreads * kItems), runs - run);
+        uint32_t chunk = min(static_cast<uint32_t>(kThreads * kItems), runs - run);
+        if (guide != nullptr)
+        {
+            // first run whose guide value reaches the top of this binade: every warp searches alike,
+            // its lanes probing 32 places of the remaining range at a time
+            const float top = 2.0f * __uint_as_float(static_cast<uint32_t>(acc_biased) << 23);
+            uint32_t lo = run, hi = run + chunk; // the answer lies in [lo, hi]; guide[hi] counts as reaching
+            while (lo < hi)
+            {
+                const uint32_t span = hi - lo;
+                const uint32_t stride = (span + 31u) / 32u;
+                const uint32_t probe = lo + lane * stride; // ascending over the lanes
+                const bool reaches = probe >= hi || guide[probe] * guide_scale >= top;
+                const unsigned votes = __ballot_sync(kFullMask, reaches);
+                const uint32_t first_lane = votes != 0u ? static_cast<uint32_t>(__ffs(votes)) - 1u : 32u; // 32: beyond every probe
+                hi = min(hi, lo + first_lane * stride);
+                lo = first_lane == 0u ? hi : lo + (first_lane - 1u) * stride + 1u;
+            }
+            const uint32_t expected = lo - run + 1u;
+            chunk = min(chunk, max(expected + (expected >> 5) + 8u, 64u));
+        }
 
-        // my kItems consecutive runs of the chunk
+        SEQ_LAP(5);
+#ifdef MOE_PHASE_TIMERS
+        if (tid == 0)
+        {
+            atomicAdd(&g_seq_debug[0], 1ull);
+            atomicAdd(&g_seq_debug[1], static_cast<unsigned long long>(chunk));
+        }
+#endif
+        // my consecutive runs of the chunk: as few per thread as the chunk allows (the round is
+        // as long as one thread's work)
+        const uint32_t per_thread = (chunk + kThreads - 1u) / kThreads;
         float mine[kItems];
         uint32_t copies[kItems];
         uint32_t t0 = 0, t1 = 0;
-        const uint32_t first = tid * kItems;
+        const uint32_t first = tid * per_thread;
 #pragma unroll
         for (int j = 0; j < kItems; ++j)
         {
             const uint32_t offset = first + j;
             mine[j] = 0.0f;
             copies[j] = 0;
-            if (offset < chunk)
+            if (j < per_thread && offset < chunk)
             {
                 mine[j] = x[run + offset];
                 copies[j] = copies_of(run + offset) - (offset == 0 ? done : 0u);
@@ -128,6 +305,8 @@ __device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, 
 #pragma unroll
             for (int j = 0; j < kItems; ++j)
             {
+                if (j >= per_thread)
+                    break;
                 uint32_t d0, d1;
                 seq_element(mine[j], inverse_unit, d0, d1);
                 const uint32_t e0 = seq_clamp64(seq_run_steps(d0, d1, copies[j], 0u));
@@ -144,7 +323,7 @@ __device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, 
             }
         }
         // warps whose runs all lie beyond the chunk only keep the barriers company
-        const bool warp_active = warp * 32u * kItems < chunk;
+        const bool warp_active = warp * 32u * per_thread < chunk;
         uint32_t s0 = t0, s1 = t1;
         if (warp_active)
         {
@@ -168,6 +347,7 @@ __device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, 
             sh.stopped = 0;
         }
         __syncthreads();
+        SEQ_LAP(2);
         const uint32_t start_parity = start_integer & 1u;
         uint32_t before = 0; // integer steps taken before my first run
         if (warp_active)
@@ -203,7 +383,7 @@ __device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, 
         for (int j = 0; j < kItems; ++j)
         {
             const uint32_t offset = first + j;
-            if (first < chunk && offset < chunk && event == 0xFFFFFFFFu && copies[j] != 0u)
+            if (j < per_thread && offset < chunk && event == 0xFFFFFFFFu && copies[j] != 0u)
             {
                 uint32_t d0, d1;
                 seq_element(mine[j], inverse_unit, d0, d1);
@@ -225,12 +405,13 @@ __device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, 
         if (event != 0xFFFFFFFFu)
             atomicMin(&sh.first_event, event);
         __syncthreads();
+        SEQ_LAP(3);
         const uint32_t first_event = sh.first_event;
         if (first_event == 0xFFFFFFFFu)
         {
             // the whole chunk inside the binade, no stop: the thread that owns the last run holds the final integer
             const uint32_t last_offset = chunk - 1;
-            if (last_offset / kItems == tid)
+            if (last_offset / per_thread == tid)
                 sh.acc = __uint2float_rn(running) * unit;
             __syncthreads();
             acc = sh.acc;
@@ -239,7 +420,7 @@ __device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, 
             __syncthreads();
             continue;
         }
-        if (first_event / kItems == tid)
+        if (first_event / per_thread == tid)
         {
             // `running` is the exact integer before the event run.  Find the first copy m (1-based)
             // after which the integer has left the binade or the bound is met.
