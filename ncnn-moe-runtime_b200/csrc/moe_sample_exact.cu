@@ -887,80 +887,102 @@ __device__ bool exact_row_bf16_runs(const SampleArgs& a, uint32_t row, const moe
     MOE_EXACT_MARK(13);
 
     // ---- the occurrence-th lowest index that carries the chosen value ------------------------
-    // each thread owns a contiguous range of the row (whole 16-byte vectors), so that "lowest" is a
-    // prefix count over threads
-    const uint32_t range = ((vocab + kExactThreads - 1u) / kExactThreads + 7u) & ~7u;
-    const uint32_t begin = min(vocab, tid * range);
-    const uint32_t end = min(vocab, begin + range);
-    const auto matches = [&](uint16_t pattern) -> bool { return pattern == wanted || (((pattern | wanted) & 0x7FFFu) == 0u); };
+    // Each warp owns a contiguous part of the row (whole 16-byte vectors) and reads it with
+    // consecutive lanes on consecutive vectors, so "lowest" is a prefix count over warps, then
+    // over the trips of one warp, then over its lanes.
     const bool aligned = (reinterpret_cast<uintptr_t>(bits) & 15u) == 0u;
+    const bool wanted_is_zero = (wanted & 0x7FFFu) == 0u; // +0 and -0 are one value
+    const uint32_t wanted_pair = static_cast<uint32_t>(wanted) | (static_cast<uint32_t>(wanted) << 16);
+    const auto matches = [&](uint16_t pattern) -> bool { return wanted_is_zero ? (pattern & 0x7FFFu) == 0u : pattern == wanted; };
+    // bits 2i, 2i+1 of the result = the two logits of word i carry the value
+    const auto pair_mask = [&](uint32_t word) -> uint32_t {
+        const uint32_t differs = wanted_is_zero ? (word & 0x7FFF7FFFu) : (word ^ wanted_pair);
+        return ((differs & 0xFFFFu) == 0u ? 1u : 0u) | ((differs >> 16) == 0u ? 2u : 0u);
+    };
     // bit i of the mask = the i-th logit of the vector carries the value
     const auto vector_mask = [&](const uint4& v) -> uint32_t {
-        return (matches(static_cast<uint16_t>(v.x)) ? 1u : 0u) | (matches(static_cast<uint16_t>(v.x >> 16)) ? 2u : 0u) |
-               (matches(static_cast<uint16_t>(v.y)) ? 4u : 0u) | (matches(static_cast<uint16_t>(v.y >> 16)) ? 8u : 0u) |
-               (matches(static_cast<uint16_t>(v.z)) ? 16u : 0u) | (matches(static_cast<uint16_t>(v.z >> 16)) ? 32u : 0u) |
-               (matches(static_cast<uint16_t>(v.w)) ? 64u : 0u) | (matches(static_cast<uint16_t>(v.w >> 16)) ? 128u : 0u);
+        return pair_mask(v.x) | (pair_mask(v.y) << 2) | (pair_mask(v.z) << 4) | (pair_mask(v.w) << 6);
     };
-    const uint32_t whole_end = aligned ? begin + ((end - begin) & ~7u) : begin; // vectors first, the ragged rest one by one
-    uint32_t in_range = 0;
+    // mask of the eight logits that start at `at` (a multiple of 8 inside the warp's part), by vector or one by one
+    const auto mask_at = [&](uint32_t at, uint32_t end) -> uint32_t {
+        if (at >= end)
+            return 0u;
+        if (aligned && at + 8u <= end)
+            return vector_mask(*reinterpret_cast<const uint4*>(bits + at));
+        uint32_t mask = 0;
+        for (uint32_t j = 0; j < 8u && at + j < end; ++j)
+            mask |= matches(bits[at + j]) ? (1u << j) : 0u;
+        return mask;
+    };
+    const uint32_t part = ((vocab + kExactWarps - 1u) / kExactWarps + 255u) & ~255u; // whole trips of 32 vectors
+    const uint32_t begin = min(vocab, warp * part);
+    const uint32_t end = min(vocab, begin + part);
+    const uint32_t trips = (end - begin + 255u) / 256u;
+    // lane g keeps the count of trip group g, so that the second look goes straight to the right trips
+    const uint32_t trips_per_group = max(1u, (part / 256u + 31u) / 32u);
+    uint32_t in_part = 0, group_total = 0;
+    for (uint32_t trip = 0; trip < trips; trip += 4u)
     {
-        // four independent 16-byte loads per trip: the pass is bound by their latency
-        uint32_t i = begin;
-        for (; i + 32u <= whole_end; i += 32u)
+        uint32_t mask[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            mask[u] = trip + u < trips ? mask_at(begin + (trip + u) * 256u + lane * 8u, end) : 0u;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
         {
-            uint4 v[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-                v[u] = *reinterpret_cast<const uint4*>(bits + i + 8u * u);
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-                in_range += __popc(vector_mask(v[u]));
+            const uint32_t total = __reduce_add_sync(kFullMask, __popc(mask[u]));
+            in_part += total;
+            if (lane == (trip + u) / trips_per_group)
+                group_total += total;
         }
-        for (; i < whole_end; i += 8)
-            in_range += __popc(vector_mask(*reinterpret_cast<const uint4*>(bits + i)));
     }
-    for (uint32_t i = whole_end; i < end; ++i)
-        in_range += matches(bits[i]) ? 1u : 0u;
-    uint32_t scan = in_range;
-#pragma unroll
-    for (int offset = 1; offset < 32; offset <<= 1)
-    {
-        const uint32_t other = __shfl_up_sync(kFullMask, scan, offset);
-        if (lane >= static_cast<uint32_t>(offset))
-            scan += other;
-    }
-    if (lane == 31)
-        sh.warp_count[warp] = scan;
+    if (lane == 0)
+        sh.warp_count[warp] = in_part;
     if (tid == 0)
         sh.chosen_index = 0xFFFFFFFFu;
     __syncthreads();
-    uint32_t before = scan - in_range;
+    uint32_t before = 0;
     for (uint32_t w = 0; w < warp; ++w)
         before += sh.warp_count[w];
-    if (occurrence >= before && occurrence < before + in_range)
+    if (occurrence >= before && occurrence < before + in_part)
     {
-        uint32_t seen = before;
-        uint32_t found = 0xFFFFFFFFu;
-        for (uint32_t i = begin; i < whole_end && found == 0xFFFFFFFFu; i += 8)
+        // this warp's part holds it: the group of trips first, then the trip, then the lane
+        uint32_t inclusive = group_total;
+#pragma unroll
+        for (int offset = 1; offset < 32; offset <<= 1)
         {
-            uint32_t mask = vector_mask(*reinterpret_cast<const uint4*>(bits + i));
-            const uint32_t here = __popc(mask);
-            if (seen + here > occurrence)
-            {
-                for (uint32_t skip = occurrence - seen; skip > 0; --skip)
-                    mask &= mask - 1u; // drop the lowest set bits
-                found = i + static_cast<uint32_t>(__ffs(mask) - 1);
-            }
-            seen += here;
+            const uint32_t other = __shfl_up_sync(kFullMask, inclusive, offset);
+            if (lane >= static_cast<uint32_t>(offset))
+                inclusive += other;
         }
-        for (uint32_t i = whole_end; i < end && found == 0xFFFFFFFFu; ++i)
-            if (matches(bits[i]))
+        const unsigned reached = __ballot_sync(kFullMask, occurrence < before + inclusive);
+        const uint32_t group = static_cast<uint32_t>(__ffs(reached)) - 1u; // not empty: the last lane holds in_part
+        uint32_t seen = before + __shfl_sync(kFullMask, inclusive - group_total, group);
+        const uint32_t last_trip = min(trips, (group + 1u) * trips_per_group);
+        for (uint32_t trip = group * trips_per_group; trip < last_trip; ++trip)
+        {
+            const uint32_t at = begin + trip * 256u + lane * 8u;
+            uint32_t mask = mask_at(at, end);
+            const uint32_t here = __popc(mask);
+            uint32_t scan = here;
+#pragma unroll
+            for (int offset = 1; offset < 32; offset <<= 1)
             {
-                if (seen == occurrence)
-                    found = i;
-                ++seen;
+                const uint32_t other = __shfl_up_sync(kFullMask, scan, offset);
+                if (lane >= static_cast<uint32_t>(offset))
+                    scan += other;
             }
-        sh.chosen_index = found;
+            const uint32_t mine_first = seen + scan - here;
+            if (occurrence >= mine_first && occurrence < mine_first + here)
+            {
+                for (uint32_t skip = occurrence - mine_first; skip > 0; --skip)
+                    mask &= mask - 1u; // drop the lowest set bits
+                sh.chosen_index = at + static_cast<uint32_t>(__ffs(mask) - 1);
+            }
+            seen += __shfl_sync(kFullMask, scan, 31);
+            if (seen > occurrence)
+                break;
+        }
     }
     __syncthreads();
     out.token = static_cast<int32_t>(sh.chosen_index);
