@@ -271,7 +271,7 @@ int moe_sampler_create(int device, uint32_t max_rows, uint32_t max_vocab, moe_sa
             status = cudaMalloc(pointer, bytes);
     };
     uint32_t* counters = nullptr;
-    allocate(reinterpret_cast<void**>(&counters), 2 * sizeof(uint32_t));
+    allocate(reinterpret_cast<void**>(&counters), 3 * sizeof(uint32_t));
     allocate(reinterpret_cast<void**>(&ws.exact_rows), sizeof(uint32_t) * max_rows);
     ws.slice_slots = static_cast<uint32_t>(sampler->sm_count) * 6u * 2u + 64u;
     allocate(reinterpret_cast<void**>(&ws.slice_records), sizeof(uint64_t) * MOE_SLICE_SLOT_RECORDS * ws.slice_slots);
@@ -289,7 +289,7 @@ int moe_sampler_create(int device, uint32_t max_rows, uint32_t max_vocab, moe_sa
     allocate(reinterpret_cast<void**>(&sampler->gather_status), sizeof(int32_t));
     allocate(reinterpret_cast<void**>(&sampler->router_status_dev), sizeof(int32_t));
     if (status == cudaSuccess)
-        status = cudaMemset(counters, 0, 2 * sizeof(uint32_t));
+        status = cudaMemset(counters, 0, 3 * sizeof(uint32_t));
     if (status == cudaSuccess)
         status = cudaMemset(ws.row_arrivals, 0, sizeof(uint32_t) * max_rows);
     if (status == cudaSuccess)
@@ -304,6 +304,7 @@ int moe_sampler_create(int device, uint32_t max_rows, uint32_t max_vocab, moe_sa
         status = cudaDeviceSynchronize();
     ws.exact_count = counters;
     ws.exact_done = counters != nullptr ? counters + 1 : nullptr;
+    ws.exact_next = counters != nullptr ? counters + 2 : nullptr;
     if (status != cudaSuccess)
     {
         moe_sampler_destroy(sampler);

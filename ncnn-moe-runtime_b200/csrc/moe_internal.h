@@ -24,6 +24,7 @@ struct Workspace
     // the exact kernel of the same call
     uint32_t* exact_count = nullptr;   // [1]
     uint32_t* exact_done = nullptr;    // [1] CTAs of the exact kernel that have finished
+    uint32_t* exact_next = nullptr;    // [1] next entry of exact_rows nobody has taken yet
     uint32_t* exact_rows = nullptr;    // [max_rows]
     // per-slot scratch of the exact kernel: (keys, index) pair 0 then pair 1,
     // each array `max_vocab` rounded up to a multiple of 4 entries

@@ -25,8 +25,6 @@ __device__ unsigned long long g_exact_cycles[16];
 extern "C" void moe_debug_exact_cycles(unsigned long long* out, int reset)
 {
     cudaMemcpyFromSymbol(out, g_exact_cycles, sizeof(unsigned long long) * 16);
-    cudaMemcpyFromSymbol(out + 14, g_seq_debug, sizeof(unsigned long long) * 2);
-    cudaMemcpyFromSymbol(out + 1, g_seq_debug, sizeof(unsigned long long) * 4, sizeof(unsigned long long) * 2);
     if (reset)
     {
         unsigned long long none[8] = {};
@@ -68,6 +66,7 @@ struct ExactShared
     uint32_t chosen_warp;   // ... warp whose segment holds the drawn occurrence
     uint32_t chosen_index;
     uint32_t first_fail; // Min-P: first rank whose probability is below the floor
+    uint32_t next_entry; // entry of the row queue this CTA took
     uint32_t warp_hist[kExactWarps][256];
     uint32_t digit_total[256];
     uint32_t warp_count[kExactWarps];
@@ -77,6 +76,7 @@ struct ExactShared
     uint32_t total;
     uint32_t finite_total; // finite logits of the row
     uint32_t max_key;      // ordered key of the largest finite logit
+    uint32_t min_live_key; // ordered key of the smallest logit compact_live kept
     uint32_t floor_bucket; // coarse bucket below which every logit is numerically dead
     float warp_sum[kExactWarps];
 };
@@ -226,6 +226,10 @@ __device__ uint32_t compact_live(const T* row, uint32_t vocab, uint32_t floor_ke
     const uint32_t end = min(vocab, begin + segment);
     const uint32_t least = max(floor_key, kKeyNegInf + 1u);
     uint32_t mine = 0;
+    uint32_t lowest = 0xFFFFFFFFu;
+    if (tid == 0)
+        sh.min_live_key = 0xFFFFFFFFu;
+    __syncthreads();
     for (uint32_t base = begin; base < end; base += 128)
     {
         float v[4];
@@ -239,11 +243,18 @@ __device__ uint32_t compact_live(const T* row, uint32_t vocab, uint32_t floor_ke
         for (int u = 0; u < 4; ++u)
         {
             const uint32_t key = ordered_key(v[u]);
-            mine += __popc(__ballot_sync(kFullMask, fabsf(v[u]) < INFINITY && key >= least));
+            const bool keep = fabsf(v[u]) < INFINITY && key >= least;
+            mine += __popc(__ballot_sync(kFullMask, keep));
+            if (keep)
+                lowest = min(lowest, key);
         }
     }
+    lowest = __reduce_min_sync(kFullMask, lowest);
     if (lane == 0)
+    {
         sh.warp_count[warp] = mine;
+        atomicMin(&sh.min_live_key, lowest);
+    }
     __syncthreads();
     if (warp == 0)
     {
@@ -301,6 +312,12 @@ __device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32
     const uint32_t begin = min(n, warp * segment);
     const uint32_t end = min(n, begin + segment);
 
+#ifdef MOE_PHASE_TIMERS
+    long long pass_lap = clock64();
+#define PASS_LAP(slot) do { if (threadIdx.x == 0) { const long long now_ = clock64(); atomicAdd(&g_exact_cycles[slot], static_cast<unsigned long long>(now_ - pass_lap)); pass_lap = now_; } } while (0)
+#else
+#define PASS_LAP(slot) do {} while (0)
+#endif
     for (int d = lane; d < 256; d += 32)
         sh.warp_hist[warp][d] = 0;
     __syncwarp();
@@ -320,14 +337,12 @@ __device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32
         {
             const uint32_t i = base + u * 32 + lane;
             const bool valid = i < end;
-            const uint32_t digit = valid ? ((key[u] >> shift) & 0xFFu) : 0xFFFFFFFFu;
-            const unsigned peers = __match_any_sync(kFullMask, digit);
-            if (valid && lane == (__ffs(peers) - 1))
-                sh.warp_hist[warp][digit] += __popc(peers);
-            __syncwarp();
+            if (valid)
+                atomicAdd(&sh.warp_hist[warp][(key[u] >> shift) & 0xFFu], 1u); // the warp's own counters: only its lanes meet here
         }
     }
     __syncthreads();
+    PASS_LAP(8);
     // exclusive offsets: digit-major, then warp order
     if (tid < 256)
     {
@@ -375,6 +390,7 @@ __device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32
             sh.warp_hist[w][tid] += digit_base;
     }
     __syncthreads();
+    PASS_LAP(9);
     for (uint32_t base = begin; base < end; base += 128)
     {
         uint64_t item[4];
@@ -389,8 +405,15 @@ __device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32
         {
             const uint32_t i = base + u * 32 + lane;
             const bool valid = i < end;
-            const uint32_t digit = valid ? (static_cast<uint32_t>(item[u] >> (32 + shift)) & 0xFFu) : 0xFFFFFFFFu;
-            const unsigned peers = __match_any_sync(kFullMask, digit);
+            const uint32_t digit = valid ? (static_cast<uint32_t>(item[u] >> (32 + shift)) & 0xFFu) : 0u;
+            // lanes with my digit: one vote per bit of the digit (far cheaper here than a match instruction)
+            unsigned peers = __ballot_sync(kFullMask, valid);
+#pragma unroll
+            for (int bit = 0; bit < 8; ++bit)
+            {
+                const unsigned votes = __ballot_sync(kFullMask, (digit >> bit) & 1u);
+                peers &= ((digit >> bit) & 1u) ? votes : ~votes;
+            }
             if (valid)
             {
                 const uint32_t slot = sh.warp_hist[warp][digit] + __popc(peers & ((1u << lane) - 1u));
@@ -403,6 +426,211 @@ __device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32
         }
     }
     __syncthreads();
+    PASS_LAP(10);
+}
+
+// ---- order by value buckets: one scatter and a look inside each bucket -------------------------
+//
+// The live logits of an fp32 row are spread over a bounded range of values, so a linear map of the
+// value onto kOrderBuckets buckets (bucket 0 = the maximum) leaves a handful of candidates per
+// bucket.  One pass counts the buckets, one scatters the items into bucket order (the only
+// scattered stores of the method: a byte-digit sort pays them four times), and a last pass puts
+// each bucket in order: warps take 128 positions of the scattered list at a time, stage the
+// buckets that begin there in shared memory and rank every item inside its own bucket.
+// Rows whose values pile up (a bucket above kOrderBucketLimit items) keep the byte-digit sort.
+constexpr uint32_t kOrderBuckets = 16384;
+constexpr uint32_t kOrderBucketLimit = 128;
+constexpr uint32_t kOrderChunk = 128;
+constexpr uint32_t kOrderStageItems = kOrderChunk + kOrderBucketLimit; // per warp
+constexpr size_t kOrderSharedBytes = sizeof(uint32_t) * kOrderBuckets + sizeof(uint64_t) * kExactWarps * kOrderStageItems;
+
+struct BucketMap
+{
+    float top;   // largest live logit
+    float scale; // buckets per unit of value
+};
+
+// Monotone: a larger logit never gets a larger bucket, equal logits share a bucket.
+__device__ __forceinline__ uint32_t order_bucket(uint64_t item, const BucketMap& map)
+{
+    const float value = key_to_float(~static_cast<uint32_t>(item >> 32));
+    const float scaled = __fmul_rn(__fsub_rn(map.top, value), map.scale);
+    return min(kOrderBuckets - 1u, __float2uint_rz(scaled));
+}
+
+// smallest bucket b with start(b) >= position, where start(b) = b ? cursor[b - 1] : 0 and
+// start(kOrderBuckets) = n; every lane of the warp calls this with the same arguments
+__device__ __forceinline__ uint32_t first_bucket_at(const uint32_t* cursor, uint32_t position)
+{
+    if (position == 0u)
+        return 0u;
+    const uint32_t lane = threadIdx.x & 31u;
+    // b >= 1 qualifies iff cursor[b - 1] >= position; search t = b - 1 in [0, kOrderBuckets)
+    uint32_t lo = 0, hi = kOrderBuckets; // answer t in [lo, hi]; hi = none qualifies
+    while (lo < hi)
+    {
+        const uint32_t span = hi - lo;
+        const uint32_t stride = (span + 31u) / 32u;
+        const uint32_t probe = lo + lane * stride;
+        const bool reaches = probe >= hi || cursor[probe] >= position;
+        const unsigned votes = __ballot_sync(kFullMask, reaches);
+        const uint32_t first_lane = votes != 0u ? static_cast<uint32_t>(__ffs(votes)) - 1u : 32u;
+        const uint32_t new_hi = min(hi, lo + first_lane * stride);
+        lo = first_lane == 0u ? new_hi : lo + (first_lane - 1u) * stride + 1u;
+        hi = new_hi;
+    }
+    return lo + 1u;
+}
+
+// items_in[0..n): the live items in any order.  On success records_out[0..n) holds the candidate
+// records (complemented items) in rank order and true is returned; false: nothing usable was written,
+// the caller sorts by digits.  `cursor` and `stage` are the kernel's dynamic shared memory.
+__device__ bool order_by_buckets(const uint64_t* items_in, uint64_t* scattered, uint64_t* records_out, uint32_t n, uint32_t max_key, uint32_t min_key,
+                                 uint32_t* cursor, uint64_t* stage, ExactShared& sh)
+{
+    const uint32_t tid = threadIdx.x;
+    const uint32_t lane = tid & 31u;
+    const uint32_t warp = tid >> 5;
+    BucketMap map;
+    map.top = key_to_float(max_key);
+    const float range = __fsub_rn(map.top, key_to_float(min_key));
+    if (!(range > 0.0f) || !(range < INFINITY))
+        return false; // one value, or a span fp32 cannot hold
+    map.scale = __fdiv_rn(static_cast<float>(kOrderBuckets - 1u), range);
+    if (!(map.scale < INFINITY))
+        return false;
+
+#ifdef MOE_PHASE_TIMERS
+    long long order_lap = clock64();
+#define ORDER_LAP(slot) do { if (threadIdx.x == 0) { const long long now_ = clock64(); atomicAdd(&g_exact_cycles[slot], static_cast<unsigned long long>(now_ - order_lap)); order_lap = now_; } } while (0)
+#else
+#define ORDER_LAP(slot) do {} while (0)
+#endif
+    for (uint32_t b = tid; b < kOrderBuckets; b += kExactThreads)
+        cursor[b] = 0;
+    __syncthreads();
+    for (uint32_t base = 0; base < n; base += 4u * kExactThreads)
+    {
+        uint64_t item[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+        {
+            const uint32_t i = base + u * kExactThreads + tid;
+            item[u] = i < n ? items_in[i] : 0ull;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (base + u * kExactThreads + tid < n)
+                atomicAdd(&cursor[order_bucket(item[u], map)], 1u);
+    }
+    __syncthreads();
+    ORDER_LAP(6);
+    // exclusive scan of the counts (16 consecutive buckets per thread) and the largest bucket
+    constexpr uint32_t kPerThread = kOrderBuckets / kExactThreads;
+    uint32_t counts[kPerThread];
+    uint32_t sum = 0, largest = 0;
+#pragma unroll
+    for (uint32_t j = 0; j < kPerThread; ++j)
+    {
+        counts[j] = cursor[tid * kPerThread + j];
+        sum += counts[j];
+        largest = max(largest, counts[j]);
+    }
+    uint32_t scan = sum;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1)
+    {
+        const uint32_t other = __shfl_up_sync(kFullMask, scan, offset);
+        if (lane >= static_cast<uint32_t>(offset))
+            scan += other;
+    }
+    largest = __reduce_max_sync(kFullMask, largest);
+    if (lane == 31)
+        sh.warp_count[warp] = scan;
+    if (lane == 0)
+        sh.warp_or[warp] = largest;
+    __syncthreads();
+    uint32_t before = scan - sum;
+    for (uint32_t w = 0; w < kExactWarps; ++w)
+    {
+        if (w < warp)
+            before += sh.warp_count[w];
+        largest = max(largest, sh.warp_or[w]);
+    }
+    __syncthreads();
+    if (largest > kOrderBucketLimit)
+        return false;
+#pragma unroll
+    for (uint32_t j = 0; j < kPerThread; ++j)
+    {
+        cursor[tid * kPerThread + j] = before;
+        before += counts[j];
+    }
+    __syncthreads();
+    ORDER_LAP(14);
+    // scatter: the slot comes from the bucket's cursor, which ends at the end of its bucket
+    for (uint32_t base = 0; base < n; base += 4u * kExactThreads)
+    {
+        uint64_t item[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+        {
+            const uint32_t i = base + u * kExactThreads + tid;
+            item[u] = i < n ? items_in[i] : 0ull;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (base + u * kExactThreads + tid < n)
+                scattered[atomicAdd(&cursor[order_bucket(item[u], map)], 1u)] = item[u];
+    }
+    __syncthreads();
+    ORDER_LAP(15);
+    // order inside the buckets
+    uint64_t* const mine = stage + static_cast<size_t>(warp) * kOrderStageItems;
+    const uint32_t chunks = (n + kOrderChunk - 1u) / kOrderChunk;
+    for (uint32_t chunk = warp; chunk < chunks; chunk += kExactWarps)
+    {
+        const uint32_t first_bucket = first_bucket_at(cursor, chunk * kOrderChunk);
+        const uint32_t end_bucket = first_bucket_at(cursor, min(n, (chunk + 1u) * kOrderChunk));
+        const uint32_t begin = first_bucket == 0u ? 0u : cursor[first_bucket - 1u];
+        const uint32_t end = end_bucket == 0u ? 0u : cursor[end_bucket - 1u];
+        const uint32_t count = end - begin; // < kOrderChunk + kOrderBucketLimit
+        // all of a lane's loads first: the list lives in L2 and a dependent round trip per item would dominate
+        constexpr uint32_t kPerLane = kOrderStageItems / 32u;
+        uint64_t held[kPerLane];
+#pragma unroll
+        for (uint32_t u = 0; u < kPerLane; ++u)
+        {
+            const uint32_t i = lane + 32u * u;
+            held[u] = i < count ? scattered[begin + i] : 0ull;
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < kPerLane; ++u)
+        {
+            const uint32_t i = lane + 32u * u;
+            if (i < count)
+                mine[i] = held[u];
+        }
+        __syncwarp();
+#pragma unroll
+        for (uint32_t u = 0; u < kPerLane; ++u)
+        {
+            const uint32_t i = lane + 32u * u;
+            if (i >= count)
+                break;
+            const uint64_t item = held[u];
+            const uint32_t bucket = order_bucket(item, map);
+            const uint32_t bucket_begin = (bucket == 0u ? 0u : cursor[bucket - 1u]) - begin;
+            const uint32_t bucket_end = cursor[bucket] - begin;
+            uint32_t rank = 0;
+            for (uint32_t j = bucket_begin; j < bucket_end; ++j)
+                rank += mine[j] < item ? 1u : 0u;
+            records_out[begin + bucket_begin + rank] = ~item;
+        }
+        __syncwarp();
+    }
+    __syncthreads();
+    return true;
 }
 
 // The arithmetic tail of session.cpp:89-136,429-442 for a complete, sorted
@@ -1051,7 +1279,26 @@ __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys
             MOE_EXACT_MARK(0);
             int source = 0;
             bool complemented = false;
-            if (n > 1)
+            bool ordered = false;
+            if constexpr (sizeof(T) == 4)
+            {
+                if (n > 1)
+                {
+                    extern __shared__ __align__(16) uint32_t order_words[];
+                    ordered = order_by_buckets(items[0], items[1], items[0], n, sh.max_key, sh.min_live_key, order_words,
+                                               reinterpret_cast<uint64_t*>(order_words + kOrderBuckets), sh);
+                    complemented = ordered;
+#ifdef MOE_PHASE_TIMERS
+                    if (tid == 0)
+                    {
+                        atomicAdd(&g_exact_cycles[ordered ? 11 : 12], 1ull);
+                        if (!ordered)
+                            printf("fallback row %u n %u max %08x min %08x\n", row, n, sh.max_key, sh.min_live_key);
+                    }
+#endif
+                }
+            }
+            if (n > 1 && !ordered)
             {
                 // A digit needs no pass when it is the same function of the higher digits
                 // for every key.  Keys (high words) are ~ordered_key(v): their low bytes are the
@@ -1161,8 +1408,18 @@ __global__ void __launch_bounds__(kExactThreads, 1) sample_exact_kernel(const Sa
     const uint32_t pending = *ws.exact_count;
     const uint32_t slot_stride = (ws.max_vocab + 3u) & ~3u;
     uint32_t* slot_keys = ws.sort_keys + static_cast<size_t>(blockIdx.x) * 4u * slot_stride;
-    for (uint32_t i = blockIdx.x; i < pending; i += gridDim.x)
-        exact_row<T>(a, ws.exact_rows[i], slot_keys, nullptr, slot_stride, sh);
+    // rows cost from a few to several hundred microseconds: a CTA takes the next one when it is free
+    for (;;)
+    {
+        if (threadIdx.x == 0)
+            sh.next_entry = atomicAdd(ws.exact_next, 1u);
+        __syncthreads();
+        const uint32_t entry = sh.next_entry;
+        __syncthreads();
+        if (entry >= pending)
+            break;
+        exact_row<T>(a, ws.exact_rows[entry], slot_keys, nullptr, slot_stride, sh);
+    }
     __syncthreads();
     if (threadIdx.x == 0)
     {
@@ -1171,6 +1428,7 @@ __global__ void __launch_bounds__(kExactThreads, 1) sample_exact_kernel(const Sa
         {
             *ws.exact_count = 0; // every CTA has read it: ready for the next call
             *ws.exact_done = 0;
+            *ws.exact_next = 0;
             __threadfence();
         }
     }
@@ -1185,7 +1443,10 @@ cudaError_t launch_sample_exact(const SampleArgs& args, const Workspace& ws, cud
     const uint32_t grid = ws.slots < args.rows ? ws.slots : args.rows;
     if (args.dtype == MOE_DTYPE_F32)
     {
-        sample_exact_kernel<float><<<grid, kExactThreads, 0, stream>>>(args, ws);
+        static SharedOptIn opt_in;
+        if (cudaError_t status = opt_in_shared(opt_in, sample_exact_kernel<float>, kOrderSharedBytes))
+            return status;
+        sample_exact_kernel<float><<<grid, kExactThreads, kOrderSharedBytes, stream>>>(args, ws);
     }
     else
     {
