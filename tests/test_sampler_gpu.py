@@ -392,3 +392,36 @@ def test_more_rows_than_resident_ctas(pkg, workloads, parity, dtype):
     params["top_p"][::97] = 0.0                                   # rejected rows in between
     logits = values if dtype == "f32" else workloads.to_bf16_bits(values)
     parity.check(logits, params, topk_stride=8)
+
+
+def test_fp32_rows_without_topk_are_ordered_by_value_buckets_or_by_digits(pkg, parity):
+    """fp32 rows without Top-K are put in rank order by value buckets (one scatter, then a look inside
+    each bucket); rows whose values pile up in a bucket, span more than fp32 can subtract, or hold one
+    value fall back to the byte-digit sort.  Every shape must give the reference's token, bit for bit,
+    and more rows than CTAs go through the row queue."""
+    rng = np.random.default_rng(404)
+    vocab = 40009
+    rows = []
+    rows.append((3.0 * rng.standard_normal(vocab)).astype(np.float32))                      # spread values: buckets
+    piled = (3.0 * rng.standard_normal(vocab)).astype(np.float32)
+    piled[rng.choice(vocab, 1500, replace=False)] = np.float32(1.2345)                      # 1500 copies of one value: digits
+    rows.append(piled)
+    rows.append(np.where(rng.random(vocab) < 0.5, np.float32(2.0), np.float32(-1.0)).astype(np.float32))   # two values
+    wide = (3.0 * rng.standard_normal(vocab)).astype(np.float32)
+    wide[7], wide[11] = np.float32(3.0e38), np.float32(-3.0e38)                             # span overflows fp32
+    rows.append(wide)
+    near = np.float32(5.0) + (rng.integers(0, 40, vocab).astype(np.float32) * np.float32(2.0 ** -20))   # forty adjacent values
+    rows.append(near.astype(np.float32))
+    tiny = np.full(vocab, -np.inf, dtype=np.float32)
+    tiny[[3, 30000]] = [0.5, 0.25]                                                           # two finite logits
+    rows.append(tiny)
+    dense = (0.01 * rng.standard_normal(vocab)).astype(np.float32)                          # everything live, narrow range
+    rows.append(dense)
+    logits = np.stack(rows * 24)                                                            # 168 rows: more than resident CTAs
+    count = logits.shape[0]
+    temperatures = np.tile(np.array([1.0, 0.7, 1.5, 0.4], dtype=np.float32), count)[:count]
+    top_p = np.tile(np.array([1.0, 0.9, 0.97], dtype=np.float32), count)[:count]
+    min_p = np.tile(np.array([0.0, 0.0, 0.001, 0.0, 0.02], dtype=np.float32), count)[:count]
+    params = pkg.make_row_params(count, seed=77, temperature=temperatures, top_k=0, top_p=top_p, min_p=min_p)
+    params["step"] = np.arange(count) % 5
+    parity.check(logits, params)

@@ -21,13 +21,20 @@ MAX_ROUTES = 65536
 MAX_EXPERTS = 4096
 
 
-def call_static(pkg, torch, logits, top_k, score_function, bias, normalization=1, scaling=1.0, flags=1):
+def plan_buffers(pkg, torch, logits, top_k):
     tokens, experts = logits.shape
     routes = tokens * top_k
     device = logits.device
-    out = pkg.DispatchPlan(torch.empty(experts + 1, dtype=torch.int32, device=device), torch.empty(routes, dtype=torch.int32, device=device),
-                           torch.empty(routes, dtype=torch.int32, device=device), torch.empty(routes, dtype=torch.float32, device=device),
-                           torch.full((1,), -1, dtype=torch.int32, device=device))
+    return pkg.DispatchPlan(torch.empty(experts + 1, dtype=torch.int32, device=device), torch.empty(routes, dtype=torch.int32, device=device),
+                            torch.empty(routes, dtype=torch.int32, device=device), torch.empty(routes, dtype=torch.float32, device=device),
+                            torch.full((1,), -1, dtype=torch.int32, device=device))
+
+
+def call_static(pkg, torch, logits, top_k, score_function, bias, normalization=1, scaling=1.0, flags=1, out=None):
+    tokens, experts = logits.shape
+    device = logits.device
+    if out is None:
+        out = plan_buffers(pkg, torch, logits, top_k)
     options = pkg.RouterOptions(experts, top_k, score_function, normalization, scaling, flags, bias.data_ptr() if bias is not None else None, None)
     message = C.create_string_buffer(256)
     stream = torch.cuda.current_stream(device).cuda_stream
@@ -50,8 +57,10 @@ def test_static_router_matches_the_allocating_entry_point(pkg, workloads, sample
         bias = torch.from_numpy(bias_host).cuda()
         want = sampler.router_dispatch(logits, top_k, score_function=score_function, selection_bias=bias)
         torch.cuda.synchronize()
+        buffers = plan_buffers(pkg, torch, logits, top_k)   # the caller's outputs exist before the measured call
+        torch.cuda.synchronize()
         free_before = torch.cuda.mem_get_info()[0]
-        code, message, got = call_static(pkg, torch, logits, top_k, score_function, bias)
+        code, message, got = call_static(pkg, torch, logits, top_k, score_function, bias, out=buffers)
         torch.cuda.synchronize()
         assert code == 0, message
         assert torch.cuda.mem_get_info()[0] == free_before      # the call took no device memory
