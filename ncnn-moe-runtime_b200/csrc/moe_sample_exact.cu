@@ -33,6 +33,13 @@ extern "C" void moe_debug_exact_cycles(unsigned long long* out, int reset)
         cudaMemcpyToSymbol(g_exact_cycles, zeros, sizeof(zeros));
     }
 }
+__device__ unsigned long long g_order_cycles[8];
+extern "C" void moe_debug_order_cycles(unsigned long long* out)
+{
+    cudaMemcpyFromSymbol(out, g_order_cycles, sizeof(unsigned long long) * 8);
+    unsigned long long zeros[8] = {};
+    cudaMemcpyToSymbol(g_order_cycles, zeros, sizeof(zeros));
+}
 #define MOE_EXACT_MARK(slot)                                                                              \
     do                                                                                                    \
     {                                                                                                     \
@@ -441,8 +448,9 @@ __device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32
 constexpr uint32_t kOrderBuckets = 16384;
 constexpr uint32_t kOrderBucketLimit = 128;
 constexpr uint32_t kOrderChunk = 128;
-constexpr uint32_t kOrderStageItems = kOrderChunk + kOrderBucketLimit; // per warp
-constexpr size_t kOrderSharedBytes = sizeof(uint32_t) * kOrderBuckets + sizeof(uint64_t) * kExactWarps * kOrderStageItems;
+constexpr uint32_t kOrderStageItems = kOrderChunk + kOrderBucketLimit; // per warp (plus kOrderStagePad readable words behind)
+constexpr uint32_t kOrderStagePad = 4;
+constexpr size_t kOrderSharedBytes = sizeof(uint32_t) * kOrderBuckets + sizeof(uint64_t) * kExactWarps * (kOrderStageItems + kOrderStagePad);
 
 struct BucketMap
 {
@@ -525,7 +533,7 @@ __device__ bool order_by_buckets(const uint64_t* items_in, uint64_t* scattered, 
     }
     __syncthreads();
     ORDER_LAP(6);
-    // exclusive scan of the counts (16 consecutive buckets per thread) and the largest bucket
+    // exclusive scan of the counts (consecutive buckets per thread) and the largest bucket
     constexpr uint32_t kPerThread = kOrderBuckets / kExactThreads;
     uint32_t counts[kPerThread];
     uint32_t sum = 0, largest = 0;
@@ -586,48 +594,71 @@ __device__ bool order_by_buckets(const uint64_t* items_in, uint64_t* scattered, 
     __syncthreads();
     ORDER_LAP(15);
     // order inside the buckets
-    uint64_t* const mine = stage + static_cast<size_t>(warp) * kOrderStageItems;
+    uint64_t* const mine = stage + static_cast<size_t>(warp) * (kOrderStageItems + kOrderStagePad);
     const uint32_t chunks = (n + kOrderChunk - 1u) / kOrderChunk;
     for (uint32_t chunk = warp; chunk < chunks; chunk += kExactWarps)
     {
-        const uint32_t first_bucket = first_bucket_at(cursor, chunk * kOrderChunk);
-        const uint32_t end_bucket = first_bucket_at(cursor, min(n, (chunk + 1u) * kOrderChunk));
-        const uint32_t begin = first_bucket == 0u ? 0u : cursor[first_bucket - 1u];
-        const uint32_t end = end_bucket == 0u ? 0u : cursor[end_bucket - 1u];
-        const uint32_t count = end - begin; // < kOrderChunk + kOrderBucketLimit
-        // all of a lane's loads first: the list lives in L2 and a dependent round trip per item would dominate
+#ifdef MOE_PHASE_TIMERS
+        long long c_lap = clock64();
+#define C_LAP(slot) do { if (tid == 0) { const long long now_ = clock64(); atomicAdd(&g_order_cycles[slot], static_cast<unsigned long long>(now_ - c_lap)); c_lap = now_; } } while (0)
+#else
+#define C_LAP(slot) do {} while (0)
+#endif
+        // The window: the chunk's positions and the longest bucket that may reach past them.  The
+        // chunk owns the buckets that begin inside its positions; where those begin and end follows
+        // from the buckets of the items at the chunk's first position and at the next chunk's.
+        const uint32_t window_begin = chunk * kOrderChunk;
+        const uint32_t window_count = min(n - window_begin, kOrderStageItems);
         constexpr uint32_t kPerLane = kOrderStageItems / 32u;
         uint64_t held[kPerLane];
 #pragma unroll
         for (uint32_t u = 0; u < kPerLane; ++u)
         {
             const uint32_t i = lane + 32u * u;
-            held[u] = i < count ? scattered[begin + i] : 0ull;
+            held[u] = i < window_count ? scattered[window_begin + i] : ~0ull; // the padding ranks above everything
         }
 #pragma unroll
         for (uint32_t u = 0; u < kPerLane; ++u)
-        {
-            const uint32_t i = lane + 32u * u;
-            if (i < count)
-                mine[i] = held[u];
-        }
+            mine[lane + 32u * u] = held[u];
+        if (lane < kOrderStagePad)
+            mine[kOrderStageItems + lane] = ~0ull;
         __syncwarp();
+        C_LAP(1);
+        // first position the chunk owns: the start of the first bucket that begins at or after window_begin
+        const uint32_t head_bucket = order_bucket(mine[0], map);
+        const uint32_t head_start = head_bucket == 0u ? 0u : cursor[head_bucket - 1u];
+        const uint32_t begin = head_start == window_begin ? window_begin : cursor[head_bucket];
+        uint32_t end = n;
+        if (window_begin + kOrderChunk < n)
+        {
+            const uint32_t next_bucket = order_bucket(mine[kOrderChunk], map);
+            const uint32_t next_start = next_bucket == 0u ? 0u : cursor[next_bucket - 1u];
+            end = next_start == window_begin + kOrderChunk ? next_start : cursor[next_bucket];
+        }
+        C_LAP(0);
 #pragma unroll
         for (uint32_t u = 0; u < kPerLane; ++u)
         {
-            const uint32_t i = lane + 32u * u;
-            if (i >= count)
-                break;
+            const uint32_t position = window_begin + lane + 32u * u;
+            if (position < begin || position >= end)
+                continue;
             const uint64_t item = held[u];
             const uint32_t bucket = order_bucket(item, map);
-            const uint32_t bucket_begin = (bucket == 0u ? 0u : cursor[bucket - 1u]) - begin;
-            const uint32_t bucket_end = cursor[bucket] - begin;
+            const uint32_t bucket_begin = bucket == 0u ? 0u : cursor[bucket - 1u];
+            const uint32_t bucket_end = cursor[bucket];
+            // what follows a bucket in the window is larger (later buckets, then the padding), so whole
+            // trips of four need no guard
             uint32_t rank = 0;
-            for (uint32_t j = bucket_begin; j < bucket_end; ++j)
-                rank += mine[j] < item ? 1u : 0u;
-            records_out[begin + bucket_begin + rank] = ~item;
+            for (uint32_t j = bucket_begin - window_begin; j < bucket_end - window_begin; j += 4u)
+                rank += (mine[j] < item ? 1u : 0u) + (mine[j + 1u] < item ? 1u : 0u) + (mine[j + 2u] < item ? 1u : 0u) + (mine[j + 3u] < item ? 1u : 0u);
+            records_out[bucket_begin + rank] = ~item;
         }
         __syncwarp();
+        C_LAP(2);
+#ifdef MOE_PHASE_TIMERS
+        if (tid == 0)
+            atomicAdd(&g_order_cycles[3], 1ull);
+#endif
     }
     __syncthreads();
     return true;
