@@ -466,30 +466,6 @@ __device__ __forceinline__ uint32_t order_bucket(uint64_t item, const BucketMap&
     return min(kOrderBuckets - 1u, __float2uint_rz(scaled));
 }
 
-// smallest bucket b with start(b) >= position, where start(b) = b ? cursor[b - 1] : 0 and
-// start(kOrderBuckets) = n; every lane of the warp calls this with the same arguments
-__device__ __forceinline__ uint32_t first_bucket_at(const uint32_t* cursor, uint32_t position)
-{
-    if (position == 0u)
-        return 0u;
-    const uint32_t lane = threadIdx.x & 31u;
-    // b >= 1 qualifies iff cursor[b - 1] >= position; search t = b - 1 in [0, kOrderBuckets)
-    uint32_t lo = 0, hi = kOrderBuckets; // answer t in [lo, hi]; hi = none qualifies
-    while (lo < hi)
-    {
-        const uint32_t span = hi - lo;
-        const uint32_t stride = (span + 31u) / 32u;
-        const uint32_t probe = lo + lane * stride;
-        const bool reaches = probe >= hi || cursor[probe] >= position;
-        const unsigned votes = __ballot_sync(kFullMask, reaches);
-        const uint32_t first_lane = votes != 0u ? static_cast<uint32_t>(__ffs(votes)) - 1u : 32u;
-        const uint32_t new_hi = min(hi, lo + first_lane * stride);
-        lo = first_lane == 0u ? new_hi : lo + (first_lane - 1u) * stride + 1u;
-        hi = new_hi;
-    }
-    return lo + 1u;
-}
-
 // items_in[0..n): the live items in any order.  On success records_out[0..n) holds the candidate
 // records (complemented items) in rank order and true is returned; false: nothing usable was written,
 // the caller sorts by digits.  `cursor` and `stage` are the kernel's dynamic shared memory.

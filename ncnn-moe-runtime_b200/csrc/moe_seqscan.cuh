@@ -38,10 +38,13 @@ struct SeqResult
     bool stopped;       // the stop condition fired
 };
 
+constexpr int kSeqHead = 256; // addends at the head of a sequence that one warp adds one by one
+
 template<int kThreads>
 struct SeqShared
 {
     uint32_t warp_pair[kThreads / 32][2];
+    float head[kSeqHead];   // the first addends of the sequence
     uint32_t first_event;   // smallest element offset in the chunk with a stop or a carry
     float acc;
     uint32_t stopped;
@@ -97,6 +100,71 @@ __device__ __noinline__ SeqResult block_sequential_sum(const float* x, uint32_t 
     {
         result = SeqResult{acc, 1u, true};
         return result;
+    }
+    // The head of the sequence, literally: the first addends carry the accumulator through several
+    // binades with a handful of addends each, and a round of the block (below) spends a whole chunk
+    // on each of them.  One warp adds them in order, eight per trip and one test (the accumulator
+    // does not decrease: a bound met by any of the eight is met by the last).
+    {
+        const uint32_t head = min(static_cast<uint32_t>(kSeqHead), n);
+        if (tid < head)
+            sh.head[tid] = x[tid];
+        __syncthreads();
+        if (warp == 0)
+        {
+            float a = acc;
+            uint32_t taken = 1;
+            bool stopped = false;
+            while (taken < head)
+            {
+                const uint32_t group = min(8u, head - taken);
+                float value[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    value[j] = static_cast<uint32_t>(j) < group ? sh.head[taken + j] : 0.0f; // adding +0 changes nothing
+                float partial[8];
+                float t = a;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                {
+                    t = __fadd_rn(t, value[j]);
+                    partial[j] = t;
+                }
+                if ((stop == kSeqReachBound && t >= bound) || (stop == kSeqExceedBound && bound < t))
+                {
+                    int first = 7;
+#pragma unroll
+                    for (int j = 6; j >= 0; --j)
+                        if ((stop == kSeqReachBound && partial[j] >= bound) || (stop == kSeqExceedBound && bound < partial[j]))
+                            first = j;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (j == first)
+                            a = partial[j];
+                    taken += static_cast<uint32_t>(first) + 1u;
+                    stopped = true;
+                    break;
+                }
+                a = t;
+                taken += group;
+            }
+            if (lane == 0)
+            {
+                sh.acc = a;
+                sh.first_event = taken;
+                sh.stopped = stopped ? 1u : 0u;
+            }
+        }
+        __syncthreads();
+        acc = sh.acc;
+        position = sh.first_event;
+        const bool stopped = sh.stopped != 0;
+        __syncthreads();
+        if (stopped)
+        {
+            result = SeqResult{acc, position, true};
+            return result;
+        }
     }
     while (position < n)
     {
