@@ -291,6 +291,12 @@ def time_step_graph(torch, step, steps, chunk, min_seconds, clocks=None, barrier
     per_replay_s = max(start.elapsed_time(stop) / 3 * 1e-3, 1e-7)
     replays = max((steps + chunk - 1) // chunk, int(np.ceil(min_seconds / per_replay_s)))
     if barrier is not None:
+        # every rank must replay the same number of times: the graph may hold a collective, and the
+        # probe above times differently on every rank
+        import torch.distributed as dist
+        agreed = torch.tensor([replays], dtype=torch.int64, device="cuda")
+        dist.all_reduce(agreed, op=dist.ReduceOp.MAX)
+        replays = int(agreed.item())
         barrier()
     torch.cuda.synchronize()
     if clocks is not None:
