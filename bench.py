@@ -403,7 +403,9 @@ def run_router_bench(args, as_dict=False):
             "config": {"workload": "config 5b: 4096 tokens x 256 experts fp32 N(0,1) + bias N(0,0.1), sigmoid, top_k 8, renormalised", "kernels_per_step": 3},
             "gpu_launches": 3 * timed,
             "regroup_gather": {"ms": gather_ms, "achieved_gbs": gather_bytes / (gather_ms * 1e-3) / 1e9, "peak_gbs": peak, "frac": gather_bytes / (gather_ms * 1e-3) / 1e9 / peak,
-                               "shape": "32768 routes x 4096 fp32 columns"},
+                               "shape": "32768 routes x 4096 fp32 columns",
+                               "note": "algorithmic bytes = one read and one write per routed row; the 64 MiB of hidden rows are each read top_k times "
+                                       "and stay in L2, so DRAM sees about (1 + 1/top_k) / 2 of these bytes and the fraction can exceed 1"},
             "cpu_baseline": {"value": tokens / cpu_s, "unit": "tokens/s", "cores": 1, "kind": oracle.kind, "sample": "the whole 4096-token call, single thread (the reference dispatcher is single-threaded)"},
             "routes_equal_to_reference": equal}
     sampler.close()

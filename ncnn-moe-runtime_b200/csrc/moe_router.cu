@@ -471,8 +471,23 @@ __global__ void __launch_bounds__(256) regroup_gather_kernel(const float* hidden
         {
             const float4* source4 = reinterpret_cast<const float4*>(source);
             float4* target4 = reinterpret_cast<float4*>(target);
-            for (uint32_t c = lane; c < columns / 4; c += 32)
-                target4[c] = valid ? __ldg(source4 + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            // eight 16-byte loads in flight per lane; the copies leave with a streaming store so that the
+            // hidden rows (read once per route of their token) stay in L2
+            const uint32_t vectors = columns / 4;
+            const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            uint32_t c = lane;
+            for (; c + 7u * 32u < vectors; c += 8u * 32u)
+            {
+                float4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    v[u] = valid ? __ldg(source4 + c + 32u * u) : zero;
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    __stcs(target4 + c + 32u * u, v[u]);
+            }
+            for (; c < vectors; c += 32)
+                __stcs(target4 + c, valid ? __ldg(source4 + c) : zero);
         }
         else
         {
