@@ -115,22 +115,6 @@ __device__ __forceinline__ uint4 load_stream_16(const void* pointer)
     return v;
 }
 
-// 256-bit form (sm_100): half the load instructions for the same bytes in
-// flight, and the only vector width that accepts the L2 evict-first hint, which
-// keeps a batch larger than L2 from displacing resident data.  32-byte aligned.
-struct Vec32
-{
-    uint32_t w[8];
-};
-__device__ __forceinline__ Vec32 load_stream_32(const void* pointer)
-{
-    Vec32 v;
-    asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]), "=r"(v.w[5]), "=r"(v.w[6]), "=r"(v.w[7])
-                 : "l"(pointer));
-    return v;
-}
-
 // ---- shared-memory accesses with the state space spelled out -------------------
 // A pointer into dynamic shared memory that has travelled through a struct or a
 // function argument is a generic pointer to the compiler, and generic loads go

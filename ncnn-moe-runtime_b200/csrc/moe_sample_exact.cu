@@ -27,18 +27,9 @@ extern "C" void moe_debug_exact_cycles(unsigned long long* out, int reset)
     cudaMemcpyFromSymbol(out, g_exact_cycles, sizeof(unsigned long long) * 16);
     if (reset)
     {
-        unsigned long long none[8] = {};
-        cudaMemcpyToSymbol(g_seq_debug, none, sizeof(none));
         unsigned long long zeros[16] = {};
         cudaMemcpyToSymbol(g_exact_cycles, zeros, sizeof(zeros));
     }
-}
-__device__ unsigned long long g_order_cycles[8];
-extern "C" void moe_debug_order_cycles(unsigned long long* out)
-{
-    cudaMemcpyFromSymbol(out, g_order_cycles, sizeof(unsigned long long) * 8);
-    unsigned long long zeros[8] = {};
-    cudaMemcpyToSymbol(g_order_cycles, zeros, sizeof(zeros));
 }
 #define MOE_EXACT_MARK(slot)                                                                              \
     do                                                                                                    \
@@ -319,12 +310,6 @@ __device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32
     const uint32_t begin = min(n, warp * segment);
     const uint32_t end = min(n, begin + segment);
 
-#ifdef MOE_PHASE_TIMERS
-    long long pass_lap = clock64();
-#define PASS_LAP(slot) do { if (threadIdx.x == 0) { const long long now_ = clock64(); atomicAdd(&g_exact_cycles[slot], static_cast<unsigned long long>(now_ - pass_lap)); pass_lap = now_; } } while (0)
-#else
-#define PASS_LAP(slot) do {} while (0)
-#endif
     for (int d = lane; d < 256; d += 32)
         sh.warp_hist[warp][d] = 0;
     __syncwarp();
@@ -349,7 +334,6 @@ __device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32
         }
     }
     __syncthreads();
-    PASS_LAP(8);
     // exclusive offsets: digit-major, then warp order
     if (tid < 256)
     {
@@ -397,7 +381,6 @@ __device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32
             sh.warp_hist[w][tid] += digit_base;
     }
     __syncthreads();
-    PASS_LAP(9);
     for (uint32_t base = begin; base < end; base += 128)
     {
         uint64_t item[4];
@@ -433,7 +416,6 @@ __device__ void radix_pass(const uint64_t* items_in, uint64_t* items_out, uint32
         }
     }
     __syncthreads();
-    PASS_LAP(10);
 }
 
 // ---- order by value buckets: one scatter and a look inside each bucket -------------------------
@@ -484,12 +466,6 @@ __device__ bool order_by_buckets(const uint64_t* items_in, uint64_t* scattered, 
     if (!(map.scale < INFINITY))
         return false;
 
-#ifdef MOE_PHASE_TIMERS
-    long long order_lap = clock64();
-#define ORDER_LAP(slot) do { if (threadIdx.x == 0) { const long long now_ = clock64(); atomicAdd(&g_exact_cycles[slot], static_cast<unsigned long long>(now_ - order_lap)); order_lap = now_; } } while (0)
-#else
-#define ORDER_LAP(slot) do {} while (0)
-#endif
     for (uint32_t b = tid; b < kOrderBuckets; b += kExactThreads)
         cursor[b] = 0;
     __syncthreads();
@@ -508,7 +484,6 @@ __device__ bool order_by_buckets(const uint64_t* items_in, uint64_t* scattered, 
                 atomicAdd(&cursor[order_bucket(item[u], map)], 1u);
     }
     __syncthreads();
-    ORDER_LAP(6);
     // exclusive scan of the counts (consecutive buckets per thread) and the largest bucket
     constexpr uint32_t kPerThread = kOrderBuckets / kExactThreads;
     uint32_t counts[kPerThread];
@@ -551,7 +526,6 @@ __device__ bool order_by_buckets(const uint64_t* items_in, uint64_t* scattered, 
         before += counts[j];
     }
     __syncthreads();
-    ORDER_LAP(14);
     // scatter: the slot comes from the bucket's cursor, which ends at the end of its bucket
     for (uint32_t base = 0; base < n; base += 4u * kExactThreads)
     {
@@ -568,18 +542,11 @@ __device__ bool order_by_buckets(const uint64_t* items_in, uint64_t* scattered, 
                 scattered[atomicAdd(&cursor[order_bucket(item[u], map)], 1u)] = item[u];
     }
     __syncthreads();
-    ORDER_LAP(15);
     // order inside the buckets
     uint64_t* const mine = stage + static_cast<size_t>(warp) * (kOrderStageItems + kOrderStagePad);
     const uint32_t chunks = (n + kOrderChunk - 1u) / kOrderChunk;
     for (uint32_t chunk = warp; chunk < chunks; chunk += kExactWarps)
     {
-#ifdef MOE_PHASE_TIMERS
-        long long c_lap = clock64();
-#define C_LAP(slot) do { if (tid == 0) { const long long now_ = clock64(); atomicAdd(&g_order_cycles[slot], static_cast<unsigned long long>(now_ - c_lap)); c_lap = now_; } } while (0)
-#else
-#define C_LAP(slot) do {} while (0)
-#endif
         // The window: the chunk's positions and the longest bucket that may reach past them.  The
         // chunk owns the buckets that begin inside its positions; where those begin and end follows
         // from the buckets of the items at the chunk's first position and at the next chunk's.
@@ -599,7 +566,6 @@ __device__ bool order_by_buckets(const uint64_t* items_in, uint64_t* scattered, 
         if (lane < kOrderStagePad)
             mine[kOrderStageItems + lane] = ~0ull;
         __syncwarp();
-        C_LAP(1);
         // first position the chunk owns: the start of the first bucket that begins at or after window_begin
         const uint32_t head_bucket = order_bucket(mine[0], map);
         const uint32_t head_start = head_bucket == 0u ? 0u : cursor[head_bucket - 1u];
@@ -611,7 +577,6 @@ __device__ bool order_by_buckets(const uint64_t* items_in, uint64_t* scattered, 
             const uint32_t next_start = next_bucket == 0u ? 0u : cursor[next_bucket - 1u];
             end = next_start == window_begin + kOrderChunk ? next_start : cursor[next_bucket];
         }
-        C_LAP(0);
 #pragma unroll
         for (uint32_t u = 0; u < kPerLane; ++u)
         {
@@ -630,11 +595,6 @@ __device__ bool order_by_buckets(const uint64_t* items_in, uint64_t* scattered, 
             records_out[bucket_begin + rank] = ~item;
         }
         __syncwarp();
-        C_LAP(2);
-#ifdef MOE_PHASE_TIMERS
-        if (tid == 0)
-            atomicAdd(&g_order_cycles[3], 1ull);
-#endif
     }
     __syncthreads();
     return true;
@@ -1295,14 +1255,6 @@ __device__ void exact_row(const SampleArgs& a, uint32_t row, uint32_t* slot_keys
                     ordered = order_by_buckets(items[0], items[1], items[0], n, sh.max_key, sh.min_live_key, order_words,
                                                reinterpret_cast<uint64_t*>(order_words + kOrderBuckets), sh);
                     complemented = ordered;
-#ifdef MOE_PHASE_TIMERS
-                    if (tid == 0)
-                    {
-                        atomicAdd(&g_exact_cycles[ordered ? 11 : 12], 1ull);
-                        if (!ordered)
-                            printf("fallback row %u n %u max %08x min %08x\n", row, n, sh.max_key, sh.min_live_key);
-                    }
-#endif
                 }
             }
             if (n > 1 && !ordered)

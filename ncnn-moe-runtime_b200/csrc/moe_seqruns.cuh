@@ -21,12 +21,6 @@
 
 #include "moe_seqscan.cuh"
 
-#ifdef MOE_PHASE_TIMERS
-__device__ unsigned long long g_seq_debug[8]; // rounds, runs looked at, cycles: to barrier 1, to barrier 2, rest, search
-#define SEQ_LAP(slot) do { if (tid == 0) { const long long now_ = clock64(); atomicAdd(&g_seq_debug[slot], static_cast<unsigned long long>(now_ - lap_)); lap_ = now_; } } while (0)
-#else
-#define SEQ_LAP(slot) do {} while (0)
-#endif
 
 namespace moe {
 
@@ -223,12 +217,8 @@ __device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, 
         if (stopped)
             return SeqRunsResult{acc, cum[run] + done, true, false};
     }
-#ifdef MOE_PHASE_TIMERS
-    long long lap_ = clock64();
-#endif
     for (;;)
     {
-        SEQ_LAP(4);
         while (run < runs && cum[run] < limit && done >= copies_of(run))
         {
             ++run;
@@ -272,14 +262,6 @@ __device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, 
             chunk = min(chunk, max(expected + (expected >> 5) + 8u, 64u));
         }
 
-        SEQ_LAP(5);
-#ifdef MOE_PHASE_TIMERS
-        if (tid == 0)
-        {
-            atomicAdd(&g_seq_debug[0], 1ull);
-            atomicAdd(&g_seq_debug[1], static_cast<unsigned long long>(chunk));
-        }
-#endif
         // my consecutive runs of the chunk: as few per thread as the chunk allows (the round is
         // as long as one thread's work)
         const uint32_t per_thread = (chunk + kThreads - 1u) / kThreads;
@@ -347,7 +329,6 @@ __device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, 
             sh.stopped = 0;
         }
         __syncthreads();
-        SEQ_LAP(2);
         const uint32_t start_parity = start_integer & 1u;
         uint32_t before = 0; // integer steps taken before my first run
         if (warp_active)
@@ -405,7 +386,6 @@ __device__ __noinline__ SeqRunsResult block_sequential_sum_runs(const float* x, 
         if (event != 0xFFFFFFFFu)
             atomicMin(&sh.first_event, event);
         __syncthreads();
-        SEQ_LAP(3);
         const uint32_t first_event = sh.first_event;
         if (first_event == 0xFFFFFFFFu)
         {
