@@ -293,10 +293,8 @@ def time_step_graph(torch, step, steps, chunk, min_seconds, clocks=None, barrier
     if barrier is not None:
         # every rank must replay the same number of times: the graph may hold a collective, and the
         # probe above times differently on every rank
-        import torch.distributed as dist
-        agreed = torch.tensor([replays], dtype=torch.int64, device="cuda")
-        dist.all_reduce(agreed, op=dist.ReduceOp.MAX)
-        replays = int(agreed.item())
+        parallel = __import__(graft.PACKAGE_NAME + ".parallel", fromlist=["parallel"])
+        replays = parallel.agree_on_maximum(replays, device="cuda")
         barrier()
     torch.cuda.synchronize()
     if clocks is not None:

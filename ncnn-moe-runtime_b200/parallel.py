@@ -46,3 +46,17 @@ def all_gather_candidates(local_candidates, group=None):
     gathered = torch.empty((world * rows,) + tuple(local_candidates.shape[1:]), dtype=local_candidates.dtype, device=local_candidates.device)
     dist.all_gather_into_tensor(gathered, local_candidates.contiguous(), group=group)
     return gathered.view((world, rows) + tuple(local_candidates.shape[1:]))
+
+
+def agree_on_maximum(value: int, device="cpu", group=None) -> int:
+    """The largest `value` any rank holds, on every rank (one all-reduce).
+
+    For decisions every rank must take alike although each derives them from its own
+    measurement — e.g. how often a timed CUDA graph that holds a collective is replayed:
+    ranks that replay it a different number of times leave the collective unmatched and hang."""
+    import torch
+    import torch.distributed as dist
+
+    holder = torch.tensor([int(value)], dtype=torch.int64, device=device)
+    dist.all_reduce(holder, op=dist.ReduceOp.MAX, group=group)
+    return int(holder.item())

@@ -72,6 +72,8 @@ def _worker(rank, world, port, rows, vocab, top_k, queue):
     whole = oracle.sample_batch(logits, np.full(rows, 0.8, np.float32), np.full(rows, 20, np.uint32), np.full(rows, 0.9, np.float32),
                                 np.zeros(rows, np.float32), uniforms, threads=1)
     ok_rows = np.array_equal(tokens, whole["token"])
+    # --- a count every rank derives from its own clock is agreed before it is used ----
+    ok_rows = ok_rows and parallel.agree_on_maximum(10 + 5 * rank) == 10 + 5 * (world - 1)
     queue.put((rank, ok_vocab, ok_rows))
     dist.barrier()
     dist.destroy_process_group()
