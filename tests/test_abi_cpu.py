@@ -72,6 +72,15 @@ def test_sampler_needs_a_gpu_and_has_no_fallback(pkg):
         raise AssertionError("creating a sampler without a GPU must fail")
 
 
+def test_entry_points_refuse_a_null_handle(pkg):
+    """Every call that takes a sampler answers MOE_STATUS_INVALID_ARGUMENT (1) to a null handle instead of
+    touching the device: checkable without a GPU."""
+    library = pkg.library()
+    assert library.moe_speculative_verify_batch(None, None, None, None, pkg.DTYPE_F32, 2, 4, 128, 128, None, None, None, None) == 1
+    assert library.moe_speculative_verify(None, None, None, None, pkg.DTYPE_F32, 4, 128, 128, None, None, None, None) == 1
+    assert library.moe_sample_batch(None, None, None, pkg.DTYPE_F32, 1, 128, 128, None, 0, None, None, None, None, None, None, None, 0) == 1
+
+
 def test_shard_ranges(pkg):
     parallel = __import__("ncnn_moe_runtime_b200.parallel", fromlist=["x"])
     for total in (0, 1, 7, 256, 8192, 1048576):
