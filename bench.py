@@ -36,6 +36,7 @@ the same line shape with "impl": "reference".
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import sys
@@ -54,6 +55,7 @@ METRIC = "sampled rows/s at vocab 201088, batch 256"
 UNIT = "rows/s"
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only when MEASURED_PEAKS.json is absent
 MIN_TIMED_SECONDS = 0.5
+GROUP_TIMEOUT = datetime.timedelta(seconds=240)  # process-group watchdog: longer than any rank's host-side work
 
 WORKLOADS = {
     # name: (generator, kwargs, dtype label, description)
@@ -677,7 +679,7 @@ def run_vocab_sharded_bench(args):
     torch.cuda.set_device(local_rank)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29533")
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), rank=rank, world_size=world)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), rank=rank, world_size=world, timeout=GROUP_TIMEOUT)
     package = graft.load_package()
     workloads = __import__(graft.PACKAGE_NAME + ".workloads", fromlist=["workloads"])
     parallel = __import__(graft.PACKAGE_NAME + ".parallel", fromlist=["parallel"])
@@ -731,7 +733,8 @@ def main() -> int:
     distributed = world > 1
     if distributed:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # a collective left unmatched ends the run after four minutes instead of the default ten
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=GROUP_TIMEOUT)
     barrier = dist.barrier if distributed else None
 
     package = graft.load_package()
